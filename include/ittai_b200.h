@@ -1,0 +1,156 @@
+/*
+ * ittai_b200 — C ABI of the B200 (sm_100a) inference kernels behind the Python engines.
+ *
+ * The reference has no FFI layer: its device code is CuTe-DSL Python compiled at run time and
+ * launched from `Engine.forward` (reference src/ittai/qwen3/engine.py:141,153-187 and
+ * src/ittai/siglip/kernel.py:614-620,651-664).  These entry points replace that compile-and-launch
+ * step.  Conventions for every function:
+ *   - returns 0 on success, a negative ITTAI_E_* code otherwise; ittai_last_error() gives the text;
+ *   - all data pointers are DEVICE pointers borrowed from the caller (torch owns every buffer, as the
+ *     reference's Engine owns its tensors: src/ittai/qwen3/engine.py:123-140);
+ *   - `stream` is a cudaStream_t passed as void*; launch functions enqueue work and return, they do not
+ *     synchronise, allocate or read device memory on the host;
+ *   - device-side waits are bounded: a wait that runs out records a code in the `status` words of the
+ *     call's struct and every CTA leaves the kernel; the host decodes it with ittai_decode_status().
+ *
+ * Model widths are compile-time (Qwen3-0.6B: reference src/ittai/qwen3/config.py:1-5); layer count,
+ * vocabulary, batch and cache capacity are run-time.
+ */
+#ifndef ITTAI_B200_H
+#define ITTAI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ITTAI_ABI_VERSION 1
+
+/* Qwen3-0.6B widths (reference src/ittai/qwen3/config.py:1-5). */
+#define ITTAI_Q3_D 1024
+#define ITTAI_Q3_NH 16
+#define ITTAI_Q3_NKV 8
+#define ITTAI_Q3_HD 128
+#define ITTAI_Q3_FF 3072
+#define ITTAI_Q3_DQ 2048
+#define ITTAI_Q3_DKV 1024
+#define ITTAI_Q3_DQKV 4096
+#define ITTAI_Q3_DGU 6144
+
+#define ITTAI_MAX_BATCH 8
+
+/* IttaiQwen3Decode.flags */
+#define ITTAI_F_L2_PREFETCH 1 /* while a phase runs, ask L2 to fetch the weights of the phase that follows */
+
+enum {
+    ITTAI_OK = 0,
+    ITTAI_E_ARG = -1,     /* bad argument (null pointer, size out of range, misaligned pointer) */
+    ITTAI_E_CUDA = -2,    /* a CUDA runtime call failed; see ittai_last_error() */
+    ITTAI_E_DEVICE = -3,  /* not an sm_100 device, or it cannot co-schedule the persistent grid */
+    ITTAI_E_STATUS = -4   /* the device status words report a failed wait */
+};
+
+/* Device status words written by a kernel whose bounded wait ran out (status[0] != 0). */
+#define ITTAI_STATUS_WORDS 8
+enum {
+    ITTAI_ST_OK = 0,
+    ITTAI_ST_BARRIER_TIMEOUT = 1, /* status[1]=phase tag, status[2]=CTA, status[3]=counter seen, status[4]=target */
+    ITTAI_ST_FLAG_TIMEOUT = 2,
+    ITTAI_ST_BAD_TOKEN = 3        /* status[1]=token id, status[2]=step */
+};
+
+/* Phases of one decoded token, in execution order inside a layer (ids used by ittai_qwen3_phase_launch). */
+enum {
+    ITTAI_PH_QKV = 0,   /* embed gather (layer 0) + RMSNorm + QKV GEMV                         */
+    ITTAI_PH_ATTN = 1,  /* QK-RMSNorm + RoPE + in-place KV append + split-K GQA attention + combine */
+    ITTAI_PH_OPROJ = 2, /* O-proj GEMV + residual                                              */
+    ITTAI_PH_GU = 3,    /* RMSNorm + gate/up GEMV + SwiGLU                                     */
+    ITTAI_PH_DOWN = 4,  /* down-proj GEMV + residual                                           */
+    ITTAI_PH_HEAD = 5   /* final RMSNorm + tied lm_head GEMV + argmax                          */
+};
+
+/*
+ * Everything one Qwen3 decode launch needs.  Weight layout follows the reference's packed engine
+ * (src/ittai/qwen3/engine.py:100-117) except that the norm gains stay separate (so the bf16 rounding
+ * points are those of the eager modules) and Q/K rows keep the half-split RoPE order, so the cache holds
+ * keys exactly as the eager model's cache does.
+ * All matrices are bf16, row-major [out_features, in_features], stacked over layers.
+ */
+typedef struct IttaiQwen3Decode {
+    int32_t n_layers;   /* L                                                                   */
+    int32_t vocab;      /* V                                                                   */
+    int32_t kv_cap;     /* cache capacity in tokens per sequence                               */
+    int32_t batch;      /* B, 1..ITTAI_MAX_BATCH                                               */
+    int32_t n_steps;    /* tokens to run in this launch (>= 1)                                 */
+    int32_t n_forced;   /* first n_forced steps take their input id from `forced` (prompt feeding);
+                           lm_head + argmax run only from step n_forced-1 on                   */
+    float eps;          /* RMSNorm epsilon                                                     */
+    int32_t write_logits; /* non-zero: store bf16 logits of the last step that ran the head    */
+    int32_t flags;      /* ITTAI_F_* bits                                                      */
+    int32_t reserved0;
+
+    const void* wqkv;   /* [L, 4096, 1024] rows: q(2048) | k(1024) | v(1024)                   */
+    const void* wo;     /* [L, 1024, 2048]                                                     */
+    const void* wgu;    /* [L, 6144, 1024] gate row i at 2i, up row i at 2i+1 (engine.py:110-111) */
+    const void* wd;     /* [L, 1024, 3072]                                                     */
+    const void* ln1;    /* [L, 1024] input_layernorm gain                                      */
+    const void* ln2;    /* [L, 1024] post_attention_layernorm gain                             */
+    const void* qn;     /* [L, 128] q_norm gain                                                */
+    const void* kn;     /* [L, 128] k_norm gain                                                */
+    const void* fin_w;  /* [1024] final norm gain                                              */
+    const void* embed;  /* [V, 1024] embedding table = tied lm_head                            */
+    const void* rope;   /* [kv_cap, 128] bf16: cos[0..63] | sin[0..63] per position            */
+
+    void* kcache;       /* [L, B, 8, kv_cap, 128] bf16                                         */
+    void* vcache;       /* [L, B, 8, kv_cap, 128] bf16                                         */
+    int32_t* pos;       /* [B] tokens already in each sequence's cache; advanced by n_steps    */
+    int32_t* next_id;   /* [B] input id of the first free-running step; holds the last argmax after the launch */
+    const int32_t* forced; /* [n_forced, B] or NULL                                            */
+    int32_t* out_ids;   /* [n_steps, B] argmax of each step (-1 where the head did not run)    */
+    void* logits;       /* [B, V] bf16 (may be NULL when write_logits == 0)                    */
+
+    void* workspace;    /* ittai_qwen3_decode_workspace_bytes() bytes, 256-byte aligned        */
+    uint32_t* status;   /* [ITTAI_STATUS_WORDS] device words, zeroed by the launch             */
+    uint64_t* step_ns;  /* [n_steps] device: globaltimer at the end of each step, or NULL      */
+} IttaiQwen3Decode;
+
+/* ---- library ------------------------------------------------------------------------------------ */
+
+/* ABI version of the loaded library (ITTAI_ABI_VERSION). */
+int ittai_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* ittai_last_error(void);
+
+/* Checks that `device` is an sm_100 part able to run the persistent grid; fills *n_sms (may be NULL).
+ * Replaces the capability probe of reference src/ittai/qwen3/model.py:22-24. */
+int ittai_device_check(int device, int* n_sms);
+
+/* Turns a host copy of the device status words into text.  Returns 0 when status[0]==0,
+ * ITTAI_E_STATUS otherwise.  The reference has no counterpart: its device waits are unbounded
+ * (src/ittai/qwen3/base.py:53-57). */
+int ittai_decode_status(const uint32_t* status_host, char* msg, size_t msg_len);
+
+/* ---- Qwen3 decode ------------------------------------------------------------------------------- */
+
+/* Scratch bytes the decode kernels need for `batch` sequences (activations, split-K partials, argmax
+ * candidates, barrier and arrival counters).  Replaces the buffer plan of engine.py:123-134. */
+int ittai_qwen3_decode_workspace_bytes(int batch, size_t* bytes);
+
+/* One persistent cooperative launch that runs p->n_steps tokens: per layer RMSNorm+QKV, QK-norm+RoPE+
+ * KV append + split-K GQA attention, O-proj+residual, gate/up SwiGLU, down+residual, then final norm +
+ * tied lm_head + argmax, with the chosen id fed back on the device.  Replaces the launch of
+ * engine.py:153-155 (`_graph_body`) for the decode loop the reference does not have. */
+int ittai_qwen3_decode_launch(const IttaiQwen3Decode* p, void* stream);
+
+/* Runs ONE phase (ITTAI_PH_*) of layer `layer` as its own kernel with the same grid and the same device
+ * code as the persistent kernel, for unit parity tests and per-phase profiling.  `pos`/`next_id` are
+ * read, not advanced. */
+int ittai_qwen3_phase_launch(const IttaiQwen3Decode* p, int phase, int layer, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ITTAI_B200_H */

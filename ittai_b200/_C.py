@@ -1,0 +1,80 @@
+"""ctypes binding of ``libittai_b200.so`` (the C ABI of ``include/ittai_b200.h``).
+
+The reference compiles its kernels at construction time (reference ``src/ittai/qwen3/engine.py:141``);
+here the library is prebuilt and only loaded.  A missing library is an error, never a fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libittai_b200.so")
+
+ABI_VERSION = 1
+MAX_BATCH = 8
+STATUS_WORDS = 8
+F_L2_PREFETCH = 1
+PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
+
+# every symbol include/ittai_b200.h declares
+EXPORTS = (
+    "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
+    "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
+)
+
+
+class IttaiError(RuntimeError):
+    pass
+
+
+class Qwen3Decode(C.Structure):
+    """Mirror of ``struct IttaiQwen3Decode``."""
+    _fields_ = [
+        ("n_layers", C.c_int32), ("vocab", C.c_int32), ("kv_cap", C.c_int32), ("batch", C.c_int32),
+        ("n_steps", C.c_int32), ("n_forced", C.c_int32), ("eps", C.c_float), ("write_logits", C.c_int32),
+        ("flags", C.c_int32), ("reserved0", C.c_int32),
+        ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("wgu", C.c_void_p), ("wd", C.c_void_p),
+        ("ln1", C.c_void_p), ("ln2", C.c_void_p), ("qn", C.c_void_p), ("kn", C.c_void_p),
+        ("fin_w", C.c_void_p), ("embed", C.c_void_p), ("rope", C.c_void_p),
+        ("kcache", C.c_void_p), ("vcache", C.c_void_p), ("pos", C.c_void_p), ("next_id", C.c_void_p),
+        ("forced", C.c_void_p), ("out_ids", C.c_void_p), ("logits", C.c_void_p),
+        ("workspace", C.c_void_p), ("status", C.c_void_p), ("step_ns", C.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the shared library once; raise if it is missing or of another ABI version."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise IttaiError(f"{LIB_PATH} is missing: build it with `python -m ittai_b200.build` (there is no fallback path)")
+    L = C.CDLL(LIB_PATH)
+    L.ittai_version.restype = C.c_int
+    L.ittai_last_error.restype = C.c_char_p
+    L.ittai_device_check.argtypes = [C.c_int, C.POINTER(C.c_int)]
+    L.ittai_decode_status.argtypes = [C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]
+    L.ittai_qwen3_decode_workspace_bytes.argtypes = [C.c_int, C.POINTER(C.c_size_t)]
+    L.ittai_qwen3_decode_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
+    L.ittai_qwen3_phase_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_int, C.c_int, C.c_void_p]
+    if L.ittai_version() != ABI_VERSION:
+        raise IttaiError(f"library ABI {L.ittai_version()} != binding ABI {ABI_VERSION}; rebuild")
+    _lib = L
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise IttaiError(f"ittai_b200 call failed ({rc}): {lib().ittai_last_error().decode()}")
+
+
+def decode_status(words) -> None:
+    """Raise if a host copy of the device status words reports a failed wait."""
+    arr = (C.c_uint32 * STATUS_WORDS)(*[int(w) for w in words])
+    msg = C.create_string_buffer(256)
+    if lib().ittai_decode_status(arr, msg, 256) != 0:
+        raise IttaiError(msg.value.decode())

@@ -1,0 +1,27 @@
+"""Qwen3-0.6B geometry and op vocabulary, under the names the reference exports
+(reference ``src/ittai/qwen3/config.py:1-20``; its benchmark imports ``D, DQ, DQKV, DGU, FF, L``).
+
+``VOCAB`` is the 151936-row table of Qwen3-0.6B; the reference's constant (151669, the embedding
+checkpoint's tokenizer size) is never read by its code, the table height always comes from the weights.
+"""
+D, NH, NKV, HD, FF, L, VOCAB, EPS, THETA = 1024, 16, 8, 128, 3072, 28, 151936, 1e-6, 1e6
+DQ, DKV = NH * HD, NKV * HD
+DQKV, DGU = DQ + 2 * DKV, 2 * FF
+K_OFF, V_OFF = DQ, DQ + DKV
+G = NH // NKV
+LOG2E = 1.4426950408889634
+SCALE_LOG2 = HD ** -0.5 * LOG2E
+
+# decode phases in execution order (ids of include/ittai_b200.h: ITTAI_PH_*)
+PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
+PHASE_NAMES = ("qkv", "attn", "oproj", "gu", "down", "head")
+
+
+def decode_bytes_per_token(kv_len: int, n_layers: int = L, vocab: int = VOCAB) -> int:
+    """Algorithmic HBM bytes one batch-1 decoded token must move at cache length ``kv_len``:
+    every weight once (tied lm_head included), the whole KV cache once, the appended K/V row, one embedding row."""
+    layer = 2 * (DQKV * D + D * DQ + DGU * D + D * FF)
+    gains = 2 * (n_layers * (2 * D + 2 * HD) + D)
+    weights = n_layers * layer + 2 * vocab * D + gains
+    kv_row = n_layers * 2 * NKV * HD * 2
+    return weights + kv_row * kv_len + kv_row + 2 * D

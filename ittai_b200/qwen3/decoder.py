@@ -1,0 +1,208 @@
+"""Host engine of the Qwen3-0.6B KV-cache decode loop.
+
+The reference's ``Engine`` (reference ``src/ittai/qwen3/engine.py:87-187``) packs weights, owns every
+device buffer as a torch tensor and launches one persistent kernel per forward; this class keeps that
+shape for the decode loop the reference does not have: torch owns the buffers, the C-ABI library
+borrows raw pointers and the current stream, and one cooperative launch runs ``n_steps`` tokens with
+the argmax fed back on the device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _C
+from .config import D, DGU, DQ, DQKV, EPS, FF, HD, NKV, THETA
+
+
+def _strip(sd: dict) -> dict:
+    """Drop the ``model.`` prefix as the reference does (``src/ittai/qwen3/engine.py:91``)."""
+    return {k.removeprefix("model."): v for k, v in sd.items()}
+
+
+def pack_weights(sd: dict, n_layers: int, device) -> dict:
+    """Layer-stacked bf16 matrices in the layout ``include/ittai_b200.h`` documents.
+
+    Differences from the reference's packing (``src/ittai/qwen3/engine.py:100-117``): the norm gains are
+    kept as separate bf16 vectors instead of being folded into the weights, and Q/K rows stay in the
+    half-split RoPE order (no ``rope_perm``), so the cache holds keys exactly as the eager model does.
+    Gate and up rows are interleaved as there (``:110-111``).
+    """
+    sd = _strip(sd)
+    bf = lambda t: t.detach().to(torch.bfloat16).contiguous().to(device)
+    wqkv, wo, wgu, wd, ln1, ln2, qn, kn = ([] for _ in range(8))
+    for l in range(n_layers):
+        p = f"layers.{l}."
+        wqkv.append(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]))
+        wo.append(sd[p + "self_attn.o_proj.weight"])
+        wgu.append(torch.stack([sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]], 1).reshape(DGU, D))
+        wd.append(sd[p + "mlp.down_proj.weight"])
+        ln1.append(sd[p + "input_layernorm.weight"])
+        ln2.append(sd[p + "post_attention_layernorm.weight"])
+        qn.append(sd[p + "self_attn.q_norm.weight"])
+        kn.append(sd[p + "self_attn.k_norm.weight"])
+    out = dict(wqkv=bf(torch.stack(wqkv)), wo=bf(torch.stack(wo)), wgu=bf(torch.stack(wgu)), wd=bf(torch.stack(wd)),
+               ln1=bf(torch.stack(ln1)), ln2=bf(torch.stack(ln2)), qn=bf(torch.stack(qn)), kn=bf(torch.stack(kn)),
+               fin_w=bf(sd["norm.weight"]), embed=bf(sd["embed_tokens.weight"]))
+    assert out["wqkv"].shape == (n_layers, DQKV, D) and out["wo"].shape == (n_layers, D, DQ)
+    assert out["wgu"].shape == (n_layers, DGU, D) and out["wd"].shape == (n_layers, D, FF)
+    return out
+
+
+def rope_table(kv_cap: int, device, theta: float = THETA) -> torch.Tensor:
+    """bf16 [kv_cap, 128]: cos of the 64 pair angles, then sin; angle = pos * theta**(-2i/128) in fp32.
+
+    Same angles as the reference's table (``src/ittai/qwen3/engine.py:118-122``), rounded to bf16 because the
+    eager rotary module hands bf16 cos/sin to bf16 queries and keys.
+    """
+    inv = 1.0 / (theta ** (torch.arange(0, HD, 2, dtype=torch.int64).to(torch.float32) / HD))
+    ang = torch.arange(kv_cap, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cat([ang.cos(), ang.sin()], 1).to(torch.bfloat16).contiguous().to(device)
+
+
+class Qwen3Decoder:
+    """Greedy batch decode with an in-place bf16 KV cache ``[L, B, 8, kv_capacity, 128]``.
+
+    ``sd_or_model``: a Hugging Face Qwen3 module or its ``state_dict`` (no hub access is needed).
+    ``.prefill(ids)`` feeds a prompt, ``.decode(n)`` runs n greedy steps, ``.logits`` holds the bf16 logits of
+    the last step, ``.kcache`` / ``.vcache`` are the cache tensors.
+    """
+
+    def __init__(self, sd_or_model, max_batch: int = 1, kv_capacity: int = 8192, device="cuda", l2_prefetch: bool = True):
+        sd = sd_or_model if isinstance(sd_or_model, dict) else sd_or_model.state_dict()
+        sd = _strip(sd)
+        if max_batch not in (1, 2, 4, 8):
+            raise ValueError("max_batch must be 1, 2, 4 or 8")
+        self.dev = torch.device(device)
+        self.lib = _C.lib()
+        n_sms = C.c_int()
+        _C.check(self.lib.ittai_device_check(self.dev.index or 0, C.byref(n_sms)))
+        self.n_sms = n_sms.value
+        self.L = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
+        self.V = sd["embed_tokens.weight"].shape[0]
+        self.B, self.cap = max_batch, kv_capacity
+        self.w = pack_weights(sd, self.L, self.dev)
+        self.rope = rope_table(kv_capacity, self.dev)
+        z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt, device=self.dev)
+        self.kcache = z(self.L, self.B, NKV, self.cap, HD)
+        self.vcache = z(self.L, self.B, NKV, self.cap, HD)
+        self.pos = z(self.B, dt=torch.int32)
+        self.next_id = z(self.B, dt=torch.int32)
+        self.logits = z(self.B, self.V)
+        self.status = z(_C.STATUS_WORDS, dt=torch.int32)
+        nbytes = C.c_size_t()
+        _C.check(self.lib.ittai_qwen3_decode_workspace_bytes(self.B, C.byref(nbytes)))
+        self.workspace = z(nbytes.value + 256, dt=torch.uint8)
+        self._ws_ptr = (self.workspace.data_ptr() + 255) // 256 * 256
+        self.flags = _C.F_L2_PREFETCH if l2_prefetch else 0
+        self.lengths = [0] * self.B          # host mirror of `pos`, for capacity checks without a device read
+        self._keep = None
+
+    # ---- plumbing -------------------------------------------------------------------------------
+    def _params(self, n_steps, n_forced, forced, out_ids, step_ns, write_logits=True) -> _C.Qwen3Decode:
+        p = _C.Qwen3Decode()
+        p.n_layers, p.vocab, p.kv_cap, p.batch = self.L, self.V, self.cap, self.B
+        p.n_steps, p.n_forced, p.eps, p.write_logits, p.flags = n_steps, n_forced, EPS, int(write_logits), self.flags
+        for k, t in self.w.items():
+            setattr(p, k, t.data_ptr())
+        p.rope, p.kcache, p.vcache = self.rope.data_ptr(), self.kcache.data_ptr(), self.vcache.data_ptr()
+        p.pos, p.next_id = self.pos.data_ptr(), self.next_id.data_ptr()
+        p.forced = forced.data_ptr() if forced is not None else None
+        p.out_ids, p.logits = out_ids.data_ptr(), self.logits.data_ptr()
+        p.workspace, p.status = self._ws_ptr, self.status.data_ptr()
+        p.step_ns = step_ns.data_ptr() if step_ns is not None else None
+        return p
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a bounded device wait ran out during the last launch."""
+        _C.decode_status(self.status.cpu().tolist())
+
+    def reset(self) -> None:
+        self.pos.zero_()
+        self.lengths = [0] * self.B
+
+    def _launch(self, n_steps, forced=None, timed=False, check=True):
+        if max(self.lengths) + n_steps > self.cap:
+            raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths)} cached + {n_steps} steps")
+        n_forced = 0 if forced is None else forced.shape[0]
+        out_ids = torch.empty(n_steps, self.B, dtype=torch.int32, device=self.dev)
+        step_ns = torch.zeros(n_steps, dtype=torch.int64, device=self.dev) if timed else None
+        p = self._params(n_steps, n_forced, forced, out_ids, step_ns)
+        self._keep = (p, forced, out_ids, step_ns)
+        _C.check(self.lib.ittai_qwen3_decode_launch(C.byref(p), self._stream()))
+        self.lengths = [n + n_steps for n in self.lengths]
+        if check:
+            self.check_status()
+        return out_ids, step_ns
+
+    # ---- public API -----------------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, ids) -> torch.Tensor:
+        """Feed prompts ``ids`` ([B, T] ints, equal lengths) into the cache; returns the first greedy id per sequence.
+
+        The prompt is fed token by token through the decode kernel (ids forced, lm_head only on the last one).
+        """
+        ids = torch.as_tensor(ids, dtype=torch.int32)
+        if ids.dim() == 1:
+            ids = ids[None]
+        assert ids.shape[0] == self.B, "one prompt per sequence of the batch"
+        forced = ids.t().contiguous().to(self.dev, non_blocking=True)       # [T, B]
+        out, _ = self._launch(forced.shape[0], forced=forced)
+        return out[-1]
+
+    @torch.no_grad()
+    def decode(self, n_steps: int, timed: bool = False, check: bool = True):
+        """Run ``n_steps`` greedy steps from ``next_id``; returns int32 ``[B, n_steps]`` (device tensor).
+
+        With ``timed`` also returns the device ``globaltimer`` stamp (ns) taken at the end of every step.
+        """
+        out, ns = self._launch(n_steps, timed=timed, check=check)
+        return (out.t(), ns) if timed else out.t()
+
+    @torch.no_grad()
+    def decode_forced(self, ids) -> torch.Tensor:
+        """Teacher forcing: feed ``ids`` ([B, T]) one per step but run the head on every step.
+
+        Returns the model's own argmax ``[B, T]``; ``.logits`` holds the last step's logits.
+        """
+        ids = torch.as_tensor(ids, dtype=torch.int32)
+        if ids.dim() == 1:
+            ids = ids[None]
+        outs = []
+        for t in range(ids.shape[1]):
+            self.next_id.copy_(ids[:, t].to(self.dev))
+            outs.append(self.decode(1)[:, 0].clone())
+        return torch.stack(outs, 1)
+
+    @torch.no_grad()
+    def run_phase(self, phase: int, layer: int) -> None:
+        """Launch one phase of one layer as its own kernel (unit tests, per-phase profiles)."""
+        out_ids = torch.empty(1, self.B, dtype=torch.int32, device=self.dev)
+        p = self._params(1, 0, None, out_ids, None)
+        self._keep = (p, out_ids)
+        _C.check(self.lib.ittai_qwen3_phase_launch(C.byref(p), phase, layer, self._stream()))
+        self.check_status()
+
+    def workspace_views(self) -> dict:
+        """Typed views of the activation scratch (h, qkv, attn, act) for phase-level tests."""
+        off = self._ws_ptr - self.workspace.data_ptr()
+        up = lambda n: (n + 255) // 256 * 256
+        views, o = {}, off + up(128 * 4)
+        for name, n in (("h", D), ("qkv", DQKV), ("attn", DQ), ("act", FF)):
+            nb = self.B * n * 2
+            views[name] = self.workspace[o:o + nb].view(torch.bfloat16).view(self.B, n)
+            o += up(nb)
+        return views
+
+    @torch.no_grad()
+    def generate(self, prompt_host: torch.Tensor, n_steps: int) -> torch.Tensor:
+        """End to end from host memory: copy the prompt ids in, prefill, decode, copy the ids out (host tensor [B, n_steps])."""
+        self.reset()
+        first = self.prefill(prompt_host)
+        rest = self.decode(n_steps - 1) if n_steps > 1 else None
+        out = first[:, None] if rest is None else torch.cat([first[:, None], rest], 1)
+        return out.cpu()

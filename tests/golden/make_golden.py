@@ -1,0 +1,75 @@
+"""Write the golden fixtures in this directory from the Hugging Face eager modules.
+
+Run from the repository root:  python tests/golden/make_golden.py [qwen3_tiny|qwen3_full|siglip ...]
+
+The reference ships no fixtures; these are outputs of the ``transformers`` modules it validates
+against (reference ``src/ittai/qwen3/model.py:32-37``, ``src/ittai/siglip/kernel.py:701-702``),
+built offline from seeded random initialisation.  Weights are not stored: the fixtures are only
+meaningful together with the torch / transformers versions recorded inside them, which regenerate
+the same weights from the same seed.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _versions():
+    import transformers
+    return dict(torch=str(torch.__version__), transformers=transformers.__version__, threads=torch.get_num_threads())
+
+
+def qwen3_tiny():
+    from oracle import qwen3_hf as hf
+    dims = hf.TINY
+    m = hf.build_hf(dims, seed=0)
+    ids = hf.prompt_ids(16, seed=0, vocab=dims.vocab)
+    picks, logits, cache = hf.greedy(m, ids, 8)
+    k1, v1 = hf.cache_kv(cache, 1)
+    torch.save(dict(meta=dict(_versions(), dims=dims.__dict__, seed=0, prompt_seed=0, attn="sdpa", dtype="bf16"),
+                    prompt=ids, ids=picks, logits=logits, k_layer1=k1[0].clone(), v_layer1=v1[0].clone()),
+               os.path.join(HERE, "qwen3_tiny.pt"))
+    print("qwen3_tiny", picks.tolist())
+
+
+def qwen3_full():
+    """BASELINE config 1: full 28-layer model, 32-id prompt seed 0, 64 greedy steps on CPU."""
+    from oracle import qwen3_hf as hf
+    dims = hf.FULL
+    m = hf.build_hf(dims, seed=0)
+    ids = hf.prompt_ids(32, seed=0)
+    picks, logits, cache = hf.greedy(m, ids, 64)
+    top_v, top_i = logits.float().topk(8, dim=-1)
+    k0, v0 = hf.cache_kv(cache, dims.n_layers - 1)
+    torch.save(dict(meta=dict(_versions(), dims=dims.__dict__, seed=0, prompt_seed=0, attn="sdpa", dtype="bf16"),
+                    prompt=ids, ids=picks, top_values=top_v.to(torch.bfloat16), top_indices=top_i.to(torch.int32),
+                    strided_logits=logits[:, ::1009].clone(), logit_norm=logits.float().norm(dim=-1),
+                    k_last_layer_head0=k0[0, 0].clone()),
+               os.path.join(HERE, "qwen3_full_c1.pt"))
+    print("qwen3_full", picks.tolist())
+
+
+def siglip():
+    """BASELINE config 3 at batch 1 and the first 4 images of the batch-64 stream (seed 3)."""
+    from oracle import siglip_hf as hf
+    m = hf.build_hf(seed=2)
+    px = hf.pixels(4, seed=3)
+    with torch.no_grad():
+        out = m(pixel_values=px.to(torch.bfloat16))
+        out32 = m.float()(pixel_values=px)
+    torch.save(dict(meta=dict(_versions(), seed=2, pixel_seed=3, dtype="bf16"),
+                    pooled_bf16=out.pooler_output.clone(), pooled_fp32=out32.pooler_output.clone(),
+                    last_hidden_fp32_img0=out32.last_hidden_state[0, ::49].clone()),
+               os.path.join(HERE, "siglip_b16.pt"))
+    print("siglip", out32.pooler_output[0, :4])
+
+
+if __name__ == "__main__":
+    which = sys.argv[1:] or ["qwen3_tiny", "qwen3_full", "siglip"]
+    for w in which:
+        globals()[w]()
