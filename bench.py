@@ -1,0 +1,259 @@
+"""Headline benchmark: Qwen3-0.6B batch-1 bf16 greedy decode, tokens per second, against the HBM roofline.
+
+Workload (BASELINE config 2): random-init Qwen3-0.6B, 4096-token prompt (uniform ids, seed 1) prefilled into
+a bf16 KV cache of capacity 8192, then 256 greedy decode steps.  One bench "step" is one such 256-token decode
+run starting at cache length 4096 (the cache length is rewound between steps; the prompt is prefilled once, before
+the timed region).  Every token streams about 1.66 GB of weights and cache, far more than the 126 MB L2, so no L2
+flush is needed between steps.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N > 1 runs N independent replicas (one process per GPU, launched by torchrun; no data-path collective) and sums
+their tokens.  ``--impl reference`` times the reference's eager PyTorch path (the Hugging Face modules it loads
+and validates against) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT, CAP, DECODE = 4096, 8192, 256
+METRIC, UNIT = "qwen3_0.6b_bs1_decode_tok_per_s", "tok/s"
+
+
+def synthetic_state_dict(n_layers=28, vocab=151936, seed=0, device="cuda"):
+    """Random-init Qwen3-0.6B weights under the Hugging Face key names: normal(0, 0.02) matrices, unit norm gains."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda *s: (torch.randn(*s, generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    one = lambda n: torch.ones(n, dtype=torch.bfloat16, device=device)
+    sd = {"embed_tokens.weight": rn(vocab, 1024), "norm.weight": one(1024)}
+    for l in range(n_layers):
+        p = f"layers.{l}."
+        sd[p + "self_attn.q_proj.weight"] = rn(2048, 1024)
+        sd[p + "self_attn.k_proj.weight"] = rn(1024, 1024)
+        sd[p + "self_attn.v_proj.weight"] = rn(1024, 1024)
+        sd[p + "self_attn.o_proj.weight"] = rn(1024, 2048)
+        sd[p + "mlp.gate_proj.weight"] = rn(3072, 1024)
+        sd[p + "mlp.up_proj.weight"] = rn(3072, 1024)
+        sd[p + "mlp.down_proj.weight"] = rn(1024, 3072)
+        sd[p + "input_layernorm.weight"] = one(1024)
+        sd[p + "post_attention_layernorm.weight"] = one(1024)
+        sd[p + "self_attn.q_norm.weight"] = one(128)
+        sd[p + "self_attn.k_norm.weight"] = one(128)
+    return sd
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                            "samples": len(sm)}
+
+
+def cpu_reference(steps: int, warmup: int):
+    """The reference's eager PyTorch path on host cores: batch-1 decode at cache length 4096 (see oracle/qwen3_hf.py)."""
+    from oracle import qwen3_hf as hf
+    r = hf.time_decode_cpu(hf.FULL, kv_len=PROMPT, n_steps=max(steps, 1))
+    sample = (f"{r['steps']} eager decode steps at cache length {PROMPT} (cache filled with N(0,1) values instead of a "
+              f"CPU prefill), after 2 warm-up steps, {r['threads']} threads")
+    return r, sample
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    n = max(8, min(32, args.steps * 8))
+    r, sample = cpu_reference(n, args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": r["tok_s"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_tok"] * DECODE, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"qwen3-0.6b random-init bf16, batch 1, cache length {PROMPT}, greedy decode on host cores"},
+            "cpu_baseline": {"value": r["tok_s"], "unit": UNIT, "cores": r["threads"], "kind": "reference", "sample": sample},
+            "e2e": {"value": r["tok_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
+    ap.add_argument("--no-prefetch", action="store_true", help="disable the L2 weight prefetch (A/B runs)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun), got WORLD_SIZE={world}")
+
+    import torch.distributed as dist
+    from ittai_b200.qwen3 import Qwen3Decoder, decode_bytes_per_token
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+
+    sd = synthetic_state_dict(seed=rank, device=dev)
+    dec = Qwen3Decoder(sd, max_batch=1, kv_capacity=CAP, device=dev, l2_prefetch=not args.no_prefetch)
+    del sd
+    g = torch.Generator().manual_seed(1 + rank)
+    prompt = torch.randint(0, dec.V, (1, PROMPT), generator=g, dtype=torch.int32)
+    first = dec.prefill(prompt).clone()          # outside the timed region: cache resident in HBM
+
+    def rewind():
+        dec.pos.fill_(PROMPT)
+        dec.lengths = [PROMPT]
+        dec.next_id.copy_(first)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    launches = 0
+    for _ in range(warmup):
+        rewind()
+        dec.decode(DECODE)
+    # ---- device-resident timing ------------------------------------------------------------------------
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    with ClockSampler(local) as clk:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for k in range(args.steps):
+            rewind()
+            ev[k][0].record()
+            dec.decode(DECODE, check=False)
+            ev[k][1].record()
+            launches += 1
+        t1.record()
+        barrier()
+    dec.check_status()
+    total_ms = t0.elapsed_time(t1)
+    kern_ms = [a.elapsed_time(b) for a, b in ev]
+    # per-token times of one more run (device globaltimer stamps)
+    rewind()
+    _, ns = dec.decode(DECODE, timed=True)
+    per_tok_us = (ns[1:] - ns[:-1]).float().cpu() / 1e3
+    # ---- end to end from host buffers ------------------------------------------------------------------
+    host_in = first.cpu().pin_memory()
+    host_out = torch.empty(1, DECODE, dtype=torch.int32).pin_memory()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        dec.pos.fill_(PROMPT)
+        dec.lengths = [PROMPT]
+        dec.next_id.copy_(host_in, non_blocking=True)
+        out = dec.decode(DECODE, check=False)
+        host_out.copy_(out, non_blocking=True)
+        launches += 1
+    e1.record()
+    barrier()
+    dec.check_status()
+    e2e_ms = e0.elapsed_time(e1)
+
+    t = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    toks = world * args.steps * DECODE
+    value = toks / (total_ms / 1e3)
+    peaks, peak_kind = measured_peaks()
+    mean_bytes = sum(decode_bytes_per_token(PROMPT + i) for i in range(DECODE)) / DECODE
+    kern_ms_avg = sum(kern_ms) / len(kern_ms)
+    achieved = mean_bytes * DECODE / (kern_ms_avg / 1e3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"qwen3-0.6b random-init bf16, batch 1, {PROMPT}-token prompt, kv capacity {CAP}, "
+                               f"{DECODE} greedy decode steps per step", "l2": "inputs larger than L2 (1.66 GB streamed per token)",
+                   "replicas": world, "l2_prefetch": not args.no_prefetch},
+        "us_per_token": {"median": float(per_tok_us.median()), "p99": float(per_tok_us.quantile(0.99)),
+                         "mean_kernel": kern_ms_avg * 1e3 / DECODE},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind,
+                     "frac_of_nominal_8TBs": achieved / 8000.0, "bytes_per_token": mean_bytes},
+        "e2e": {"value": toks / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * DECODE},
+        "gpu_launches": launches,
+        "clocks": clk.summary,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        r, sample = cpu_reference(8, 2)
+        line["cpu_baseline"] = {"value": r["tok_s"], "unit": UNIT, "cores": r["threads"], "kind": "reference", "sample": sample}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -43,6 +43,8 @@ extern "C" {
 
 /* IttaiQwen3Decode.flags */
 #define ITTAI_F_L2_PREFETCH 1 /* while a phase runs, ask L2 to fetch the weights of the phase that follows */
+#define ITTAI_F_TEST_DROP_ARRIVAL 2 /* test hook: CTA 0 leaves before its first barrier arrival, so the
+                                       other CTAs' bounded wait runs out and reports ITTAI_ST_BARRIER_TIMEOUT */
 
 enum {
     ITTAI_OK = 0,
@@ -89,7 +91,7 @@ typedef struct IttaiQwen3Decode {
     float eps;          /* RMSNorm epsilon                                                     */
     int32_t write_logits; /* non-zero: store bf16 logits of the last step that ran the head    */
     int32_t flags;      /* ITTAI_F_* bits                                                      */
-    int32_t reserved0;
+    int32_t spin_limit; /* polls before a device wait gives up; 0 = library default (about a second) */
 
     const void* wqkv;   /* [L, 4096, 1024] rows: q(2048) | k(1024) | v(1024)                   */
     const void* wo;     /* [L, 1024, 2048]                                                     */

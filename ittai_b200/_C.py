@@ -15,6 +15,7 @@ ABI_VERSION = 1
 MAX_BATCH = 8
 STATUS_WORDS = 8
 F_L2_PREFETCH = 1
+F_TEST_DROP_ARRIVAL = 2
 PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 
 # every symbol include/ittai_b200.h declares
@@ -33,7 +34,7 @@ class Qwen3Decode(C.Structure):
     _fields_ = [
         ("n_layers", C.c_int32), ("vocab", C.c_int32), ("kv_cap", C.c_int32), ("batch", C.c_int32),
         ("n_steps", C.c_int32), ("n_forced", C.c_int32), ("eps", C.c_float), ("write_logits", C.c_int32),
-        ("flags", C.c_int32), ("reserved0", C.c_int32),
+        ("flags", C.c_int32), ("spin_limit", C.c_int32),
         ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("wgu", C.c_void_p), ("wd", C.c_void_p),
         ("ln1", C.c_void_p), ("ln2", C.c_void_p), ("qn", C.c_void_p), ("kn", C.c_void_p),
         ("fin_w", C.c_void_p), ("embed", C.c_void_p), ("rope", C.c_void_p),
@@ -74,7 +75,7 @@ def check(rc: int) -> None:
 
 def decode_status(words) -> None:
     """Raise if a host copy of the device status words reports a failed wait."""
-    arr = (C.c_uint32 * STATUS_WORDS)(*[int(w) for w in words])
+    arr = (C.c_uint32 * STATUS_WORDS)(*[int(w) & 0xFFFFFFFF for w in words])
     msg = C.create_string_buffer(256)
     if lib().ittai_decode_status(arr, msg, 256) != 0:
         raise IttaiError(msg.value.decode())

@@ -116,6 +116,7 @@ struct GridSync {
     uint32_t* status;
     uint32_t epoch;
     uint32_t ncta;
+    uint32_t limit;     // polls before giving up
 };
 
 __device__ __forceinline__ void report_status(uint32_t* status, uint32_t* sync, uint32_t code, uint32_t a, uint32_t b,
@@ -140,7 +141,7 @@ __device__ __forceinline__ bool grid_barrier(GridSync& g, int tag, int* ok_smem)
             ++spins;
             if ((spins & 1023u) == 0u) {
                 if (ld_relaxed(&g.sync[1]) != 0u) { ok = 0; break; }
-                if (spins >= kSpinLimit) {
+                if (spins >= g.limit) {
                     report_status(g.status, g.sync, ITTAI_ST_BARRIER_TIMEOUT, (uint32_t)tag, blockIdx.x, seen, target);
                     ok = 0;
                     break;

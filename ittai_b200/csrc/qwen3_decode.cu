@@ -523,6 +523,7 @@ __device__ void phase_head(Cta& c, int step) {
         }
     }
     // CTA-level argmax, then the last CTA to arrive folds the per-CTA candidates
+#pragma unroll
     for (int b = 0; b < NB; ++b) {
         if (c.lane == 0) { c.hdr->bestv[c.warp] = bv[b]; c.hdr->besti[c.warp] = bi[b]; }
         __syncthreads();
@@ -641,7 +642,8 @@ template <int NB>
 __global__ void __launch_bounds__(kThreads, 1) q3_decode_kernel(const __grid_constant__ IttaiQwen3Decode p) {
     extern __shared__ __align__(256) unsigned char smem[];
     Cta c = make_cta(p, smem);
-    GridSync gs{c.ws.sync, p.status, 0u, (uint32_t)gridDim.x};
+    GridSync gs{c.ws.sync, p.status, 0u, (uint32_t)gridDim.x, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit};
+    if ((p.flags & ITTAI_F_TEST_DROP_ARRIVAL) != 0 && c.cta == 0) return;
     __shared__ int pos0[ITTAI_MAX_BATCH];
     if (c.tid < p.batch) pos0[c.tid] = p.pos[c.tid];
     __syncthreads();

@@ -96,6 +96,7 @@ class Qwen3Decoder:
         self.workspace = z(nbytes.value + 256, dt=torch.uint8)
         self._ws_ptr = (self.workspace.data_ptr() + 255) // 256 * 256
         self.flags = _C.F_L2_PREFETCH if l2_prefetch else 0
+        self.spin_limit = 0                  # 0 = library default
         self.lengths = [0] * self.B          # host mirror of `pos`, for capacity checks without a device read
         self._keep = None
 
@@ -104,6 +105,7 @@ class Qwen3Decoder:
         p = _C.Qwen3Decode()
         p.n_layers, p.vocab, p.kv_cap, p.batch = self.L, self.V, self.cap, self.B
         p.n_steps, p.n_forced, p.eps, p.write_logits, p.flags = n_steps, n_forced, EPS, int(write_logits), self.flags
+        p.spin_limit = self.spin_limit
         for k, t in self.w.items():
             setattr(p, k, t.data_ptr())
         p.rope, p.kcache, p.vcache = self.rope.data_ptr(), self.kcache.data_ptr(), self.vcache.data_ptr()

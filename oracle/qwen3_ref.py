@@ -83,8 +83,12 @@ class Qwen3Ref:
         self.v = torch.zeros_like(self.k)
         self.len = 0
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        """Append ``ids`` (any count >= 1) at positions len.., return bf16-valued logits of the last one."""
+    def forward(self, ids: torch.Tensor, trace: list | None = None) -> torch.Tensor:
+        """Append ``ids`` (any count >= 1) at positions len.., return bf16-valued logits of the last one.
+
+        With ``trace`` a dict of the last token's intermediates is appended per layer (what each decode phase
+        leaves in its output buffer): qkv (raw projections), attn, h_mid (after o_proj), act, h (after down).
+        """
         d = self.d
         T, p0 = len(ids), self.len
         pos = torch.arange(p0, p0 + T)
@@ -98,6 +102,7 @@ class Qwen3Ref:
             q = linear(x, w["wq"]).view(T, d.n_heads, d.head_dim)
             k = linear(x, w["wk"]).view(T, d.n_kv_heads, d.head_dim)
             v = linear(x, w["wv"]).view(T, d.n_kv_heads, d.head_dim)
+            t = dict(qkv=torch.cat([q[-1].flatten(), k[-1].flatten(), v[-1].flatten()])) if trace is not None else None
             q = rope(rmsnorm(q, w["qn"], d.eps), cos, sin)
             k = rope(rmsnorm(k, w["kn"], d.eps), cos, sin)
             self.k[l, :, p0:p0 + T] = k.transpose(0, 1)
@@ -108,10 +113,14 @@ class Qwen3Ref:
             s = s.masked_fill(~causal[None], float("-inf"))
             a = r(torch.einsum("hts,hsd->thd", torch.softmax(s, -1), V)).reshape(T, -1)
             h = r(h + linear(a, w["wo"]))
+            h_mid = h
             x = rmsnorm(h, w["ln2"], d.eps)
             gate, up = linear(x, w["wg"]), linear(x, w["wu"])
             act = r(r(gate * torch.sigmoid(gate)) * up)
             h = r(h + linear(act, w["wd"]))
+            if trace is not None:
+                t.update(attn=a[-1], h_mid=h_mid[-1], act=act[-1], h=h[-1])
+                trace.append(t)
         self.len = p0 + T
         self.h_last = h[-1]
         return linear(rmsnorm(h[-1:], self.fin_w, d.eps), self.embed)[0]
