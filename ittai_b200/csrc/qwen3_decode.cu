@@ -629,19 +629,19 @@ __device__ void prefetch_next(const Cta& c, int phase, int l, bool head_follows)
     }
 }
 
-__device__ __forceinline__ Cta make_cta(const IttaiQwen3Decode& p, unsigned char* smem) {
-    Q3Workspace ws;
-    q3_ws_layout(p.batch, reinterpret_cast<char*>(p.workspace), &ws);
-    Cta c{p, ws, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<float*>(smem + kHdrBytes),
-          reinterpret_cast<SmemAttn*>(smem + kHdrBytes), (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x,
-          (int)(threadIdx.x & 31), (int)(threadIdx.x >> 5)};
-    return c;
-}
+// The per-CTA context is brace-initialised inside each kernel.  nvcc 12.9 mis-infers the shared state space for the
+// global pointers of a struct returned by value from a helper that also receives the shared-memory base, so there is
+// deliberately no make_cta() function.
+#define ITTAI_MAKE_CTA(p, wsp, smem)                                                                              \
+    Cta c{p, wsp, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<float*>(smem + kHdrBytes),                   \
+          reinterpret_cast<SmemAttn*>(smem + kHdrBytes), (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x,       \
+          (int)(threadIdx.x & 31), (int)(threadIdx.x >> 5)}
 
 template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) q3_decode_kernel(const __grid_constant__ IttaiQwen3Decode p) {
+__global__ void __launch_bounds__(kThreads, 1) q3_decode_kernel(const __grid_constant__ IttaiQwen3Decode p,
+                                                                const __grid_constant__ Q3Workspace wsp) {
     extern __shared__ __align__(256) unsigned char smem[];
-    Cta c = make_cta(p, smem);
+    ITTAI_MAKE_CTA(p, wsp, smem);
     GridSync gs{c.ws.sync, p.status, 0u, (uint32_t)gridDim.x, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit};
     if ((p.flags & ITTAI_F_TEST_DROP_ARRIVAL) != 0 && c.cta == 0) return;
     __shared__ int pos0[ITTAI_MAX_BATCH];
@@ -673,9 +673,10 @@ __global__ void __launch_bounds__(kThreads, 1) q3_decode_kernel(const __grid_con
 
 // One phase on its own (no grid barrier): unit tests and per-phase profiles.
 template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) q3_phase_kernel(const __grid_constant__ IttaiQwen3Decode p, int phase, int l) {
+__global__ void __launch_bounds__(kThreads, 1) q3_phase_kernel(const __grid_constant__ IttaiQwen3Decode p,
+                                                               const __grid_constant__ Q3Workspace wsp, int phase, int l) {
     extern __shared__ __align__(256) unsigned char smem[];
-    Cta c = make_cta(p, smem);
+    ITTAI_MAKE_CTA(p, wsp, smem);
     __shared__ int pos0[ITTAI_MAX_BATCH];
     if (c.tid < p.batch) pos0[c.tid] = p.pos[c.tid];
     __syncthreads();
@@ -728,7 +729,7 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
     int n_sms = 0;
     int rc = device_info(&n_sms);
     if (rc != ITTAI_OK) return rc;
-    const size_t smem = q3_smem_bytes(NB);
+    const size_t smem = q3_smem_bytes(NB) + 256;   // slack: the dynamic region starts on a 256-byte boundary after the static words
     const void* fn_decode = (const void*)q3_decode_kernel<NB>;
     const void* fn_phase = (const void*)q3_phase_kernel<NB>;
     constexpr int slot = NB == 1 ? 0 : NB == 2 ? 1 : NB == 4 ? 2 : 3;
@@ -751,11 +752,11 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
     const int grid = n_sms < Q3_MAX_CTAS ? n_sms : Q3_MAX_CTAS;
     if (phase < 0) {
-        void* args[] = {(void*)p};
+        void* args[] = {(void*)p, (void*)&ws};
         e = cudaLaunchCooperativeKernel(fn_decode, dim3(grid), dim3(kThreads), args, smem, st);
         if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchCooperativeKernel(q3_decode_kernel)");
     } else {
-        q3_phase_kernel<NB><<<grid, kThreads, smem, st>>>(*p, phase, layer);
+        q3_phase_kernel<NB><<<grid, kThreads, smem, st>>>(*p, ws, phase, layer);
         e = cudaGetLastError();
         if (e != cudaSuccess) return cuda_fail(e, "launch q3_phase_kernel");
     }

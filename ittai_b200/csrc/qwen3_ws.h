@@ -1,5 +1,5 @@
-// Layout of the Qwen3 decode workspace: one carve-up shared by the host (size query, memset of the
-// synchronisation words) and the device (pointer set-up at kernel entry).
+// Layout of the Qwen3 decode workspace: carved up on the host (size query, memset of the
+// synchronisation words); the resulting pointer set travels to the kernels as a launch parameter.
 #pragma once
 #include <cuda_bf16.h>
 #include <stddef.h>
@@ -27,17 +27,30 @@ struct Q3Workspace {
     int* cand_idx;         // [Q3_MAX_CTAS, ITTAI_MAX_BATCH]
 };
 
-__host__ __device__ inline size_t q3_ws_layout(int batch, char* base, Q3Workspace* ws) {
+// Host only: the kernels receive the finished pointer set as a launch parameter.
+inline size_t q3_ws_layout(int batch, char* base, Q3Workspace* ws) {
     size_t off = 0;
-    auto take = [&](size_t bytes) { char* p = base + off; off += (bytes + 255) / 256 * 256; return p; };
-    ws->sync = reinterpret_cast<uint32_t*>(take(Q3_SYNC_WORDS * sizeof(uint32_t)));
-    ws->h = reinterpret_cast<__nv_bfloat16*>(take((size_t)batch * ITTAI_Q3_D * 2));
-    ws->qkv = reinterpret_cast<__nv_bfloat16*>(take((size_t)batch * ITTAI_Q3_DQKV * 2));
-    ws->attn = reinterpret_cast<__nv_bfloat16*>(take((size_t)batch * ITTAI_Q3_DQ * 2));
-    ws->act = reinterpret_cast<__nv_bfloat16*>(take((size_t)batch * ITTAI_Q3_FF * 2));
-    ws->part = reinterpret_cast<float*>(take((size_t)Q3_MAX_CTAS * Q3_PART_FLOATS * sizeof(float)));
-    ws->cand_val = reinterpret_cast<float*>(take((size_t)Q3_MAX_CTAS * ITTAI_MAX_BATCH * sizeof(float)));
-    ws->cand_idx = reinterpret_cast<int*>(take((size_t)Q3_MAX_CTAS * ITTAI_MAX_BATCH * sizeof(int)));
+    const size_t sizes[8] = {Q3_SYNC_WORDS * sizeof(uint32_t),
+                             (size_t)batch * ITTAI_Q3_D * 2,
+                             (size_t)batch * ITTAI_Q3_DQKV * 2,
+                             (size_t)batch * ITTAI_Q3_DQ * 2,
+                             (size_t)batch * ITTAI_Q3_FF * 2,
+                             (size_t)Q3_MAX_CTAS * Q3_PART_FLOATS * sizeof(float),
+                             (size_t)Q3_MAX_CTAS * ITTAI_MAX_BATCH * sizeof(float),
+                             (size_t)Q3_MAX_CTAS * ITTAI_MAX_BATCH * sizeof(int)};
+    char* ptr[8];
+    for (int i = 0; i < 8; ++i) {
+        ptr[i] = base + off;
+        off += (sizes[i] + 255) / 256 * 256;
+    }
+    ws->sync = reinterpret_cast<uint32_t*>(ptr[0]);
+    ws->h = reinterpret_cast<__nv_bfloat16*>(ptr[1]);
+    ws->qkv = reinterpret_cast<__nv_bfloat16*>(ptr[2]);
+    ws->attn = reinterpret_cast<__nv_bfloat16*>(ptr[3]);
+    ws->act = reinterpret_cast<__nv_bfloat16*>(ptr[4]);
+    ws->part = reinterpret_cast<float*>(ptr[5]);
+    ws->cand_val = reinterpret_cast<float*>(ptr[6]);
+    ws->cand_idx = reinterpret_cast<int*>(ptr[7]);
     return off;
 }
 
