@@ -43,8 +43,8 @@ extern "C" {
 
 /* IttaiQwen3Decode.flags */
 #define ITTAI_F_L2_PREFETCH 1 /* while a phase runs, ask L2 to fetch the weights of the phase that follows */
-#define ITTAI_F_TEST_DROP_ARRIVAL 2 /* test hook: CTA 0 leaves before its first barrier arrival, so the
-                                       other CTAs' bounded wait runs out and reports ITTAI_ST_BARRIER_TIMEOUT */
+#define ITTAI_F_TEST_DROP_CTA 2 /* test hook: CTA 0 leaves at once, so the words it would publish never arrive and
+                                  the other CTAs' bounded waits run out and report ITTAI_ST_FLAG_TIMEOUT */
 
 enum {
     ITTAI_OK = 0,
@@ -58,8 +58,9 @@ enum {
 #define ITTAI_STATUS_WORDS 8
 enum {
     ITTAI_ST_OK = 0,
-    ITTAI_ST_BARRIER_TIMEOUT = 1, /* status[1]=phase tag, status[2]=CTA, status[3]=counter seen, status[4]=target */
-    ITTAI_ST_FLAG_TIMEOUT = 2,
+    ITTAI_ST_BARRIER_TIMEOUT = 1, /* reserved */
+    ITTAI_ST_FLAG_TIMEOUT = 2,    /* status[1]=what was awaited (phase id, +16 merge, +32 residual, 64 step order),
+                                     status[2]=CTA, status[3]=tag seen, status[4]=tag expected */
     ITTAI_ST_BAD_TOKEN = 3        /* status[1]=token id, status[2]=step */
 };
 
@@ -116,6 +117,8 @@ typedef struct IttaiQwen3Decode {
     void* workspace;    /* ittai_qwen3_decode_workspace_bytes() bytes, 256-byte aligned        */
     uint32_t* status;   /* [ITTAI_STATUS_WORDS] device words, zeroed by the launch             */
     uint64_t* step_ns;  /* [n_steps] device: globaltimer at the end of each step, or NULL      */
+    uint64_t* phase_clk; /* [n_steps, 5*L+1, 2] device, or NULL: CTA 0's SM cycle counter when each phase had
+                            its inputs and when it finished (in-kernel profile)                  */
 } IttaiQwen3Decode;
 
 /* ---- library ------------------------------------------------------------------------------------ */

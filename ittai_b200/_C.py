@@ -15,7 +15,7 @@ ABI_VERSION = 1
 MAX_BATCH = 8
 STATUS_WORDS = 8
 F_L2_PREFETCH = 1
-F_TEST_DROP_ARRIVAL = 2
+F_TEST_DROP_CTA = 2
 PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 
 # every symbol include/ittai_b200.h declares
@@ -40,7 +40,7 @@ class Qwen3Decode(C.Structure):
         ("fin_w", C.c_void_p), ("embed", C.c_void_p), ("rope", C.c_void_p),
         ("kcache", C.c_void_p), ("vcache", C.c_void_p), ("pos", C.c_void_p), ("next_id", C.c_void_p),
         ("forced", C.c_void_p), ("out_ids", C.c_void_p), ("logits", C.c_void_p),
-        ("workspace", C.c_void_p), ("status", C.c_void_p), ("step_ns", C.c_void_p),
+        ("workspace", C.c_void_p), ("status", C.c_void_p), ("step_ns", C.c_void_p), ("phase_clk", C.c_void_p),
     ]
 
 

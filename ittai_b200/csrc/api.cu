@@ -61,4 +61,4 @@ extern "C" int ittai_decode_status(const uint32_t* st, char* msg, size_t n) {
     return ITTAI_OK;
 }
 
-static_assert(sizeof(IttaiQwen3Decode) == 40 + 21 * sizeof(void*), "IttaiQwen3Decode layout differs from the ctypes mirror");
+static_assert(sizeof(IttaiQwen3Decode) == 40 + 22 * sizeof(void*), "IttaiQwen3Decode layout differs from the ctypes mirror");

@@ -106,16 +106,25 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
-// ---- grid-wide synchronisation with a bounded wait -------------------------------------------------
-// sync[0] arrival counter (monotonic within a launch), sync[1] abort flag.  Needs all CTAs co-resident
-// (cooperative launch).  Returns false when the wait ran out or another CTA aborted; the caller must then
-// leave the kernel.  The same role as the reference's arrive/ready flags (src/ittai/qwen3/base.py:42-78),
-// which spin without a limit.
-struct GridSync {
-    uint32_t* sync;
+// ---- flagged words: payload + tag in one 64-bit word -------------------------------------------------------
+// The role of the reference's arrive/ready flags (src/ittai/qwen3/base.py:42-78), which spin without a limit; here
+// the flag travels with the data and every wait is bounded.
+__device__ __forceinline__ uint64_t ld_flagged(const uint64_t* p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_flagged(uint64_t* p, uint32_t payload, uint32_t tag) {
+    const uint64_t v = ((uint64_t)tag << 32) | payload;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+}
+
+struct Waiter {
+    uint32_t* sync;     // sync[1] = abort flag
     uint32_t* status;
-    uint32_t epoch;
-    uint32_t ncta;
     uint32_t limit;     // polls before giving up
 };
 
@@ -128,31 +137,20 @@ __device__ __forceinline__ void report_status(uint32_t* status, uint32_t* sync, 
     atomicExch(&sync[1], 1u);
 }
 
-__device__ __forceinline__ bool grid_barrier(GridSync& g, int tag, int* ok_smem) {
-    __syncthreads();
-    g.epoch += 1;
-    if (threadIdx.x == 0) {
-        const uint32_t target = g.epoch * g.ncta;
-        __threadfence();
-        red_release_add(&g.sync[0], 1u);
-        int ok = 1;
-        uint32_t spins = 0, seen = 0;
-        while ((seen = ld_acquire(&g.sync[0])) < target) {
-            ++spins;
-            if ((spins & 1023u) == 0u) {
-                if (ld_relaxed(&g.sync[1]) != 0u) { ok = 0; break; }
-                if (spins >= g.limit) {
-                    report_status(g.status, g.sync, ITTAI_ST_BARRIER_TIMEOUT, (uint32_t)tag, blockIdx.x, seen, target);
-                    ok = 0;
-                    break;
-                }
+// Polls one word until its tag matches; returns false when the wait ran out or another CTA aborted.
+__device__ __forceinline__ bool wait_word(const Waiter& w, const uint64_t* p, uint32_t tag, uint32_t& payload, int what) {
+    uint32_t spins = 0;
+    for (;;) {
+        const uint64_t v = ld_flagged(p);
+        if ((uint32_t)(v >> 32) == tag) { payload = (uint32_t)v; return true; }
+        if (((++spins) & 1023u) == 0u) {
+            if (ld_relaxed(&w.sync[1]) != 0u) return false;
+            if (spins >= w.limit) {
+                report_status(w.status, w.sync, ITTAI_ST_FLAG_TIMEOUT, (uint32_t)what, blockIdx.x, (uint32_t)(v >> 32), tag);
+                return false;
             }
         }
-        __threadfence();
-        *ok_smem = ok;
     }
-    __syncthreads();
-    return *ok_smem != 0;
 }
 
 }  // namespace ittai

@@ -99,6 +99,7 @@ class Qwen3Decoder:
         self.spin_limit = 0                  # 0 = library default
         self.lengths = [0] * self.B          # host mirror of `pos`, for capacity checks without a device read
         self._keep = None
+        self._phase_clk = None
 
     # ---- plumbing -------------------------------------------------------------------------------
     def _params(self, n_steps, n_forced, forced, out_ids, step_ns, write_logits=True) -> _C.Qwen3Decode:
@@ -114,6 +115,7 @@ class Qwen3Decoder:
         p.out_ids, p.logits = out_ids.data_ptr(), self.logits.data_ptr()
         p.workspace, p.status = self._ws_ptr, self.status.data_ptr()
         p.step_ns = step_ns.data_ptr() if step_ns is not None else None
+        p.phase_clk = self._phase_clk.data_ptr() if self._phase_clk is not None else None
         return p
 
     def _stream(self):
@@ -166,6 +168,18 @@ class Qwen3Decoder:
         return (out.t(), ns) if timed else out.t()
 
     @torch.no_grad()
+    def decode_profiled(self, n_steps: int) -> torch.Tensor:
+        """Decode ``n_steps`` tokens recording CTA 0's SM cycle counter for every phase.
+
+        Returns int64 ``[n_steps, 5*L+1, 2]``: cycles at (inputs of the phase complete, phase finished)."""
+        self._phase_clk = torch.zeros(n_steps, 5 * self.L + 1, 2, dtype=torch.int64, device=self.dev)
+        try:
+            self._launch(n_steps)
+        finally:
+            clk, self._phase_clk = self._phase_clk, None
+        return clk
+
+    @torch.no_grad()
     def decode_forced(self, ids) -> torch.Tensor:
         """Teacher forcing: feed ``ids`` ([B, T]) one per step but run the head on every step.
 
@@ -189,16 +203,32 @@ class Qwen3Decoder:
         _C.check(self.lib.ittai_qwen3_phase_launch(C.byref(p), phase, layer, self._stream()))
         self.check_status()
 
-    def workspace_views(self) -> dict:
-        """Typed views of the activation scratch (h, qkv, attn, act) for phase-level tests."""
+    # The vectors one phase hands to the next live in the workspace as flagged 64-bit words: two bf16 values in the low
+    # half, the tag of the producing (step, layer) in the high half.  These helpers let tests and profiles read a
+    # phase's output and plant a phase's input; a phase launch runs at step 0, where layer l's tag is l + 1.
+    _FLAGGED = (("h", D), ("qkv", DQKV), ("attn", DQ), ("hmid", D), ("act", FF))
+
+    def _flagged_words(self, name: str) -> torch.Tensor:
         off = self._ws_ptr - self.workspace.data_ptr()
         up = lambda n: (n + 255) // 256 * 256
-        views, o = {}, off + up(128 * 4)
-        for name, n in (("h", D), ("qkv", DQKV), ("attn", DQ), ("act", FF)):
-            nb = self.B * n * 2
-            views[name] = self.workspace[o:o + nb].view(torch.bfloat16).view(self.B, n)
+        o = off + up(64 * 4)
+        for nm, n in self._FLAGGED:
+            nb = self.B * (n // 2) * 8
+            if nm == name:
+                return self.workspace[o:o + nb].view(torch.int64).view(self.B, n // 2)
             o += up(nb)
-        return views
+        raise KeyError(name)
+
+    def read_buf(self, name: str) -> torch.Tensor:
+        """bf16 ``[B, n]`` payload of the flagged buffer ``name`` (h, qkv, attn, hmid, act)."""
+        w = self._flagged_words(name)
+        pair = torch.stack([w & 0xFFFF, (w >> 16) & 0xFFFF], -1).to(torch.int32).to(torch.int16)
+        return pair.view(torch.bfloat16).reshape(self.B, -1)
+
+    def write_buf(self, name: str, values: torch.Tensor, layer: int) -> None:
+        """Plant ``values`` ([B, n] or [n]) in flagged buffer ``name`` with the tag of (step 0, ``layer``)."""
+        v = values.to(torch.bfloat16).reshape(self.B, -1, 2).to(self.dev).view(torch.int16).to(torch.int64) & 0xFFFF
+        self._flagged_words(name).copy_(v[..., 0] | (v[..., 1] << 16) | ((layer + 1) << 32))
 
     @torch.no_grad()
     def generate(self, prompt_host: torch.Tensor, n_steps: int) -> torch.Tensor:
