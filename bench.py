@@ -136,7 +136,6 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
-    ap.add_argument("--no-prefetch", action="store_true", help="disable the L2 weight prefetch (A/B runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -157,7 +156,7 @@ def main():
     warmup = max(args.warmup, 3)
 
     sd = synthetic_state_dict(seed=rank, device=dev)
-    dec = Qwen3Decoder(sd, max_batch=1, kv_capacity=CAP, device=dev, l2_prefetch=not args.no_prefetch)
+    dec = Qwen3Decoder(sd, max_batch=1, kv_capacity=CAP, device=dev)
     del sd
     g = torch.Generator().manual_seed(1 + rank)
     prompt = torch.randint(0, dec.V, (1, PROMPT), generator=g, dtype=torch.int32)
@@ -237,7 +236,7 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"qwen3-0.6b random-init bf16, batch 1, {PROMPT}-token prompt, kv capacity {CAP}, "
                                f"{DECODE} greedy decode steps per step", "l2": "inputs larger than L2 (1.66 GB streamed per token)",
-                   "replicas": world, "l2_prefetch": not args.no_prefetch},
+                   "replicas": world},
         "us_per_token": {"median": float(per_tok_us.median()), "p99": float(per_tok_us.quantile(0.99)),
                          "mean_kernel": kern_ms_avg * 1e3 / DECODE},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",

@@ -42,7 +42,6 @@ extern "C" {
 #define ITTAI_MAX_BATCH 8
 
 /* IttaiQwen3Decode.flags */
-#define ITTAI_F_L2_PREFETCH 1 /* while a phase runs, ask L2 to fetch the weights of the phase that follows */
 #define ITTAI_F_TEST_DROP_CTA 2 /* test hook: CTA 0 leaves at once, so the words it would publish never arrive and
                                   the other CTAs' bounded waits run out and report ITTAI_ST_FLAG_TIMEOUT */
 
@@ -61,7 +60,8 @@ enum {
     ITTAI_ST_BARRIER_TIMEOUT = 1, /* reserved */
     ITTAI_ST_FLAG_TIMEOUT = 2,    /* status[1]=what was awaited (phase id, +16 merge, +32 residual, 64 step order),
                                      status[2]=CTA, status[3]=tag seen, status[4]=tag expected */
-    ITTAI_ST_BAD_TOKEN = 3        /* status[1]=token id, status[2]=step */
+    ITTAI_ST_BAD_TOKEN = 3,       /* status[1]=token id, status[2]=step, status[3]=position, status[4]=sequence */
+    ITTAI_ST_STREAM_TIMEOUT = 4   /* a weight-stream copy did not land: status[1]=entry, status[2]=CTA */
 };
 
 /* Phases of one decoded token, in execution order inside a layer (ids used by ittai_qwen3_phase_launch). */

@@ -14,7 +14,6 @@ LIB_PATH = os.path.join(_HERE, "libittai_b200.so")
 ABI_VERSION = 1
 MAX_BATCH = 8
 STATUS_WORDS = 8
-F_L2_PREFETCH = 1
 F_TEST_DROP_CTA = 2
 PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 

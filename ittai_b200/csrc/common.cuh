@@ -10,8 +10,9 @@ namespace ittai {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int kThreads = 512;            // threads per persistent CTA
+constexpr int kThreads = 512;            // compute threads per persistent CTA
 constexpr int kWarps = kThreads / 32;
+constexpr int kBlock = kThreads + 32;    // plus one warp that only feeds the weight stream
 constexpr unsigned kSpinLimit = 1u << 22;  // polls before a device wait gives up (about a second)
 
 // ---- bf16 <-> fp32 -------------------------------------------------------------------------------
@@ -94,15 +95,30 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
-// Sum over the CTA; every thread returns the same value (fixed summation order). `red` holds kWarps floats.
+// Barrier over the kThreads compute threads only (named barrier 1): the stream-feeding warp never joins it.
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
+// The same barrier, returning the OR of `pred` over the compute threads.
+__device__ __forceinline__ bool cta_or(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %1, 0;\n"
+        "bar.red.or.pred p, 1, %2, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(r) : "r"((uint32_t)pred), "n"(kThreads) : "memory");
+    return r != 0;
+}
+// Sum over the compute threads; every thread returns the same value (fixed summation order). `red` holds kWarps floats.
 __device__ __forceinline__ float block_sum(float v, float* red) {
     v = warp_sum(v);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
+    cta_sync();
     float t = 0.f;
 #pragma unroll
     for (int i = 0; i < kWarps; ++i) t += red[i];
-    __syncthreads();
+    cta_sync();
     return t;
 }
 

@@ -1,53 +1,58 @@
 // Qwen3-0.6B decode: one persistent cooperative kernel per launch runs n_steps tokens; the chosen token id is fed
-// back on the device.  The phases of a layer are chained by data flow, not by grid barriers: every vector one phase
-// hands to the next travels as flagged 64-bit words (payload + tag of the producing step and layer), and a consumer
-// polls exactly the words it needs (see qwen3_ws.h).
+// back on the device.
 //
-// Batch-1 decode is HBM-bound (about 1.4 flop per weight byte), so there are no tensor-core tiles here: each warp
-// streams whole 1024-column weight sub-rows with 128-bit coalesced loads and reduces with shuffles.  Rounding points
-// follow the eager modules: every Linear output, norm output, rotary product and sum, SiLU, gate*up product and
-// residual sum is rounded to bf16 exactly once.
+//  * Data flow instead of grid barriers: every vector one phase hands to the next travels as flagged 64-bit words
+//    (payload + tag of the producing step and layer), and a consumer polls exactly the words it needs (qwen3_ws.h).
+//  * Weight stream: each CTA's slices of the layer matrices and of the KV cache are pulled into a shared-memory ring by
+//    TMA bulk copies issued far ahead of use (weight_stream.cuh), so HBM keeps streaming while phases wait on each other.
+//  * Batch-1 decode is HBM-bound (about 1.4 flop per weight byte), so there are no tensor-core tiles here: each warp
+//    multiplies whole 1024-column weight sub-rows with 128-bit accesses and reduces with shuffles.
 //
-// The math per phase mirrors the fused epilogues of the reference's megakernel (src/ittai/qwen3/base.py:80-129 for
-// qkv / residual / gate-up, :147-162 for the embedding row), re-cut for one token: the row-norm scale is applied before
-// the GEMV instead of after the GEMM, and keys and values go straight into the cache instead of a staging matrix.
-// KV cache, split-K decode attention, lm_head and argmax have no counterpart in the reference.
+// Rounding points follow the eager modules: every Linear output, norm output, rotary product and sum, SiLU, gate*up
+// product and residual sum is rounded to bf16 exactly once.  The math per phase mirrors the fused epilogues of the
+// reference's megakernel (src/ittai/qwen3/base.py:80-129 for qkv / residual / gate-up, :147-162 for the embedding row),
+// re-cut for one token: the row-norm scale is applied before the GEMV instead of after the GEMM, and keys and values go
+// straight into the cache instead of a staging matrix.  KV cache, split-K decode attention, lm_head and argmax have no
+// counterpart in the reference.
 #include "common.cuh"
 #include "qwen3_ws.h"
+#include "weight_stream.cuh"
 
 namespace ittai {
 
 constexpr int D = ITTAI_Q3_D, NKV = ITTAI_Q3_NKV, HD = ITTAI_Q3_HD, FF = ITTAI_Q3_FF;
 constexpr int DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV, DGU = ITTAI_Q3_DGU;
-constexpr int kTile = 256;                       // cache positions scored per attention tile
+constexpr int kTile = 128;                       // cache positions per attention tile = one ring entry of K and one of V
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kCombMax = 640;                    // floats the combine step gathers (worst case over split counts)
+constexpr int kCombMax = 640;                    // floats the merge step gathers (worst case over split counts)
+constexpr int kStreamPhases = 5;                 // phases of a layer that read streamed data (the head reads HBM directly)
 
-// ---- shared-memory plan (dynamic) ----------------------------------------------------------------------
+// ---- shared-memory plan (dynamic): header | activations or attention scratch | weight ring -----------------
 struct SmemHdr {
+    StreamShared stream;
     float red[32];
-    float m_s[2], l_s[2], corr_s[2];
+    int pos0[ITTAI_MAX_BATCH];                   // cache lengths at kernel entry
     int pos_s[ITTAI_MAX_BATCH];
     int tok_s[ITTAI_MAX_BATCH];
     float bestv[kWarps];
     int besti[kWarps];
     float sub[64 * ITTAI_MAX_BATCH];             // per-sub-row partial dot products
-    float comb[kCombMax];                        // split-K partials gathered by the combine step
+    float comb[kCombMax];                        // split-K partials gathered by the merge step
     float candv[Q3_MAX_CTAS];                    // argmax candidates of every CTA
     int candi[Q3_MAX_CTAS];
 };
 struct SmemAttn {
-    float sc[2][kTile];                          // scores, then probabilities, of the two query heads of a group
-    float qs[2][HD];                             // rotated, pre-scaled queries
+    float qs[2][HD];                             // rotated, pre-scaled queries of the two heads of a group
+    float wm[kWarps][2], wl[kWarps][2];          // per-warp running max and sum
     bf16 knew[HD];
     bf16 vnew[HD];
     float ored[kWarps][2][HD];
 };
 constexpr size_t kHdrBytes = (sizeof(SmemHdr) + 255) / 256 * 256;
-__host__ __device__ constexpr size_t q3_smem_bytes(int nb) {
+__host__ __device__ constexpr size_t q3_fixed_smem_bytes(int nb) {
     size_t xs = (size_t)nb * FF * sizeof(float);
     size_t at = sizeof(SmemAttn);
-    return kHdrBytes + (xs > at ? xs : at);
+    return kHdrBytes + ((xs > at ? xs : at) + 255) / 256 * 256;
 }
 
 struct Cta {
@@ -58,6 +63,7 @@ struct Cta {
     SmemAttn* at;       // aliases xs
     int cta, ncta, tid, lane, warp;
     Waiter w;
+    Stream st;
     int step;           // token index inside this launch
     long long t_ready;  // cycle counter when the current phase had its inputs (in-kernel profile)
 };
@@ -66,13 +72,129 @@ struct Cta {
 __device__ __forceinline__ uint32_t tag_of(const Cta& c, int step, int l) { return (uint32_t)(step * (c.p.n_layers + 1) + l + 1); }
 
 // CTA-uniform verdict on per-thread waits.
-__device__ __forceinline__ bool all_ok(bool ok) { return __syncthreads_or(ok ? 0 : 1) == 0; }
+__device__ __forceinline__ bool all_ok(bool ok) { return !cta_or(!ok); }
+
+__device__ __forceinline__ void split_range(int n, int parts, int i, int& lo, int& hi) {
+    lo = (int)(((unsigned)n * (unsigned)i) / (unsigned)parts);          // n * parts stays far below 2^32
+    hi = (int)(((unsigned)n * (unsigned)(i + 1)) / (unsigned)parts);
+}
+
+__device__ __forceinline__ int attn_splits(int ncta, int batch) {
+    int s = ncta / (batch * NKV);
+    return s < 1 ? 1 : (s > Q3_MAX_SPLITS ? Q3_MAX_SPLITS : s);
+}
+
+// The attention work of this CTA at one step: item (b, g, s) = CTA index; its cache range [start, start + n_old) of
+// rows written by earlier tokens, and whether the token being computed (row `pos`) falls into its split.
+struct AttnItem {
+    bool active;
+    int b, g, s, pos, start, n_old;
+    bool has_new;
+};
+__device__ __forceinline__ AttnItem attn_item(const Cta& c, int step) {
+    AttnItem it;
+    const int B = c.p.batch, n_splits = attn_splits(c.ncta, B);
+    it.active = c.cta < B * NKV * n_splits;
+    const int item = it.active ? c.cta : 0;
+    it.b = item / (NKV * n_splits); it.g = (item / n_splits) % NKV; it.s = item % n_splits;
+    it.pos = c.hdr->pos0[it.b] + step;
+    const int n_ctx = it.pos + 1;
+    const int chunk = (((n_ctx + n_splits - 1) / n_splits) + 31) & ~31;
+    it.start = it.s * chunk;
+    const int end = it.start + chunk < n_ctx ? it.start + chunk : n_ctx;
+    it.has_new = it.active && it.pos >= it.start && it.pos < it.start + chunk;
+    const int lim = end < it.pos ? end : it.pos;         // the row of the current token never comes from the cache
+    it.n_old = it.active && lim > it.start ? lim - it.start : 0;
+    return it;
+}
+
+// ---- the static sequence of streamed slices ---------------------------------------------------------------
+// Phase index k counts (step, layer, phase) in execution order, 5 * L + 1 phases per step (the last one is the head):
+// k = step * (5 L + 1) + l * 5 + ph.  Attention contributes 2 * ceil(n_old / kTile) entries (K tile, V tile, K tile,
+// ...), the head ceil(rows / kHeadRows) entries on steps that run it, every other phase exactly one.
+constexpr int kHeadRows = 32;                    // table rows per streamed head entry (two per warp)
+
+__device__ __forceinline__ bool head_runs(const Cta& c, int step) { return step >= c.p.n_forced - 1; }
+
+// The issuing lane's whole life: walk phases [k_begin, k_end) in execution order, launch every slice as soon as the
+// ring has room, then wait for the last copies to land.  It stops early when the compute threads raise `stop`.
+// Slice addresses are linear in the layer index, so everything but one small division per step is hoisted.
+__device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
+    const IttaiQwen3Decode& p = c.p;
+    const uint32_t limit = c.w.limit;
+    const int L = p.n_layers, PS = kStreamPhases * L + 1;
+    int lo, hi;
+    // per-phase: base of this CTA's slice in layer 0, bytes between layers, bytes of the slice
+    const char* base[kStreamPhases];
+    size_t stride[kStreamPhases];
+    uint32_t nbytes[kStreamPhases];
+    split_range(DQKV / 2, c.ncta, c.cta, lo, hi);
+    base[ITTAI_PH_QKV] = reinterpret_cast<const char*>(p.wqkv) + (size_t)2 * lo * D * 2;
+    stride[ITTAI_PH_QKV] = (size_t)DQKV * D * 2; nbytes[ITTAI_PH_QKV] = (uint32_t)(hi - lo) * 2 * D * 2;
+    split_range(D / 2, c.ncta, c.cta, lo, hi);
+    base[ITTAI_PH_OPROJ] = reinterpret_cast<const char*>(p.wo) + (size_t)2 * lo * DQ * 2;
+    stride[ITTAI_PH_OPROJ] = (size_t)D * DQ * 2; nbytes[ITTAI_PH_OPROJ] = (uint32_t)(hi - lo) * 2 * DQ * 2;
+    base[ITTAI_PH_DOWN] = reinterpret_cast<const char*>(p.wd) + (size_t)2 * lo * FF * 2;
+    stride[ITTAI_PH_DOWN] = (size_t)D * FF * 2; nbytes[ITTAI_PH_DOWN] = (uint32_t)(hi - lo) * 2 * FF * 2;
+    split_range(FF / 2, c.ncta, c.cta, lo, hi);
+    base[ITTAI_PH_GU] = reinterpret_cast<const char*>(p.wgu) + (size_t)4 * lo * D * 2;
+    stride[ITTAI_PH_GU] = (size_t)DGU * D * 2; nbytes[ITTAI_PH_GU] = (uint32_t)(hi - lo) * 4 * D * 2;
+    base[ITTAI_PH_ATTN] = nullptr; stride[ITTAI_PH_ATTN] = (size_t)p.batch * NKV * p.kv_cap * HD * 2; nbytes[ITTAI_PH_ATTN] = 0;
+    int h_lo, h_hi;
+    split_range(p.vocab, c.ncta, c.cta, h_lo, h_hi);
+
+    const int step_begin = k_begin / PS, step_end = (k_end + PS - 1) / PS;
+    for (int step = step_begin; step < step_end; ++step) {
+        const AttnItem it = attn_item(c, step);
+        const size_t head0 = (((size_t)it.b * NKV + it.g) * (size_t)p.kv_cap + it.start) * HD * 2;   // bytes, layer 0
+        const int n_kv = 2 * ((it.n_old + kTile - 1) / kTile);
+        const int n_head = head_runs(c, step) ? (h_hi - h_lo + kHeadRows - 1) / kHeadRows : 0;
+        int k = step * PS;
+        for (int r = 0; r < PS; ++r, ++k) {
+            if (k < k_begin || k >= k_end) continue;
+            const int l = r / kStreamPhases, ph = r == PS - 1 ? ITTAI_PH_HEAD : r % kStreamPhases;
+            const int n = ph == ITTAI_PH_HEAD ? n_head : (ph == ITTAI_PH_ATTN ? n_kv : 1);
+            for (int tile = 0; tile < n; ++tile) {
+                const char* src;
+                uint32_t bytes, off;
+                if (ph == ITTAI_PH_HEAD) {
+                    const int row = h_lo + tile * kHeadRows, rows = h_hi - row < kHeadRows ? h_hi - row : kHeadRows;
+                    src = reinterpret_cast<const char*>(p.embed) + (size_t)row * D * 2;
+                    bytes = (uint32_t)rows * D * 2;
+                } else if (ph == ITTAI_PH_ATTN) {
+                    const int j = tile >> 1, rows = it.n_old - j * kTile < kTile ? it.n_old - j * kTile : kTile;
+                    src = reinterpret_cast<const char*>((tile & 1) ? p.vcache : p.kcache) + (size_t)l * stride[ITTAI_PH_ATTN] +
+                          head0 + (size_t)j * kTile * HD * 2;
+                    bytes = (uint32_t)rows * HD * 2;
+                } else {
+                    src = base[ph] + (size_t)l * stride[ph];
+                    bytes = nbytes[ph];
+                }
+                if (bytes == 0) continue;
+                uint32_t spins = 0;
+                while (!stream_alloc(c.st, bytes, off)) {
+                    if (c.st.sh->stop != 0u || ++spins > (limit << 4)) { stream_drain(c.st, limit); return; }
+                }
+                stream_issue(c.st, off, src, bytes);
+            }
+        }
+    }
+    stream_drain(c.st, limit);
+}
+
+// Entry number n of the stream, with a CTA-uniform verdict.
+__device__ __forceinline__ const bf16* stream_acquire(Cta& c, uint32_t n, bool& ok) {
+    const unsigned char* ptr = stream_wait(c.st, n, c.w);
+    ok = all_ok(ptr != nullptr);
+    return reinterpret_cast<const bf16*>(ptr);
+}
 
 // ---- RMSNorm of one row (already in registers, one bf16 pair per thread) into shared memory --------------
 // xs[i] = bf16(bf16(x*rstd) * gain): the value the following Linear sees in the eager model.
-__device__ __forceinline__ void norm_pair_to_smem(Cta& c, uint32_t u, const bf16* gain, float* xs_row) {
+// `gw` is this thread's pair of gains, loaded by the caller BEFORE it waits for the input: a global load issued after
+// the wait would put a full memory round trip on the critical path of every layer.
+__device__ __forceinline__ void norm_pair_to_smem(Cta& c, uint32_t u, uint32_t gw, float* xs_row) {
     static_assert(kThreads * 2 == D, "one bf16 pair per thread");
-    const uint32_t gw = *reinterpret_cast<const uint32_t*>(gain + 2 * c.tid);
     const float x0 = bf_lo(u), x1 = bf_hi(u);
     const float tot = block_sum(x0 * x0 + x1 * x1, c.hdr->red);
     const float rstd = 1.0f / sqrtf(tot * (1.0f / D) + c.p.eps);
@@ -98,8 +220,15 @@ __device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, u
 }
 
 // ---- 1024-column sub-row dot products ------------------------------------------------------------------
-// Lane owns the 16-byte chunks lane, lane+32, lane+64, lane+96 of a sub-row: four independent 128-bit loads per
-// sub-row, R sub-rows in flight.  Batch 1 keeps its 32 activations in registers; larger batches read shared memory.
+// Lane owns the 16-byte chunks lane, lane+32, lane+64, lane+96 of a sub-row: four independent 128-bit accesses per
+// sub-row, R sub-rows at a time.  Batch 1 keeps its 32 activations in registers; larger batches read shared memory.
+// GLOBAL selects streaming global loads (the head's table) over the shared-memory ring.
+template <bool GLOBAL>
+__device__ __forceinline__ uint4 load_w(const bf16* p) {
+    if constexpr (GLOBAL) return ldg_stream(p);
+    else return *reinterpret_cast<const uint4*>(p);
+}
+
 __device__ __forceinline__ void load_xreg(const float* xs, int lane, float (&xr)[32]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -110,32 +239,32 @@ __device__ __forceinline__ void load_xreg(const float* xs, int lane, float (&xr)
     }
 }
 
-template <int R>
+template <bool GLOBAL, int R>
 __device__ __forceinline__ void dot_subrows_xreg(const bf16* const (&wp)[R], const float (&xr)[32], int lane,
                                                  float (&acc)[R]) {
     uint4 w[R][4];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) w[r][i] = ldg_stream(wp[r] + (lane + 32 * i) * 8);
+        for (int i = 0; i < 4; ++i) w[r][i] = load_w<GLOBAL>(wp[r] + (lane + 32 * i) * 8);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        float a = 0.f;
+        float a[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a = dot8(w[r][i], &xr[i * 8], a);
-        acc[r] = warp_sum(a);
+        for (int i = 0; i < 4; ++i) a[i] = dot8(w[r][i], &xr[i * 8], 0.f);      // four independent chains
+        acc[r] = warp_sum((a[0] + a[1]) + (a[2] + a[3]));
     }
 }
 
 // xseg points at the 1024-float segment this sub-row multiplies, for batch row 0; batch rows are FF floats apart.
-template <int NB, int R>
+template <bool GLOBAL, int NB, int R>
 __device__ __forceinline__ void dot_subrows_smem(const bf16* const (&wp)[R], const float* const (&xseg)[R], int lane,
                                                  float (&acc)[R][NB]) {
     uint4 w[R][4];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) w[r][i] = ldg_stream(wp[r] + (lane + 32 * i) * 8);
+        for (int i = 0; i < 4; ++i) w[r][i] = load_w<GLOBAL>(wp[r] + (lane + 32 * i) * 8);
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -154,52 +283,20 @@ __device__ __forceinline__ void dot_subrows_smem(const bf16* const (&wp)[R], con
 }
 
 // Generic "R sub-rows" step used by all K=1024 phases.
-template <int NB, int R>
+template <bool GLOBAL, int NB, int R>
 __device__ __forceinline__ void dot_rows_k1024(Cta& c, const bf16* const (&wp)[R], const float (&xr)[32],
                                                float (&acc)[R][NB]) {
     if constexpr (NB == 1) {
         float a[R];
-        dot_subrows_xreg<R>(wp, xr, c.lane, a);
+        dot_subrows_xreg<GLOBAL, R>(wp, xr, c.lane, a);
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r][0] = a[r];
     } else {
         const float* xseg[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) xseg[r] = c.xs;
-        dot_subrows_smem<NB, R>(wp, xseg, c.lane, acc);
+        dot_subrows_smem<GLOBAL, NB, R>(wp, xseg, c.lane, acc);
     }
-}
-
-__device__ __forceinline__ void split_range(int n, int parts, int i, int& lo, int& hi) {
-    lo = (int)(((long long)n * i) / parts);
-    hi = (int)(((long long)n * (i + 1)) / parts);
-}
-
-__device__ __forceinline__ int attn_splits(int ncta, int batch) {
-    int s = ncta / (batch * NKV);
-    return s < 1 ? 1 : (s > Q3_MAX_SPLITS ? Q3_MAX_SPLITS : s);
-}
-// Cache range [start, end) of split s at context length n_ctx, in multiples of 32 positions.
-__device__ __forceinline__ void attn_range(int n_ctx, int n_splits, int s, int& start, int& end, int& chunk) {
-    chunk = (((n_ctx + n_splits - 1) / n_splits) + 31) & ~31;
-    start = s * chunk;
-    end = start + chunk < n_ctx ? start + chunk : n_ctx;
-}
-
-// ---- L2 prefetch ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void prefetch_bytes(const Cta& c, const void* base, size_t bytes) {
-    constexpr uint32_t kPiece = 4096;
-    const char* p = reinterpret_cast<const char*>(base);
-    for (size_t off = (size_t)c.tid * kPiece; off < bytes; off += (size_t)kThreads * kPiece) {
-        const size_t n = bytes - off < kPiece ? bytes - off : kPiece;
-        l2_prefetch(p + off, (uint32_t)n);
-    }
-}
-// rows are split over CTAs in multiples of `unit` rows exactly as the phases do
-__device__ __forceinline__ void prefetch_slice(const Cta& c, const bf16* base, size_t row_bytes, int n_rows, int unit) {
-    int lo, hi;
-    split_range(n_rows / unit, c.ncta, c.cta, lo, hi);
-    prefetch_bytes(c, reinterpret_cast<const char*>(base) + (size_t)lo * unit * row_bytes, (size_t)(hi - lo) * unit * row_bytes);
 }
 
 // ---- phase: embed gather (layer 0) + RMSNorm + QKV GEMV ------------------------------------------------
@@ -207,6 +304,7 @@ template <int NB>
 __device__ bool phase_qkv(Cta& c, int l) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t tag = tag_of(c, c.step, l);
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.ln1) + (size_t)l * D + 2 * c.tid);
     uint32_t u[NB];
     bool ok = true;
 #pragma unroll
@@ -217,43 +315,45 @@ __device__ bool phase_qkv(Cta& c, int l) {
     if (!all_ok(ok)) return false;
     c.t_ready = clock64();
 #pragma unroll
-    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], reinterpret_cast<const bf16*>(p.ln1) + (size_t)l * D, c.xs + b * FF);
-    __syncthreads();
+    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], gw, c.xs + b * FF);
+    cta_sync();
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
-    const bf16* W = reinterpret_cast<const bf16*>(p.wqkv) + (size_t)l * DQKV * D;
     int p0, p1;
     split_range(DQKV / 2, c.ncta, c.cta, p0, p1);
+    if (p1 == p0) return true;
+    bool okw;
+    const bf16* W = stream_acquire(c, c.st.consumed, okw);     // this CTA's rows [2*p0, 2*p1), contiguous
+    if (!okw) return false;
     for (int pr = p0 + c.warp; pr < p1; pr += kWarps) {
-        const bf16* wp[2] = {W + (size_t)(2 * pr) * D, W + (size_t)(2 * pr + 1) * D};
+        const bf16* wp[2] = {W + (size_t)(2 * (pr - p0)) * D, W + (size_t)(2 * (pr - p0) + 1) * D};
         float acc[2][NB];
-        dot_rows_k1024<NB, 2>(c, wp, xr, acc);
+        dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
         if (c.lane == 0) {
 #pragma unroll
             for (int b = 0; b < NB; ++b) st_flagged(c.ws.qkv + b * (DQKV / 2) + pr, pack_bf16x2(acc[0][b], acc[1][b]), tag);
         }
     }
+    stream_release(c.st, 1);
     return true;
 }
 
-// ---- phase: QK-RMSNorm + RoPE + KV append + split-K GQA attention + combine ---------------------------
-// Work item = (sequence b, kv head g, split s); CTA i takes item i.  Scores live in the log2 domain with the
-// softmax scale folded into q, as the reference does (src/ittai/qwen3/config.py:6-7).  Each split publishes
-// (m, l, o[2][128]); the first `nc` splits of a head then each merge a slice of the 256 outputs.
+// ---- phase: QK-RMSNorm + RoPE + KV append + split-K GQA attention + merge -----------------------------
+// Work item = (sequence b, kv head g, split s) = CTA index.  Scores live in the log2 domain with the softmax scale
+// folded into q, as the reference does (src/ittai/qwen3/config.py:6-7).  Old cache rows arrive through the ring in tiles
+// of 128 positions (a K entry and a V entry per tile); the row of the token being computed is taken from shared memory
+// and appended to the cache by the split that owns its position.  Each split publishes (m, l, o[2][128]); the first
+// `nc` splits of a head then each merge a slice of the 256 outputs.
 __device__ bool phase_attn(Cta& c, int l) {
     const IttaiQwen3Decode& p = c.p;
     const int B = p.batch;
     const int n_splits = attn_splits(c.ncta, B);
-    const int n_items = B * NKV * n_splits;
     const uint32_t tag = tag_of(c, c.step, l);
     SmemAttn* at = c.at;
-    bool first = true;
-    for (int item = c.cta; item < n_items; item += c.ncta) {
-        const int b = item / (NKV * n_splits), g = (item / n_splits) % NKV, s = item % n_splits;
-        const int pos = c.hdr->pos_s[b], n_ctx = pos + 1;
-        int start, end, chunk;
-        attn_range(n_ctx, n_splits, s, start, end, chunk);
-        const bool has_new = pos >= start && pos < start + chunk;
+    const AttnItem it = attn_item(c, c.step);
+    if (it.active) {
+        const int b = it.b, g = it.g, pos = it.pos;
+        const bool has_new = it.has_new;
         const uint64_t* qw = c.ws.qkv + (size_t)b * (DQKV / 2);
         const size_t head_off = ((((size_t)l * B + b) * NKV + g) * (size_t)p.kv_cap) * HD;
         bf16* kc = reinterpret_cast<bf16*>(p.kcache) + head_off;
@@ -261,26 +361,27 @@ __device__ bool phase_attn(Cta& c, int l) {
 
         // -- norm + rotate q (warps 0,1) and the new key (warp 2); copy the new value (warp 3).
         //    A lane owns elements 2*lane, 2*lane+1 and their rotation partners 64 + the same.
+        //    Gains and the rotary row are fetched before the wait, so their latency hides behind it.
         bool ok = true;
         if (c.warp < 3 && (c.warp < 2 || has_new)) {
             const bool is_k = c.warp == 2;
             const int e0 = is_k ? DQ + g * HD : (2 * g + c.warp) * HD;
             const bf16* gain = reinterpret_cast<const bf16*>(is_k ? p.kn : p.qn) + (size_t)l * HD;
+            const bf16* rp = reinterpret_cast<const bf16*>(p.rope) + (size_t)pos * HD;
+            const uint32_t ga = *reinterpret_cast<const uint32_t*>(gain + 2 * c.lane);
+            const uint32_t gb = *reinterpret_cast<const uint32_t*>(gain + HD / 2 + 2 * c.lane);
+            const uint32_t cw = *reinterpret_cast<const uint32_t*>(rp + 2 * c.lane);
+            const uint32_t sw = *reinterpret_cast<const uint32_t*>(rp + HD / 2 + 2 * c.lane);
             uint32_t ua = 0, ub = 0;
             ok = wait_word(c.w, qw + e0 / 2 + c.lane, tag, ua, ITTAI_PH_ATTN);
             ok = ok && wait_word(c.w, qw + e0 / 2 + 32 + c.lane, tag, ub, ITTAI_PH_ATTN);
             float x[4] = {bf_lo(ua), bf_hi(ua), bf_lo(ub), bf_hi(ub)};
             const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
             const float rstd = 1.0f / sqrtf(ss * (1.0f / HD) + p.eps);
-            const uint32_t ga = *reinterpret_cast<const uint32_t*>(gain + 2 * c.lane);
-            const uint32_t gb = *reinterpret_cast<const uint32_t*>(gain + HD / 2 + 2 * c.lane);
             x[0] = bf16r(bf16r(x[0] * rstd) * bf_lo(ga));
             x[1] = bf16r(bf16r(x[1] * rstd) * bf_hi(ga));
             x[2] = bf16r(bf16r(x[2] * rstd) * bf_lo(gb));
             x[3] = bf16r(bf16r(x[3] * rstd) * bf_hi(gb));
-            const bf16* rp = reinterpret_cast<const bf16*>(p.rope) + (size_t)pos * HD;
-            const uint32_t cw = *reinterpret_cast<const uint32_t*>(rp + 2 * c.lane);
-            const uint32_t sw = *reinterpret_cast<const uint32_t*>(rp + HD / 2 + 2 * c.lane);
             float lo[2], hi[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {      // pair (i, i+64), i = 2*lane + j
@@ -297,6 +398,7 @@ __device__ bool phase_attn(Cta& c, int l) {
                     *reinterpret_cast<uint32_t*>(kc + (size_t)pos * HD + 2 * c.lane) = wlo;
                     *reinterpret_cast<uint32_t*>(kc + (size_t)pos * HD + HD / 2 + 2 * c.lane) = whi;
                     __threadfence();
+                    fence_proxy_async();       // later tokens read this row through the TMA unit
                 }
             } else {
                 const float qscale = 0.08838834764831845f * kLog2e;   // head_dim^-0.5 * log2(e)
@@ -316,12 +418,14 @@ __device__ bool phase_attn(Cta& c, int l) {
                 *reinterpret_cast<uint32_t*>(vc + (size_t)pos * HD + 2 * c.lane) = ua;
                 *reinterpret_cast<uint32_t*>(vc + (size_t)pos * HD + HD / 2 + 2 * c.lane) = ub;
                 __threadfence();
+                fence_proxy_async();
             }
         }
-        if (c.tid < 2) { c.hdr->m_s[c.tid] = -INFINITY; c.hdr->l_s[c.tid] = 0.f; }
         if (!all_ok(ok)) return false;
-        if (first) { c.t_ready = clock64(); first = false; }
+        c.t_ready = clock64();
 
+        // -- every half-warp runs its own online softmax over the positions it owns (position index = 2*warp + half
+        //    modulo 32), with no CTA-wide barrier inside a tile; the 32 private (m, l, o) are merged once at the end.
         const int half = c.lane >> 4, sub = c.lane & 15;
         float q0[8], q1[8], acc0[8], acc1[8];
 #pragma unroll
@@ -330,116 +434,126 @@ __device__ bool phase_attn(Cta& c, int l) {
             q1[e] = at->qs[1][sub * 8 + e];
             acc0[e] = 0.f; acc1[e] = 0.f;
         }
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-        for (int tile0 = start; tile0 < end; tile0 += kTile) {
-            // -- scores: a half-warp reads one 256-byte key row; 8 rows in flight per lane
-            uint4 kv[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const int t = tile0 + r * 32 + c.warp * 2 + half;
-                if (t < end) {
-                    if (has_new && t == pos) kv[r] = *reinterpret_cast<const uint4*>(at->knew + sub * 8);
-                    else kv[r] = ldcg128(kc + (size_t)t * HD + sub * 8);
-                } else kv[r] = make_uint4(0, 0, 0, 0);
+        // positions of this split: n_old rows from the ring, then (has_new) the current token's row
+        const int n_pos = it.n_old + (has_new ? 1 : 0);
+        const int n_ring_tiles = (it.n_old + kTile - 1) / kTile;
+        for (int j = 0; j * kTile < n_pos; ++j) {
+            const int ring_rows = it.n_old - j * kTile < 0 ? 0 : (it.n_old - j * kTile < kTile ? it.n_old - j * kTile : kTile);
+            const bool from_ring = j < n_ring_tiles;
+            const bf16* kt = nullptr;
+            const bf16* vt = nullptr;
+            if (from_ring) {
+                const unsigned char* pk = stream_wait(c.st, c.st.consumed, c.w);
+                const unsigned char* pv = stream_wait(c.st, c.st.consumed + 1, c.w);
+                if (!all_ok(pk != nullptr && pv != nullptr)) return false;
+                kt = reinterpret_cast<const bf16*>(pk);
+                vt = reinterpret_cast<const bf16*>(pv);
             }
+            uint4 kk[kTile / 32], vv[kTile / 32];
+            bool valid[kTile / 32];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
+            for (int r = 0; r < kTile / 32; ++r) {
                 const int tl = r * 32 + c.warp * 2 + half;
-                float s0 = dot8(kv[r], q0, 0.f), s1 = dot8(kv[r], q1, 0.f);
+                valid[r] = j * kTile + tl < n_pos;
+                if (tl < ring_rows) {
+                    kk[r] = *reinterpret_cast<const uint4*>(kt + (size_t)tl * HD + sub * 8);
+                    vv[r] = *reinterpret_cast<const uint4*>(vt + (size_t)tl * HD + sub * 8);
+                } else if (has_new && j * kTile + tl == it.n_old) {
+                    kk[r] = *reinterpret_cast<const uint4*>(at->knew + sub * 8);
+                    vv[r] = *reinterpret_cast<const uint4*>(at->vnew + sub * 8);
+                } else {
+                    kk[r] = make_uint4(0, 0, 0, 0);
+                    vv[r] = make_uint4(0, 0, 0, 0);
+                }
+            }
+            float s0[kTile / 32], s1[kTile / 32];
+#pragma unroll
+            for (int r = 0; r < kTile / 32; ++r) {
+                float a0 = dot8(kk[r], q0, 0.f), a1 = dot8(kk[r], q1, 0.f);
 #pragma unroll
                 for (int o = 8; o > 0; o >>= 1) {
-                    s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                    a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, o);
                 }
-                if (sub == 0) {
-                    const bool valid = tile0 + tl < end;
-                    at->sc[0][tl] = valid ? s0 : -INFINITY;
-                    at->sc[1][tl] = valid ? s1 : -INFINITY;
-                }
+                s0[r] = valid[r] ? a0 : -INFINITY;
+                s1[r] = valid[r] ? a1 : -INFINITY;
             }
-            __syncthreads();
-            // -- running max / sum for each of the two heads (warp 0 -> head 0, warp 1 -> head 1)
-            if (c.warp < 2) {
-                float v[kTile / 32], mx = -INFINITY;
+            float mt0 = m0, mt1 = m1;
 #pragma unroll
-                for (int j = 0; j < kTile / 32; ++j) { v[j] = at->sc[c.warp][c.lane + 32 * j]; mx = fmaxf(mx, v[j]); }
-                mx = warp_max(mx);
-                const float m_old = c.hdr->m_s[c.warp];
-                const float m_new = fmaxf(m_old, mx);
-                float ps = 0.f;
-#pragma unroll
-                for (int j = 0; j < kTile / 32; ++j) {
-                    const float e = exp2f(v[j] - m_new);
-                    at->sc[c.warp][c.lane + 32 * j] = e;
-                    ps += e;
-                }
-                ps = warp_sum(ps);
-                if (c.lane == 0) {
-                    const float corr = exp2f(m_old - m_new);
-                    c.hdr->corr_s[c.warp] = corr;
-                    c.hdr->l_s[c.warp] = c.hdr->l_s[c.warp] * corr + ps;
-                    c.hdr->m_s[c.warp] = m_new;
-                }
-            }
-            __syncthreads();
-            // -- O += P V
-            const float c0 = c.hdr->corr_s[0], c1 = c.hdr->corr_s[1];
+            for (int r = 0; r < kTile / 32; ++r) { mt0 = fmaxf(mt0, s0[r]); mt1 = fmaxf(mt1, s1[r]); }
+            const float ms0 = mt0 == -INFINITY ? 0.f : mt0, ms1 = mt1 == -INFINITY ? 0.f : mt1;   // no (-inf) - (-inf)
+            const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
+            l0 *= c0; l1 *= c1;
 #pragma unroll
             for (int e = 0; e < 8; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const int t = tile0 + r * 32 + c.warp * 2 + half;
-                if (t < end) {
-                    if (has_new && t == pos) kv[r] = *reinterpret_cast<const uint4*>(at->vnew + sub * 8);
-                    else kv[r] = ldcg128(vc + (size_t)t * HD + sub * 8);
-                } else kv[r] = make_uint4(0, 0, 0, 0);
+            for (int r = 0; r < kTile / 32; ++r) {
+                const float p0 = exp2f(s0[r] - ms0), p1 = exp2f(s1[r] - ms1);
+                l0 += p0; l1 += p1;
+                const float ve[8] = {bf_lo(vv[r].x), bf_hi(vv[r].x), bf_lo(vv[r].y), bf_hi(vv[r].y),
+                                     bf_lo(vv[r].z), bf_hi(vv[r].z), bf_lo(vv[r].w), bf_hi(vv[r].w)};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { acc0[e] = fmaf(p0, ve[e], acc0[e]); acc1[e] = fmaf(p1, ve[e], acc1[e]); }
             }
+            m0 = mt0; m1 = mt1;
+            if (from_ring) stream_release(c.st, 2);
+        }
+        // -- merge the two halves of each warp, then the 16 warps, and publish (m, l, o) of this split
+        {
+            const float pm0 = __shfl_xor_sync(0xffffffffu, m0, 16), pm1 = __shfl_xor_sync(0xffffffffu, m1, 16);
+            const float pl0 = __shfl_xor_sync(0xffffffffu, l0, 16), pl1 = __shfl_xor_sync(0xffffffffu, l1, 16);
+            const float M0 = fmaxf(m0, pm0), M1 = fmaxf(m1, pm1);
+            const float S0 = M0 == -INFINITY ? 0.f : M0, S1 = M1 == -INFINITY ? 0.f : M1;
+            const float w0 = exp2f(m0 - S0), w1 = exp2f(m1 - S1), v0 = exp2f(pm0 - S0), v1 = exp2f(pm1 - S1);
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const int tl = r * 32 + c.warp * 2 + half;
-                const float p0 = at->sc[0][tl], p1 = at->sc[1][tl];
-                const float vv[8] = {bf_lo(kv[r].x), bf_hi(kv[r].x), bf_lo(kv[r].y), bf_hi(kv[r].y),
-                                     bf_lo(kv[r].z), bf_hi(kv[r].z), bf_lo(kv[r].w), bf_hi(kv[r].w)};
-#pragma unroll
-                for (int e = 0; e < 8; ++e) { acc0[e] = fmaf(p0, vv[e], acc0[e]); acc1[e] = fmaf(p1, vv[e], acc1[e]); }
+            for (int e = 0; e < 8; ++e) {
+                const float o0 = __shfl_xor_sync(0xffffffffu, acc0[e], 16), o1 = __shfl_xor_sync(0xffffffffu, acc1[e], 16);
+                acc0[e] = acc0[e] * w0 + o0 * v0;
+                acc1[e] = acc1[e] * w1 + o1 * v1;
             }
-            __syncthreads();
-        }
-        // -- fold the 32 per-(warp, half) partial outputs and publish (m, l, o) of this split
+            if (half == 0) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            acc0[e] += __shfl_xor_sync(0xffffffffu, acc0[e], 16);
-            acc1[e] += __shfl_xor_sync(0xffffffffu, acc1[e], 16);
+                for (int e = 0; e < 8; ++e) { at->ored[c.warp][0][sub * 8 + e] = acc0[e]; at->ored[c.warp][1][sub * 8 + e] = acc1[e]; }
+                if (sub == 0) {
+                    at->wm[c.warp][0] = M0; at->wm[c.warp][1] = M1;
+                    at->wl[c.warp][0] = l0 * w0 + pl0 * v0; at->wl[c.warp][1] = l1 * w1 + pl1 * v1;
+                }
+            }
         }
-        if (half == 0) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) { at->ored[c.warp][0][sub * 8 + e] = acc0[e]; at->ored[c.warp][1][sub * 8 + e] = acc1[e]; }
-        }
-        __syncthreads();
-        uint64_t* part = c.ws.part + (size_t)item * Q3_PART_WORDS;
+        cta_sync();
+        uint64_t* part = c.ws.part + (size_t)c.cta * Q3_PART_WORDS;
         if (c.tid < 2 * HD) {
             const int h = c.tid / HD, d = c.tid % HD;
-            float o = 0.f;
+            float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) o += at->ored[w][h][d];
+            for (int w = 0; w < kWarps; ++w) M = fmaxf(M, at->wm[w][h]);
+            const float Ms = M == -INFINITY ? 0.f : M;
+            float o = 0.f, ls = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float sc = exp2f(at->wm[w][h] - Ms);
+                o = fmaf(at->ored[w][h][d], sc, o);
+                ls = fmaf(at->wl[w][h], sc, ls);
+            }
             st_flagged(part + 4 + h * HD + d, __float_as_uint(o), tag);
             if (d == 0) {
-                st_flagged(part + h, __float_as_uint(c.hdr->m_s[h]), tag);
-                st_flagged(part + 2 + h, __float_as_uint(c.hdr->l_s[h]), tag);
+                st_flagged(part + h, __float_as_uint(M), tag);
+                st_flagged(part + 2 + h, __float_as_uint(ls), tag);
             }
         }
-        __syncthreads();
+        cta_sync();
+    } else {
+        c.t_ready = clock64();
     }
-    // -- merge: split s < nc of each (b, g) gathers, from every split of that head, the running max and sum and its
-    //    own slice of the outputs.  All partials are published before any CTA waits here, so CTAs that own several
-    //    items cannot wait on each other in a cycle.
+    // -- merge across splits: split s < nc of each (b, g) gathers, from every split of that head, the running max and
+    //    sum and its own slice of the outputs
     int nc = 1;
     while (nc * 2 <= n_splits && nc < 16) nc *= 2;
     const int dpc = HD / nc, W = 4 + 2 * dpc;
-    for (int item = c.cta; item < n_items; item += c.ncta) {
-        const int b = item / (NKV * n_splits), g = (item / n_splits) % NKV, s = item % n_splits;
-        if (s >= nc) continue;
-        const int d0 = s * dpc;
+    if (it.active && it.s < nc) {
+        const int b = it.b, g = it.g, d0 = it.s * dpc;
         const uint64_t* base = c.ws.part + (size_t)(b * NKV + g) * n_splits * Q3_PART_WORDS;
         bool ok = true;
         for (int idx = c.tid; idx < n_splits * W; idx += kThreads) {
@@ -464,7 +578,7 @@ __device__ bool phase_attn(Cta& c, int l) {
         const float nb = __shfl_down_sync(0xffffffffu, out, 1);
         if (valid && (dd & 1) == 0)
             st_flagged(c.ws.attn + (size_t)b * (DQ / 2) + ((2 * g + h) * HD + d0 + dd) / 2, pack_bf16x2(out, nb), tag);
-        __syncthreads();
+        cta_sync();
     }
     return true;
 }
@@ -474,32 +588,46 @@ __device__ bool phase_attn(Cta& c, int l) {
 // memory and are added in a fixed order.  out = bf16(resid + bf16(W x)) (reference base.py:110-123).
 // `res_src` == nullptr takes the residual from the embedding row (layer 0's o_proj).
 template <int NB, int K>
-__device__ bool phase_proj_residual(Cta& c, int what, const bf16* W, const uint64_t* x_src, uint32_t x_tag,
-                                    const uint64_t* res_src, uint32_t res_tag, uint64_t* dst, uint32_t dst_tag) {
+__device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uint32_t x_tag, const uint64_t* res_src,
+                                    uint32_t res_tag, uint64_t* dst, uint32_t dst_tag) {
     constexpr int S = K / 1024;
-    if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what)) return false;
-    c.t_ready = clock64();
+    constexpr int kSlots = 60;               // sub-rows finished per pass: a multiple of 4 and of 6, so row pairs stay whole
     int p0, p1;
     split_range(D / 2, c.ncta, c.cta, p0, p1);
-    const int r0 = 2 * p0, n_sub = 2 * (p1 - p0) * S;
-    constexpr int kSlots = 60;               // sub-rows finished per pass: a multiple of 4 and of 6, so row pairs stay whole
-    float* sub = c.hdr->sub;
+    // The residual rows this CTA owns were published phases ago: fetch them now, not after the GEMV.
     bool ok = true;
+    uint32_t rw_early = 0;
+    const int early_pairs = (2 * (p1 - p0) * S < kSlots ? 2 * (p1 - p0) * S : kSlots) / (2 * S);
+    if (c.tid < early_pairs * NB) {
+        const int pair = p0 + c.tid / NB, b = c.tid % NB;
+        if (res_src == nullptr)
+            rw_early = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
+        else
+            ok = wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw_early, 32 + what);
+    }
+    if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what)) return false;
+    c.t_ready = clock64();
+    if (p1 == p0) return all_ok(ok);
+    bool okw;
+    const bf16* W = stream_acquire(c, c.st.consumed, okw);     // this CTA's rows [2*p0, 2*p1), contiguous
+    if (!okw) return false;
+    const int n_sub = 2 * (p1 - p0) * S;
+    float* sub = c.hdr->sub;
     for (int base = 0; base < n_sub; base += kSlots) {
         const int cnt = n_sub - base < kSlots ? n_sub - base : kSlots;
         for (int sr = c.warp; sr < cnt; sr += kWarps) {
             const int gsr = base + sr;
-            const int row = r0 + gsr / S, seg = gsr % S;
-            const bf16* wp[1] = {W + (size_t)row * K + seg * 1024};
+            const int seg = gsr % S;
+            const bf16* wp[1] = {W + (size_t)gsr * 1024};
             const float* xseg[1] = {c.xs + seg * 1024};
             float acc[1][NB];
-            dot_subrows_smem<NB, 1>(wp, xseg, c.lane, acc);
+            dot_subrows_smem<false, NB, 1>(wp, xseg, c.lane, acc);
             if (c.lane == 0) {
 #pragma unroll
                 for (int b = 0; b < NB; ++b) sub[sr * NB + b] = acc[0][b];
             }
         }
-        __syncthreads();
+        cta_sync();
         const int pairs_here = cnt / (2 * S);
         for (int i = c.tid; i < pairs_here * NB; i += kThreads) {
             const int pp = i / NB, b = i % NB;
@@ -507,15 +635,18 @@ __device__ bool phase_proj_residual(Cta& c, int what, const bf16* W, const uint6
 #pragma unroll
             for (int k = 0; k < S; ++k) { s0 += sub[((2 * pp) * S + k) * NB + b]; s1 += sub[((2 * pp + 1) * S + k) * NB + b]; }
             const int pair = p0 + base / (2 * S) + pp;
-            uint32_t rw = 0;
-            if (res_src == nullptr)
-                rw = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
-            else
-                ok = ok && wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw, 32 + what);
+            uint32_t rw = rw_early;
+            if (base != 0 || i != c.tid) {       // only reached with fewer CTAs than a B200 has
+                if (res_src == nullptr)
+                    rw = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
+                else
+                    ok = ok && wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw, 32 + what);
+            }
             st_flagged(dst + (size_t)b * (D / 2) + pair, pack_bf16x2(bf_lo(rw) + bf16r(s0), bf_hi(rw) + bf16r(s1)), dst_tag);
         }
-        __syncthreads();
+        cta_sync();
     }
+    stream_release(c.st, 1);
     return all_ok(ok);
 }
 
@@ -530,6 +661,7 @@ template <int NB>
 __device__ bool phase_gu(Cta& c, int l) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t tag = tag_of(c, c.step, l);
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.ln2) + (size_t)l * D + 2 * c.tid);
     uint32_t u[NB];
     bool ok = true;
 #pragma unroll
@@ -537,28 +669,31 @@ __device__ bool phase_gu(Cta& c, int l) {
     if (!all_ok(ok)) return false;
     c.t_ready = clock64();
 #pragma unroll
-    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], reinterpret_cast<const bf16*>(p.ln2) + (size_t)l * D, c.xs + b * FF);
-    __syncthreads();
+    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], gw, c.xs + b * FF);
+    cta_sync();
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
-    const bf16* W = reinterpret_cast<const bf16*>(p.wgu) + (size_t)l * DGU * D;
     int u0, u1;
     split_range(FF / 2, c.ncta, c.cta, u0, u1);      // unit = two activations = four weight rows = one flagged word
+    if (u1 == u0) return true;
+    bool okw;
+    const bf16* W = stream_acquire(c, c.st.consumed, okw);
+    if (!okw) return false;
     for (int un = u0 + c.warp; un < u1; un += kWarps) {
+        const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
         float a0[NB], a1[NB];
         if constexpr (NB == 1) {
-            const bf16* wp[4] = {W + (size_t)(4 * un) * D, W + (size_t)(4 * un + 1) * D, W + (size_t)(4 * un + 2) * D,
-                                 W + (size_t)(4 * un + 3) * D};
+            const bf16* wp[4] = {wu, wu + D, wu + 2 * D, wu + 3 * D};
             float acc[4][NB];
-            dot_rows_k1024<NB, 4>(c, wp, xr, acc);
+            dot_rows_k1024<false, NB, 4>(c, wp, xr, acc);
             a0[0] = swiglu(acc[0][0], acc[1][0]);
             a1[0] = swiglu(acc[2][0], acc[3][0]);
         } else {
 #pragma unroll
             for (int hsel = 0; hsel < 2; ++hsel) {
-                const bf16* wp[2] = {W + (size_t)(4 * un + 2 * hsel) * D, W + (size_t)(4 * un + 2 * hsel + 1) * D};
+                const bf16* wp[2] = {wu + (2 * hsel) * D, wu + (2 * hsel + 1) * D};
                 float acc[2][NB];
-                dot_rows_k1024<NB, 2>(c, wp, xr, acc);
+                dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
 #pragma unroll
                 for (int b = 0; b < NB; ++b) (hsel ? a1[b] : a0[b]) = swiglu(acc[0][b], acc[1][b]);
             }
@@ -568,15 +703,18 @@ __device__ bool phase_gu(Cta& c, int l) {
             for (int b = 0; b < NB; ++b) st_flagged(c.ws.act + (size_t)b * (FF / 2) + un, pack_bf16x2(a0[b], a1[b]), tag);
         }
     }
+    stream_release(c.st, 1);
     return true;
 }
 
 // ---- phase: final RMSNorm + tied lm_head GEMV + argmax ------------------------------------------------
-// logits = bf16(W_embed x); argmax over the bf16 values, lowest index wins ties (torch semantics).  Every CTA
-// publishes its best (value, index); every CTA then gathers all of them, so each knows the next token at once.
+// logits = bf16(W_embed x); argmax over the bf16 values, lowest index wins ties (torch semantics).  The table is read
+// straight from HBM with streaming loads (2 MB per CTA: far more than the ring holds, and nothing waits behind it).
+// Every CTA publishes its best (value, index); every CTA then gathers all of them, so each knows the next token at once.
 template <int NB>
 __device__ bool phase_head(Cta& c) {
     const IttaiQwen3Decode& p = c.p;
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.fin_w) + 2 * c.tid);
     uint32_t u[NB];
     bool ok = true;
 #pragma unroll
@@ -585,42 +723,50 @@ __device__ bool phase_head(Cta& c) {
     if (!all_ok(ok)) return false;
     c.t_ready = clock64();
 #pragma unroll
-    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], reinterpret_cast<const bf16*>(p.fin_w), c.xs + b * FF);
-    __syncthreads();
+    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], gw, c.xs + b * FF);
+    cta_sync();
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
-    const bf16* W = reinterpret_cast<const bf16*>(p.embed);
     bf16* logits = reinterpret_cast<bf16*>(p.logits);
     int r0, r1;
     split_range(p.vocab, c.ncta, c.cta, r0, r1);
-    constexpr int R = (NB == 1) ? 4 : 2;
+    constexpr int R = kHeadRows / kWarps;        // rows of one streamed entry per warp
     float bv[NB];
     int bi[NB];
 #pragma unroll
     for (int b = 0; b < NB; ++b) { bv[b] = -INFINITY; bi[b] = 0x7fffffff; }
-    for (int row = r0 + c.warp * R; row < r1; row += kWarps * R) {
-        const bf16* wp[R];
+    for (int e0 = r0; e0 < r1; e0 += kHeadRows) {
+        bool okw;
+        const bf16* W = stream_acquire(c, c.st.consumed, okw);     // rows [e0, e0 + kHeadRows) of the table
+        if (!okw) return false;
+        const int rows_here = r1 - e0 < kHeadRows ? r1 - e0 : kHeadRows;
+        const int lr = c.warp * R;                                 // this warp's first row inside the entry
+        if (lr < rows_here) {
+            const bf16* wp[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) wp[r] = W + (size_t)(row + r < r1 ? row + r : r1 - 1) * D;
-        float acc[R][NB];
-        dot_rows_k1024<NB, R>(c, wp, xr, acc);
+            for (int r = 0; r < R; ++r) wp[r] = W + (size_t)(lr + r < rows_here ? lr + r : rows_here - 1) * D;
+            float acc[R][NB];
+            dot_rows_k1024<false, NB, R>(c, wp, xr, acc);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (row + r < r1) {
+            for (int r = 0; r < R; ++r) {
+                if (lr + r < rows_here) {
+                    const int row = e0 + lr + r;
 #pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                    const float v = bf16r(acc[r][b]);
-                    if (v > bv[b]) { bv[b] = v; bi[b] = row + r; }   // rows ascend within a warp: first max kept
-                    if (p.write_logits && c.lane == 0) logits[(size_t)b * p.vocab + row + r] = __float2bfloat16_rn(v);
+                    for (int b = 0; b < NB; ++b) {
+                        const float v = bf16r(acc[r][b]);
+                        if (v > bv[b]) { bv[b] = v; bi[b] = row; }   // rows ascend within a warp: first max kept
+                        if (p.write_logits && c.lane == 0) logits[(size_t)b * p.vocab + row] = __float2bfloat16_rn(v);
+                    }
                 }
             }
         }
+        stream_release(c.st, 1);
     }
     const uint32_t tag = (uint32_t)c.step + 1u;
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
         if (c.lane == 0) { c.hdr->bestv[c.warp] = bv[b]; c.hdr->besti[c.warp] = bi[b]; }
-        __syncthreads();
+        cta_sync();
         if (c.tid == 0) {
             float v = c.hdr->bestv[0];
             int ix = c.hdr->besti[0];
@@ -632,7 +778,7 @@ __device__ bool phase_head(Cta& c) {
             st_flagged(c.ws.cand_val + c.cta * ITTAI_MAX_BATCH + b, __float_as_uint(v), tag);
             st_flagged(c.ws.cand_idx + c.cta * ITTAI_MAX_BATCH + b, (uint32_t)ix, tag);
         }
-        __syncthreads();
+        cta_sync();
     }
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
@@ -667,53 +813,23 @@ __device__ bool phase_head(Cta& c) {
                 }
             }
         }
-        __syncthreads();
+        cta_sync();
     }
     return true;
 }
 
-// ---- L2 prefetch one layer ahead ------------------------------------------------------------------------
-// While phase (l, ph) runs, ask L2 for this CTA's slice of the same phase of the next layer (layer 0 of the next
-// token after the last layer).  126 MB of L2 hold a layer's 31 MB of weights plus its cache slice several times over.
-__device__ void prefetch_ahead(const Cta& c, int ph, int l) {
-    const IttaiQwen3Decode& p = c.p;
-    const int lt = l + 1 < p.n_layers ? l + 1 : 0;
-    switch (ph) {
-        case ITTAI_PH_QKV: prefetch_slice(c, reinterpret_cast<const bf16*>(p.wqkv) + (size_t)lt * DQKV * D, D * 2, DQKV, 2); break;
-        case ITTAI_PH_ATTN: {
-            const int n_splits = attn_splits(c.ncta, p.batch);
-            const int item = c.cta;
-            if (item < p.batch * NKV * n_splits) {
-                const int b = item / (NKV * n_splits), g = (item / n_splits) % NKV, s = item % n_splits;
-                int start, end, chunk;
-                attn_range(c.hdr->pos_s[b] + 1, n_splits, s, start, end, chunk);
-                if (end > start) {
-                    const size_t off = (((((size_t)lt * p.batch + b) * NKV + g) * (size_t)p.kv_cap) + start) * HD;
-                    prefetch_bytes(c, reinterpret_cast<const bf16*>(p.kcache) + off, (size_t)(end - start) * HD * 2);
-                    prefetch_bytes(c, reinterpret_cast<const bf16*>(p.vcache) + off, (size_t)(end - start) * HD * 2);
-                }
-            }
-            break;
-        }
-        case ITTAI_PH_OPROJ: prefetch_slice(c, reinterpret_cast<const bf16*>(p.wo) + (size_t)lt * D * DQ, DQ * 2, D, 2); break;
-        case ITTAI_PH_GU: prefetch_slice(c, reinterpret_cast<const bf16*>(p.wgu) + (size_t)lt * DGU * D, D * 2, DGU, 4); break;
-        case ITTAI_PH_DOWN: prefetch_slice(c, reinterpret_cast<const bf16*>(p.wd) + (size_t)lt * D * FF, FF * 2, D, 2); break;
-        default: break;
-    }
-}
-
 // ---- per-step set-up: positions and input ids ----------------------------------------------------------
 // Returns false (uniformly over the grid) when an id or a position is out of range.
-__device__ bool step_setup(Cta& c, int step, const int* pos0, bool ids_from_head) {
+__device__ bool step_setup(Cta& c, int step, bool ids_from_head) {
     const IttaiQwen3Decode& p = c.p;
     if (c.tid < p.batch) {
         const int b = c.tid;
-        c.hdr->pos_s[b] = pos0[b] + step;
+        c.hdr->pos_s[b] = c.hdr->pos0[b] + step;
         if (step < p.n_forced) c.hdr->tok_s[b] = p.forced[(size_t)step * p.batch + b];
         else if (!ids_from_head) c.hdr->tok_s[b] = p.next_id[b];
         // else: the head of the previous step left the id in tok_s
     }
-    __syncthreads();
+    cta_sync();
     bool ok = true;
     for (int b = 0; b < p.batch; ++b) {
         const int t = c.hdr->tok_s[b], ps = c.hdr->pos_s[b];
@@ -728,18 +844,15 @@ __device__ bool step_setup(Cta& c, int step, const int* pos0, bool ids_from_head
 
 template <int NB>
 __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
-    const IttaiQwen3Decode& p = c.p;
     const uint32_t tag = tag_of(c, c.step, l);
     switch (phase) {
         case ITTAI_PH_QKV: return phase_qkv<NB>(c, l);
         case ITTAI_PH_ATTN: return phase_attn(c, l);
         case ITTAI_PH_OPROJ:
-            return phase_proj_residual<NB, DQ>(c, ITTAI_PH_OPROJ, reinterpret_cast<const bf16*>(p.wo) + (size_t)l * D * DQ,
-                                               c.ws.attn, tag, l == 0 ? nullptr : c.ws.h, tag, c.ws.hmid, tag);
+            return phase_proj_residual<NB, DQ>(c, ITTAI_PH_OPROJ, c.ws.attn, tag, l == 0 ? nullptr : c.ws.h, tag, c.ws.hmid, tag);
         case ITTAI_PH_GU: return phase_gu<NB>(c, l);
         case ITTAI_PH_DOWN:
-            return phase_proj_residual<NB, FF>(c, ITTAI_PH_DOWN, reinterpret_cast<const bf16*>(p.wd) + (size_t)l * D * FF,
-                                               c.ws.act, tag, c.ws.hmid, tag, c.ws.h, tag_of(c, c.step, l + 1));
+            return phase_proj_residual<NB, FF>(c, ITTAI_PH_DOWN, c.ws.act, tag, c.ws.hmid, tag, c.ws.h, tag_of(c, c.step, l + 1));
         default: return phase_head<NB>(c);
     }
 }
@@ -747,78 +860,94 @@ __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
 // The per-CTA context is brace-initialised inside each kernel.  nvcc 12.9 mis-infers the shared state space for the
 // global pointers of a struct returned by value from a helper that also receives the shared-memory base, so there is
 // deliberately no make_cta() function.
-#define ITTAI_MAKE_CTA(p, wsp, smem)                                                                              \
+#define ITTAI_MAKE_CTA(p, wsp, smem, nb, ring_bytes)                                                              \
     Cta c{p, wsp, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<float*>(smem + kHdrBytes),                   \
           reinterpret_cast<SmemAttn*>(smem + kHdrBytes), (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x,       \
           (int)(threadIdx.x & 31), (int)(threadIdx.x >> 5),                                                       \
-          Waiter{wsp.sync, p.status, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit}, 0, 0}
+          Waiter{wsp.sync, p.status, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit},                     \
+          Stream{&reinterpret_cast<SmemHdr*>(smem)->stream, smem + q3_fixed_smem_bytes(nb), ring_bytes, 0u},      \
+          0, 0}
 
 template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) q3_decode_kernel(const __grid_constant__ IttaiQwen3Decode p,
-                                                                const __grid_constant__ Q3Workspace wsp) {
+__global__ void __launch_bounds__(kBlock, 1) q3_decode_kernel(const __grid_constant__ IttaiQwen3Decode p,
+                                                                const __grid_constant__ Q3Workspace wsp,
+                                                                uint32_t ring_bytes) {
     extern __shared__ __align__(256) unsigned char smem[];
-    ITTAI_MAKE_CTA(p, wsp, smem);
+    ITTAI_MAKE_CTA(p, wsp, smem, NB, ring_bytes);
     if ((p.flags & ITTAI_F_TEST_DROP_CTA) != 0 && c.cta == 0) return;
-    __shared__ int pos0[ITTAI_MAX_BATCH];
-    if (c.tid < p.batch) pos0[c.tid] = p.pos[c.tid];
-    __syncthreads();
-    const bool prefetch = (p.flags & ITTAI_F_L2_PREFETCH) != 0;
+    if (c.tid < p.batch) c.hdr->pos0[c.tid] = p.pos[c.tid];
+    stream_init(c.st, c.tid);
+    if (c.tid >= kThreads) {     // the stream-feeding warp: one lane issues, the others have nothing to do
+        if (c.tid == kThreads) stream_feed(c, 0, p.n_steps * (kStreamPhases * p.n_layers + 1));
+        return;
+    }
     const bool prof = p.phase_clk != nullptr && c.cta == 0 && c.tid == 0;
-    bool prev_head = false;
+    bool prev_head = false, ok = true;
 
-    for (int step = 0; step < p.n_steps; ++step) {
+    for (int step = 0; step < p.n_steps && ok; ++step) {
         c.step = step;
-        if (!step_setup(c, step, pos0, prev_head)) return;
+        ok = step_setup(c, step, prev_head);
+        if (!ok) break;
         const bool run_head = step >= p.n_forced - 1;
         if (!run_head && c.cta == 0 && c.tid < p.batch) p.out_ids[(size_t)step * p.batch + c.tid] = -1;
         if (step > 0 && !prev_head) {
             // No head ran, so nothing yet orders this token after the previous one: wait for its last layer's output
             // before any buffer of the chain is written again.
-            bool ok = true;
+            bool okw = true;
             for (int b = 0; b < p.batch; ++b) {
                 uint32_t u;
-                ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag_of(c, step - 1, p.n_layers), u, 64);
+                okw = okw && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag_of(c, step - 1, p.n_layers), u, 64);
             }
-            if (!all_ok(ok)) return;
+            ok = all_ok(okw);
+            if (!ok) break;
         }
-        for (int l = 0; l < p.n_layers; ++l) {
+        for (int l = 0; l < p.n_layers && ok; ++l) {
 #pragma unroll 1
-            for (int phase = ITTAI_PH_QKV; phase <= ITTAI_PH_DOWN; ++phase) {
-                if (prefetch) prefetch_ahead(c, phase, l);
-                if (!run_phase<NB>(c, phase, l)) return;
-                if (prof) {
+            for (int phase = ITTAI_PH_QKV; phase <= ITTAI_PH_DOWN && ok; ++phase) {
+                ok = run_phase<NB>(c, phase, l);
+                if (prof && ok) {
                     const size_t slot = ((size_t)step * (5 * p.n_layers + 1) + l * 5 + phase) * 2;
                     p.phase_clk[slot] = (uint64_t)c.t_ready;
                     p.phase_clk[slot + 1] = (uint64_t)clock64();
                 }
             }
         }
-        if (run_head) {
-            if (!phase_head<NB>(c)) return;
-            if (prof) {
+        if (run_head && ok) {
+            ok = phase_head<NB>(c);
+            if (prof && ok) {
                 const size_t slot = ((size_t)step * (5 * p.n_layers + 1) + 5 * p.n_layers) * 2;
                 p.phase_clk[slot] = (uint64_t)c.t_ready;
                 p.phase_clk[slot + 1] = (uint64_t)clock64();
             }
         }
         prev_head = run_head;
-        if (p.step_ns != nullptr && c.cta == 0 && c.tid == 0) p.step_ns[step] = globaltimer_ns();
+        if (ok && p.step_ns != nullptr && c.cta == 0 && c.tid == 0) p.step_ns[step] = globaltimer_ns();
     }
-    if (c.cta == 0 && c.tid < p.batch) p.pos[c.tid] = pos0[c.tid] + p.n_steps;
+    if (!ok) {                   // leaving early: the feeding lane stops issuing and waits for its copies in flight
+        if (c.tid == 0) c.st.sh->stop = 1u;
+        return;
+    }
+    if (c.cta == 0 && c.tid < p.batch) p.pos[c.tid] = c.hdr->pos0[c.tid] + p.n_steps;
 }
 
 // One phase on its own at step 0 (tags of step 0): unit tests and per-phase profiles.  Inputs must carry the tag of
 // (step 0, layer); launched cooperatively because the attention merge and the head wait on other CTAs.
 template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) q3_phase_kernel(const __grid_constant__ IttaiQwen3Decode p,
-                                                               const __grid_constant__ Q3Workspace wsp, int phase, int l) {
+__global__ void __launch_bounds__(kBlock, 1) q3_phase_kernel(const __grid_constant__ IttaiQwen3Decode p,
+                                                               const __grid_constant__ Q3Workspace wsp,
+                                                               uint32_t ring_bytes, int phase, int l) {
     extern __shared__ __align__(256) unsigned char smem[];
-    ITTAI_MAKE_CTA(p, wsp, smem);
-    __shared__ int pos0[ITTAI_MAX_BATCH];
-    if (c.tid < p.batch) pos0[c.tid] = p.pos[c.tid];
-    __syncthreads();
-    if (!step_setup(c, 0, pos0, false)) return;
-    run_phase<NB>(c, phase, l);
+    ITTAI_MAKE_CTA(p, wsp, smem, NB, ring_bytes);
+    if (c.tid < p.batch) c.hdr->pos0[c.tid] = p.pos[c.tid];
+    stream_init(c.st, c.tid);
+    if (c.tid >= kThreads) {
+        const int k = phase == ITTAI_PH_HEAD ? kStreamPhases * p.n_layers : l * kStreamPhases + phase;
+        if (c.tid == kThreads) stream_feed(c, k, k + 1);
+        return;
+    }
+    bool ok = step_setup(c, 0, false);
+    if (ok) ok = run_phase<NB>(c, phase, l);
+    if (!ok && c.tid == 0) c.st.sh->stop = 1u;
 }
 
 // ---- host side ---------------------------------------------------------------------------------------
@@ -832,7 +961,7 @@ static int check_args(const IttaiQwen3Decode* p) {
     if (p->n_forced < 0 || p->n_forced > p->n_steps) { set_error("n_forced %d outside 0..n_steps", p->n_forced); return ITTAI_E_ARG; }
     if (p->n_forced > 0 && !p->forced) { set_error("n_forced > 0 with forced == NULL"); return ITTAI_E_ARG; }
     if (p->write_logits && !p->logits) { set_error("write_logits set with logits == NULL"); return ITTAI_E_ARG; }
-    if ((long long)p->n_steps * (p->n_layers + 1) >= (1ll << 31)) { set_error("n_steps * (n_layers + 1) must stay below 2^31"); return ITTAI_E_ARG; }
+    if ((long long)p->n_steps * (kStreamPhases * p->n_layers + 1) >= (1ll << 31)) { set_error("n_steps * (n_layers + 1) * 5 must stay below 2^31"); return ITTAI_E_ARG; }
     const void* req[] = {p->wqkv, p->wo, p->wgu, p->wd, p->ln1, p->ln2, p->qn, p->kn, p->fin_w, p->embed, p->rope,
                          p->kcache, p->vcache, p->pos, p->next_id, p->out_ids, p->workspace, p->status};
     for (const void* q : req) if (!q) { set_error("null device pointer in IttaiQwen3Decode"); return ITTAI_E_ARG; }
@@ -842,31 +971,38 @@ static int check_args(const IttaiQwen3Decode* p) {
     return ITTAI_OK;
 }
 
-struct DeviceInfo { int dev = -1; int n_sms = 0; bool attr_set[4] = {false, false, false, false}; };
+struct DeviceInfo { int dev = -1; int n_sms = 0; int smem_optin = 0; bool attr_set[4] = {false, false, false, false}; };
 static thread_local DeviceInfo g_info;
 
-static int device_info(int* n_sms) {
+static int device_info() {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (g_info.dev != dev) {
-        int sms = 0;
+        int sms = 0, optin = 0;
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
+        e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(shared memory)");
         g_info = DeviceInfo();
         g_info.dev = dev;
         g_info.n_sms = sms;
+        g_info.smem_optin = optin;
     }
-    *n_sms = g_info.n_sms;
     return ITTAI_OK;
 }
 
 template <int NB>
 static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream_t st) {
-    int n_sms = 0;
-    int rc = device_info(&n_sms);
+    int rc = device_info();
     if (rc != ITTAI_OK) return rc;
-    const size_t smem = q3_smem_bytes(NB) + 256;   // slack: the dynamic region starts on a 256-byte boundary after the static words
+    const int grid = g_info.n_sms < Q3_MAX_CTAS ? g_info.n_sms : Q3_MAX_CTAS;
+    if (grid < p->batch * NKV) { set_error("%d SMs cannot hold one attention item per CTA at batch %d", grid, p->batch); return ITTAI_E_DEVICE; }
+    // all the shared memory a CTA may have: header + activations + the weight ring
+    const size_t fixed = q3_fixed_smem_bytes(NB);
+    const size_t smem = (size_t)g_info.smem_optin;
+    if (smem < fixed + 96 * 1024) { set_error("%zu bytes of shared memory per CTA leave no room for the weight ring", smem); return ITTAI_E_DEVICE; }
+    uint32_t ring_bytes = (uint32_t)((smem - fixed) / 1024 * 1024);
     const void* fn_decode = (const void*)q3_decode_kernel<NB>;
     const void* fn_phase = (const void*)q3_phase_kernel<NB>;
     constexpr int slot = NB == 1 ? 0 : NB == 2 ? 1 : NB == 4 ? 2 : 3;
@@ -876,7 +1012,7 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
         e = cudaFuncSetAttribute(fn_phase, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(phase)");
         int occ = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, q3_decode_kernel<NB>, kThreads, smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, q3_decode_kernel<NB>, kBlock, smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
         if (occ < 1) { set_error("device cannot hold one persistent CTA per SM (%zu bytes of shared memory)", smem); return ITTAI_E_DEVICE; }
         g_info.attr_set[slot] = true;
@@ -891,14 +1027,13 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
     }
     e = cudaMemsetAsync(p->status, 0, ITTAI_STATUS_WORDS * sizeof(uint32_t), st);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
-    const int grid = n_sms < Q3_MAX_CTAS ? n_sms : Q3_MAX_CTAS;
     if (phase < 0) {
-        void* args[] = {(void*)p, (void*)&ws};
-        e = cudaLaunchCooperativeKernel(fn_decode, dim3(grid), dim3(kThreads), args, smem, st);
+        void* args[] = {(void*)p, (void*)&ws, (void*)&ring_bytes};
+        e = cudaLaunchCooperativeKernel(fn_decode, dim3(grid), dim3(kBlock), args, smem, st);
         if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchCooperativeKernel(q3_decode_kernel)");
     } else {
-        void* args[] = {(void*)p, (void*)&ws, (void*)&phase, (void*)&layer};
-        e = cudaLaunchCooperativeKernel(fn_phase, dim3(grid), dim3(kThreads), args, smem, st);
+        void* args[] = {(void*)p, (void*)&ws, (void*)&ring_bytes, (void*)&phase, (void*)&layer};
+        e = cudaLaunchCooperativeKernel(fn_phase, dim3(grid), dim3(kBlock), args, smem, st);
         if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchCooperativeKernel(q3_phase_kernel)");
     }
     return ITTAI_OK;

@@ -69,7 +69,7 @@ class Qwen3Decoder:
     the last step, ``.kcache`` / ``.vcache`` are the cache tensors.
     """
 
-    def __init__(self, sd_or_model, max_batch: int = 1, kv_capacity: int = 8192, device="cuda", l2_prefetch: bool = True):
+    def __init__(self, sd_or_model, max_batch: int = 1, kv_capacity: int = 8192, device="cuda"):
         sd = sd_or_model if isinstance(sd_or_model, dict) else sd_or_model.state_dict()
         sd = _strip(sd)
         if max_batch not in (1, 2, 4, 8):
@@ -95,7 +95,7 @@ class Qwen3Decoder:
         _C.check(self.lib.ittai_qwen3_decode_workspace_bytes(self.B, C.byref(nbytes)))
         self.workspace = z(nbytes.value + 256, dt=torch.uint8)
         self._ws_ptr = (self.workspace.data_ptr() + 255) // 256 * 256
-        self.flags = _C.F_L2_PREFETCH if l2_prefetch else 0
+        self.flags = 0
         self.spin_limit = 0                  # 0 = library default
         self.lengths = [0] * self.B          # host mirror of `pos`, for capacity checks without a device read
         self._keep = None
