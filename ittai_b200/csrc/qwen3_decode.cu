@@ -451,22 +451,15 @@ __device__ bool phase_attn(Cta& c, int l) {
                 kt = reinterpret_cast<const bf16*>(pk);
                 vt = reinterpret_cast<const bf16*>(pv);
             }
-            uint4 kk[kTile / 32], vv[kTile / 32];
+            uint4 kk[kTile / 32];
             bool valid[kTile / 32];
 #pragma unroll
             for (int r = 0; r < kTile / 32; ++r) {
                 const int tl = r * 32 + c.warp * 2 + half;
                 valid[r] = j * kTile + tl < n_pos;
-                if (tl < ring_rows) {
-                    kk[r] = *reinterpret_cast<const uint4*>(kt + (size_t)tl * HD + sub * 8);
-                    vv[r] = *reinterpret_cast<const uint4*>(vt + (size_t)tl * HD + sub * 8);
-                } else if (has_new && j * kTile + tl == it.n_old) {
-                    kk[r] = *reinterpret_cast<const uint4*>(at->knew + sub * 8);
-                    vv[r] = *reinterpret_cast<const uint4*>(at->vnew + sub * 8);
-                } else {
-                    kk[r] = make_uint4(0, 0, 0, 0);
-                    vv[r] = make_uint4(0, 0, 0, 0);
-                }
+                if (tl < ring_rows) kk[r] = *reinterpret_cast<const uint4*>(kt + (size_t)tl * HD + sub * 8);
+                else if (has_new && j * kTile + tl == it.n_old) kk[r] = *reinterpret_cast<const uint4*>(at->knew + sub * 8);
+                else kk[r] = make_uint4(0, 0, 0, 0);
             }
             float s0[kTile / 32], s1[kTile / 32];
 #pragma unroll
@@ -492,8 +485,12 @@ __device__ bool phase_attn(Cta& c, int l) {
             for (int r = 0; r < kTile / 32; ++r) {
                 const float p0 = exp2f(s0[r] - ms0), p1 = exp2f(s1[r] - ms1);
                 l0 += p0; l1 += p1;
-                const float ve[8] = {bf_lo(vv[r].x), bf_hi(vv[r].x), bf_lo(vv[r].y), bf_hi(vv[r].y),
-                                     bf_lo(vv[r].z), bf_hi(vv[r].z), bf_lo(vv[r].w), bf_hi(vv[r].w)};
+                const int tl = r * 32 + c.warp * 2 + half;
+                uint4 vr = make_uint4(0, 0, 0, 0);
+                if (tl < ring_rows) vr = *reinterpret_cast<const uint4*>(vt + (size_t)tl * HD + sub * 8);
+                else if (has_new && j * kTile + tl == it.n_old) vr = *reinterpret_cast<const uint4*>(at->vnew + sub * 8);
+                const float ve[8] = {bf_lo(vr.x), bf_hi(vr.x), bf_lo(vr.y), bf_hi(vr.y),
+                                     bf_lo(vr.z), bf_hi(vr.z), bf_lo(vr.w), bf_hi(vr.w)};
 #pragma unroll
                 for (int e = 0; e < 8; ++e) { acc0[e] = fmaf(p0, ve[e], acc0[e]); acc1[e] = fmaf(p1, ve[e], acc1[e]); }
             }
