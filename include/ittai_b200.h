@@ -61,7 +61,8 @@ enum {
     ITTAI_ST_FLAG_TIMEOUT = 2,    /* status[1]=what was awaited (phase id, +16 merge, +32 residual, 64 step order),
                                      status[2]=CTA, status[3]=tag seen, status[4]=tag expected */
     ITTAI_ST_BAD_TOKEN = 3,       /* status[1]=token id, status[2]=step, status[3]=position, status[4]=sequence */
-    ITTAI_ST_STREAM_TIMEOUT = 4   /* a weight-stream copy did not land: status[1]=entry, status[2]=CTA */
+    ITTAI_ST_STREAM_TIMEOUT = 4,  /* a weight-stream copy did not land: status[1]=entry, status[2]=CTA */
+    ITTAI_ST_GEMM_TIMEOUT = 5     /* a pipeline wait of the tensor-core GEMM ran out: status[1]=CTA */
 };
 
 /* Phases of one decoded token, in execution order inside a layer (ids used by ittai_qwen3_phase_launch). */
@@ -154,6 +155,34 @@ int ittai_qwen3_decode_launch(const IttaiQwen3Decode* p, void* stream);
  * code as the persistent kernel, for unit parity tests and per-phase profiling.  `pos`/`next_id` are
  * read, not advanced. */
 int ittai_qwen3_phase_launch(const IttaiQwen3Decode* p, int phase, int layer, void* stream);
+
+/* ---- dense bf16 GEMM on tcgen05 / TMEM (Qwen3 prefill, SigLIP encoder) ------------------------------- */
+
+/* Fused epilogues, the ones the reference's GEMM epilogues apply (src/ittai/qwen3/base.py:110-129,
+ * src/ittai/siglip/kernel.py:266-333).  Bias and residual are independent of `epi`: they apply when non-NULL. */
+enum {
+    ITTAI_EPI_NONE = 0,   /* out = bf16(acc [+ bias]) [then + residual, rounded again]                  */
+    ITTAI_EPI_GELU = 1,   /* out = bf16(gelu_tanh(bf16(acc + bias)))                                      */
+    ITTAI_EPI_SWIGLU = 2  /* columns (2i, 2i+1) = (gate, up): out[:, i] = bf16(bf16(silu(gate)) * up); N/2 columns */
+};
+
+/* out[M, N] = a[M, K] * w[N, K]^T with fp32 accumulation.  a, w, residual, out are bf16 row-major; bias is fp32.
+ * N must be a multiple of 128 and K of 64; leading dimensions of 0 mean "dense".  `status` must be zeroed by the
+ * caller before a sequence of launches and decoded afterwards. */
+typedef struct IttaiGemm {
+    int32_t m, n, k, epi;
+    int32_t ld_a, ld_w, ld_out, ld_res;
+    const void* a;
+    const void* w;
+    const void* bias;      /* [N] fp32 or NULL */
+    const void* residual;  /* [M, ld_res] bf16 or NULL */
+    void* out;
+    uint32_t* status;      /* [ITTAI_STATUS_WORDS] device words */
+} IttaiGemm;
+
+/* Replaces the tiled GEMM main loops + epilogues of the reference's megakernels
+ * (src/ittai/qwen3/sm80.py:175-272, src/ittai/qwen3/sm90.py:256-316, src/ittai/siglip/kernel.py:197-333). */
+int ittai_gemm_bf16_launch(const IttaiGemm* g, void* stream);
 
 #ifdef __cplusplus
 }

@@ -21,7 +21,9 @@ PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 EXPORTS = (
     "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
     "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
+    "ittai_gemm_bf16_launch",
 )
+EPI_NONE, EPI_GELU, EPI_SWIGLU = range(3)
 
 
 class IttaiError(RuntimeError):
@@ -43,6 +45,16 @@ class Qwen3Decode(C.Structure):
     ]
 
 
+class Gemm(C.Structure):
+    """Mirror of ``struct IttaiGemm``."""
+    _fields_ = [
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("epi", C.c_int32),
+        ("ld_a", C.c_int32), ("ld_w", C.c_int32), ("ld_out", C.c_int32), ("ld_res", C.c_int32),
+        ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
+        ("out", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -61,6 +73,7 @@ def lib() -> C.CDLL:
     L.ittai_qwen3_decode_workspace_bytes.argtypes = [C.c_int, C.POINTER(C.c_size_t)]
     L.ittai_qwen3_decode_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
     L.ittai_qwen3_phase_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_int, C.c_int, C.c_void_p]
+    L.ittai_gemm_bf16_launch.argtypes = [C.POINTER(Gemm), C.c_void_p]
     if L.ittai_version() != ABI_VERSION:
         raise IttaiError(f"library ABI {L.ittai_version()} != binding ABI {ABI_VERSION}; rebuild")
     _lib = L

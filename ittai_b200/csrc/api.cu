@@ -51,6 +51,7 @@ extern "C" int ittai_decode_status(const uint32_t* st, char* msg, size_t n) {
         case ITTAI_ST_BARRIER_TIMEOUT: what = "grid barrier wait ran out (a=tag b=cta c=arrivals seen d=arrivals expected)"; break;
         case ITTAI_ST_FLAG_TIMEOUT: what = "flag wait ran out (a=what was awaited b=cta c=tag seen d=tag expected)"; break;
         case ITTAI_ST_STREAM_TIMEOUT: what = "weight-stream copy did not land (a=entry b=cta c=slot d=parity)"; break;
+        case ITTAI_ST_GEMM_TIMEOUT: what = "tensor-core GEMM pipeline wait ran out (a=cta b=k-blocks)"; break;
         case ITTAI_ST_BAD_TOKEN: what = "token id or cache position out of range (a=id b=step c=position d=sequence)"; break;
         default: what = "unknown status code"; break;
     }

@@ -1,0 +1,266 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T (+ fused epilogue), fp32 accumulation in
+// tensor memory.  Both operands are K-major, as the reference stores them (activations [M,K], weights [N,K]:
+// src/ittai/qwen3/sm80.py:175-237, src/ittai/siglip/kernel.py:197-264), and the epilogues fuse what the reference's
+// GEMM epilogues fuse (src/ittai/qwen3/base.py:110-129, src/ittai/siglip/kernel.py:266-333): bias, residual add,
+// GELU-tanh, SwiGLU on interleaved gate/up columns.
+//
+// One CTA computes one 128 x 128 output tile.  Warp 0 (one lane) streams 128 x 64 operand tiles through a ring of
+// shared-memory stages with TMA (128-byte swizzle); warp 1 allocates 128 TMEM columns and (one lane) issues four
+// tcgen05.mma (M128 N128 K16) per stage, releasing the stage with tcgen05.commit; warps 2-5 read the accumulator with
+// tcgen05.ld (each warp its own 32 TMEM lanes = 32 output rows) and run the epilogue.  Every wait is bounded; a wait
+// that runs out sets the status word, all roles fall through to the common exit and TMEM is freed.
+#include <cuda.h>
+
+#include "tcgen05.cuh"
+
+namespace ittai {
+
+constexpr int GM = 128, GN = 128, GK = 64;
+constexpr int kGemmStages = 6;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kStageBytesA = GM * GK * 2, kStageBytesB = GN * GK * 2;
+constexpr uint32_t kGemmSmem = kGemmStages * (kStageBytesA + kStageBytesB) + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr uint32_t kGemmSpin = 1u << 24;
+
+struct GemmArgs {
+    int M, N, K;
+    int epi;                 // ITTAI_EPI_*
+    const float* bias;       // [N] or nullptr
+    const bf16* residual;    // [M, ld_res] or nullptr
+    int ld_res;
+    bf16* out;               // [M, ld_out]  (SwiGLU: N/2 columns)
+    int ld_out;
+    uint32_t* status;        // device status words
+};
+
+__device__ __forceinline__ float gelu_tanh(float y) {
+    return 0.5f * y * (1.0f + tanhf(0.7978845608028654f * (y + 0.044715f * y * y * y)));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmArgs g) {
+    extern __shared__ __align__(1024) unsigned char gsm_raw[];
+    unsigned char* gsm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sa = gsm;                                         // [stages][128 rows][128 B]
+    unsigned char* sb = gsm + kGemmStages * kStageBytesA;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sb + kGemmStages * kStageBytesB);
+    unsigned long long* full = bars;                                 // [stages]
+    unsigned long long* empty = bars + kGemmStages;                  // [stages]
+    unsigned long long* acc_full = bars + 2 * kGemmStages;           // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kGemmStages + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = g.N / GN;
+    const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+    const int n_kb = g.K / GK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, GN);          // 128 fp32 columns x 128 lanes
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int s = kb % kGemmStages, use = kb / kGemmStages;
+                if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1, kGemmSpin)) { *abort_flag = 1; break; }
+                if (*abort_flag) break;
+                mbar_expect_tx(&full[s], kStageBytesA + kStageBytesB);
+                tma_load_2d(sa + s * kStageBytesA, &tm_a, kb * GK, tile_m * GM, &full[s]);
+                tma_load_2d(sb + s * kStageBytesB, &tm_b, kb * GK, tile_n * GN, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            constexpr uint32_t idesc = umma_idesc_bf16(GM, GN);
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; ++kb) {
+                const int s = kb % kGemmStages, use = kb / kGemmStages;
+                ok = mbar_wait_bounded(&full[s], use & 1, kGemmSpin) && !*abort_flag;
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * kStageBytesB);
+#pragma unroll
+                for (int k = 0; k < GK / 16; ++k)      // 16 bf16 = 32 bytes = 2 descriptor address units per step
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);                // the stage is free once these MMAs have read it
+            }
+            if (!ok) *abort_flag = 1;
+            umma_commit(acc_full);                     // accumulator complete (or as far as it got)
+        }
+    } else {
+        // ---- epilogue: warp w owns TMEM lanes 32*(w%4)..+31 = rows of the tile
+        const bool ok = mbar_wait_bounded(acc_full, 0, kGemmSpin);
+        tc_fence_after();
+        if (!ok) *abort_flag = 1;
+        const int q = warp & 3;
+        const int row = tile_m * GM + q * 32 + lane;
+        if (ok && !*abort_flag) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < GN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (row < g.M) {
+                    const int col = tile_n * GN + c0;
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    if (g.bias != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(g.bias + col + i);
+                            v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+                        }
+                    }
+                    if (g.epi == ITTAI_EPI_SWIGLU) {
+                        // adjacent columns are (gate, up): act = bf16(bf16(silu(bf16 gate)) * bf16 up)
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const float g0 = bf16r(v[2 * i]), u0 = bf16r(v[2 * i + 1]);
+                            const float g1 = bf16r(v[2 * i + 2]), u1 = bf16r(v[2 * i + 3]);
+                            o[i / 2] = pack_bf16x2(bf16r(g0 / (1.0f + expf(-g0))) * u0, bf16r(g1 / (1.0f + expf(-g1))) * u1);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col / 2);
+                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else {
+                        if (g.epi == ITTAI_EPI_GELU) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(bf16r(v[i]));   // the Linear output is rounded before the activation
+                        }
+                        if (g.residual != nullptr) {
+                            // out = bf16(residual + bf16(acc [+ bias])): the module output is rounded before the add
+                            const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.ld_res + col);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint4 rr = rs[i];
+                                const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    v[i * 8 + 2 * j] = bf_lo(w[j]) + bf16r(v[i * 8 + 2 * j]);
+                                    v[i * 8 + 2 * j + 1] = bf_hi(w[j]) + bf16r(v[i * 8 + 2 * j + 1]);
+                                }
+                            }
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            dst[i] = make_uint4(pack_bf16x2(v[i * 8], v[i * 8 + 1]), pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]),
+                                                pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]), pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            if (atomicCAS(&g.status[0], 0u, (uint32_t)ITTAI_ST_GEMM_TIMEOUT) == 0u) { g.status[1] = blockIdx.x; g.status[2] = (uint32_t)n_kb; }
+            // let copies that may still be in flight land before the shared memory is handed back
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {}
+        }
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc(tmem_base, GN);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Tensor map over a row-major bf16 matrix [rows, cols] with leading dimension ld: boxes of 128 rows x 64 columns.
+static int make_tmap(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return ITTAI_E_CUDA; }
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)GK, (cuuint32_t)GM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %d)", (int)r, rows, cols, ld); return ITTAI_E_CUDA; }
+    return ITTAI_OK;
+}
+
+int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
+    if (!a || !a->a || !a->w || !a->out || !a->status) { set_error("null pointer in IttaiGemm"); return ITTAI_E_ARG; }
+    if (a->m < 1 || a->n < GN || a->n % GN != 0 || a->k < GK || a->k % GK != 0) {
+        set_error("gemm shape M=%d N=%d K=%d: N must be a multiple of %d and K of %d", a->m, a->n, a->k, GN, GK);
+        return ITTAI_E_ARG;
+    }
+    if (a->epi < ITTAI_EPI_NONE || a->epi > ITTAI_EPI_SWIGLU) { set_error("unknown epilogue %d", a->epi); return ITTAI_E_ARG; }
+    if (a->epi == ITTAI_EPI_SWIGLU && a->residual) { set_error("SwiGLU epilogue takes no residual"); return ITTAI_E_ARG; }
+    const int ld_a = a->ld_a ? a->ld_a : a->k, ld_w = a->ld_w ? a->ld_w : a->k;
+    const int n_out = a->epi == ITTAI_EPI_SWIGLU ? a->n / 2 : a->n;
+    const int ld_out = a->ld_out ? a->ld_out : n_out, ld_res = a->ld_res ? a->ld_res : a->n;
+    if (((uintptr_t)a->a & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->out & 15) || ((uintptr_t)a->residual & 15) ||
+        ((uintptr_t)a->bias & 15) || ld_a % 8 || ld_w % 8 || ld_out % 8 || ld_res % 8) {
+        set_error("gemm operands must be 16-byte aligned with leading dimensions that are multiples of 8");
+        return ITTAI_E_ARG;
+    }
+    CUtensorMap tm_a, tm_b;
+    int rc = make_tmap(&tm_a, a->a, a->m, a->k, ld_a);
+    if (rc != ITTAI_OK) return rc;
+    rc = make_tmap(&tm_b, a->w, a->n, a->k, ld_w);
+    if (rc != ITTAI_OK) return rc;
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
+        attr_dev = dev;
+    }
+    GemmArgs g;
+    g.M = a->m; g.N = a->n; g.K = a->k; g.epi = a->epi;
+    g.bias = reinterpret_cast<const float*>(a->bias);
+    g.residual = reinterpret_cast<const bf16*>(a->residual);
+    g.ld_res = ld_res;
+    g.out = reinterpret_cast<bf16*>(a->out);
+    g.ld_out = ld_out;
+    g.status = a->status;
+    const int tiles = ((a->m + GM - 1) / GM) * (a->n / GN);
+    gemm_bf16_kernel<<<tiles, kGemmThreads, kGemmSmem, st>>>(tm_a, tm_b, g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch gemm_bf16_kernel");
+    return ITTAI_OK;
+}
+
+}  // namespace ittai
+
+extern "C" int ittai_gemm_bf16_launch(const IttaiGemm* a, void* stream) {
+    return ittai::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,46 @@
+"""Host-side handles on the dense kernels shared by the Qwen3 prefill and SigLIP engines (thin ctypes calls)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _C
+
+
+def new_status(device) -> torch.Tensor:
+    """Zeroed device status words; pass to a sequence of launches, then ``check_status``."""
+    return torch.zeros(_C.STATUS_WORDS, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor) -> None:
+    _C.decode_status(status.cpu().tolist())
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = epilogue(a @ w.T)`` on the tcgen05 GEMM: a [M, K] and w [N, K] bf16 (last dim contiguous), bias fp32 [N],
+    residual bf16 [M, N].  SwiGLU takes interleaved (gate, up) weight rows and returns [M, N/2]."""
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k
+    n_out = n // 2 if epi == _C.EPI_SWIGLU else n
+    if out is None:
+        out = torch.empty(m, n_out, dtype=torch.bfloat16, device=a.device)
+    g = _C.Gemm()
+    g.m, g.n, g.k, g.epi = m, n, k, epi
+    g.ld_a, g.ld_w, g.ld_out = a.stride(0), w.stride(0), out.stride(0)
+    g.a, g.w, g.out, g.status = a.data_ptr(), w.data_ptr(), out.data_ptr(), status.data_ptr()
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+        g.bias = bias.data_ptr()
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (m, n) and residual.stride(1) == 1
+        g.residual, g.ld_res = residual.data_ptr(), residual.stride(0)
+    _C.check(_C.lib().ittai_gemm_bf16_launch(C.byref(g), _stream(a)))
+    return out
