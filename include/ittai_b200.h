@@ -184,6 +184,43 @@ typedef struct IttaiGemm {
  * (src/ittai/qwen3/sm80.py:175-272, src/ittai/qwen3/sm90.py:256-316, src/ittai/siglip/kernel.py:197-333). */
 int ittai_gemm_bf16_launch(const IttaiGemm* g, void* stream);
 
+/* ---- softmax attention for the prefill and SigLIP paths ------------------------------------------------- */
+
+/* Flash-style attention over `n_seqs` independent sequences.  Row r of sequence s lives at
+ *   q + (seqs[s].q_row0 + r) * q_row + head * q_head           (same for o)
+ *   k + s * k_seq + (head / group) * k_head + (seqs[s].kv_row0 + j) * k_row   (same for v)
+ * all strides in elements, multiples of 8.  causal != 0: query r sees keys j <= r + (kv_len - q_len).
+ * Replaces the attention tasks of src/ittai/qwen3/sm80.py:274-403 and src/ittai/siglip/kernel.py:366-500. */
+typedef struct IttaiAttention {
+    const void* q; const void* k; const void* v; void* o;          /* bf16 */
+    int64_t q_row, q_head, k_row, k_head, k_seq, v_row, v_head, v_seq, o_row, o_head;
+    const int32_t* seqs;   /* [n_seqs][4] device: first q row, q rows, first k/v row, k/v rows */
+    int32_t n_seqs, n_heads, group, head_dim, causal, max_q_len;
+} IttaiAttention;
+int ittai_attention_launch(const IttaiAttention* a, void* stream);
+
+/* ---- row-wise passes around the GEMMs ------------------------------------------------------------------- */
+
+/* y = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * gain) over rows of 1024 bf16 (Qwen3 RMSNorm; the reference folds the gain
+ * into the next weight and applies the scale in the GEMM epilogue: src/ittai/qwen3/engine.py:106-111, base.py:84-85). */
+int ittai_rmsnorm_rows(const void* x, int ld_x, const void* gain, void* y, int ld_y, int rows, float eps, void* stream);
+/* y = bf16(LayerNorm(x) * gain + beta), gain/beta fp32, width a multiple of 8 up to 2048 (SigLIP; folded into the next
+ * GEMM by the reference: src/ittai/siglip/kernel.py:284-288,523-525). */
+int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, const void* beta, void* y, int ld_y, int rows, int width,
+                         float eps, void* stream);
+/* Qwen3 prefill: per-head RMSNorm + RoPE of q (in place in qkv[T, 4096]) and k, and the scatter of k and v into one layer
+ * of the cache ([B, 8, kv_cap, 128]) at (seq[t], pos[t]).  The reference's qkv epilogue: src/ittai/qwen3/base.py:84-109. */
+int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void* kn, const void* rope, const int32_t* pos,
+                                const int32_t* seq, void* kcache_layer, void* vcache_layer, int n_tokens, int kv_cap,
+                                float eps, void* stream);
+/* fp32 pixels [B, 3, H, W] -> bf16 patch rows [B * (H/p) * (W/p), 3 p p] in (channel, row, col) order
+ * (the torch unfold of src/ittai/siglip/kernel.py:633-637). */
+int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, void* stream);
+/* out[t, :] = table[ids[t], :], rows of 1024 bf16 (src/ittai/qwen3/base.py:147-162). */
+int ittai_embed_rows(const int32_t* ids, const void* table, void* out, int rows, int vocab, void* stream);
+/* Embedding head: out[s] = l2_normalise(rmsnorm(h[rows[s]]) * gain) in fp32 (src/ittai/qwen3/base.py:131-145). */
+int ittai_qwen3_final_pool(const void* h, const int32_t* rows, const void* gain, float* out, int n_seq, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,7 +21,8 @@ PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 EXPORTS = (
     "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
     "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
-    "ittai_gemm_bf16_launch",
+    "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows",
+    "ittai_qwen3_qk_rope_scatter", "ittai_siglip_im2col", "ittai_embed_rows", "ittai_qwen3_final_pool",
 )
 EPI_NONE, EPI_GELU, EPI_SWIGLU = range(3)
 
@@ -55,6 +56,18 @@ class Gemm(C.Structure):
     ]
 
 
+class Attention(C.Structure):
+    """Mirror of ``struct IttaiAttention``."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+        ("q_row", C.c_int64), ("q_head", C.c_int64), ("k_row", C.c_int64), ("k_head", C.c_int64), ("k_seq", C.c_int64),
+        ("v_row", C.c_int64), ("v_head", C.c_int64), ("v_seq", C.c_int64), ("o_row", C.c_int64), ("o_head", C.c_int64),
+        ("seqs", C.c_void_p),
+        ("n_seqs", C.c_int32), ("n_heads", C.c_int32), ("group", C.c_int32), ("head_dim", C.c_int32),
+        ("causal", C.c_int32), ("max_q_len", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -74,6 +87,14 @@ def lib() -> C.CDLL:
     L.ittai_qwen3_decode_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
     L.ittai_qwen3_phase_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_int, C.c_int, C.c_void_p]
     L.ittai_gemm_bf16_launch.argtypes = [C.POINTER(Gemm), C.c_void_p]
+    L.ittai_attention_launch.argtypes = [C.POINTER(Attention), C.c_void_p]
+    vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+    L.ittai_rmsnorm_rows.argtypes = [vp, i32, vp, vp, i32, i32, f32, vp]
+    L.ittai_layernorm_rows.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, f32, vp]
+    L.ittai_qwen3_qk_rope_scatter.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp]
+    L.ittai_siglip_im2col.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+    L.ittai_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp]
+    L.ittai_qwen3_final_pool.argtypes = [vp, vp, vp, vp, i32, f32, vp]
     if L.ittai_version() != ABI_VERSION:
         raise IttaiError(f"library ABI {L.ittai_version()} != binding ABI {ABI_VERSION}; rebuild")
     _lib = L

@@ -1,0 +1,193 @@
+// Softmax attention for the prefill and SigLIP paths: flash-style, 64 query rows x 64 keys per step, causal (Qwen3,
+// grouped-query, head_dim 128) or dense with a key-length mask (SigLIP, head_dim 64).  Same schedule as the
+// reference's attention tasks (src/ittai/qwen3/sm80.py:274-403, src/ittai/siglip/kernel.py:366-500): Q tile resident,
+// K/V blocks streamed, scores and softmax in fp32 in the log2 domain, P rounded to bf16 for the PV product.
+// Tensor-core path: warp-level mma.sync m16n8k16 (bf16 in, fp32 accumulate) on ldmatrix fragments from swizzled
+// shared memory.  Attention is a few percent of SigLIP's FLOPs and a third of a 4k prefill's.
+#include "common.cuh"
+
+namespace ittai {
+
+struct AttnArgs {
+    const bf16* q; const bf16* k; const bf16* v; bf16* o;
+    long long q_row, q_head, k_row, k_head, k_seq, v_row, v_head, v_seq, o_row, o_head;   // strides in elements
+    const int4* seqs;     // per sequence: {first q/o row, q rows, first k/v row, k/v rows}
+    int group;            // query heads per kv head
+    float scale_log2;     // head_dim^-0.5 * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kAttnBM = 64, kAttnBN = 64, kAttnThreads = 128;
+
+// element offset of 16-byte chunk `ch` of row `r` in a [rows][HD] tile whose chunks are XOR-swizzled by the row
+template <int HD>
+__device__ __forceinline__ int sw(int r, int ch) { return r * HD + ((ch ^ (r & 7)) << 3); }
+
+template <int HD>
+__device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, long long row_stride, int rows_valid, int tid) {
+    constexpr int CH = HD / 8;
+    for (int i = tid; i < 64 * CH; i += kAttnThreads) {
+        const int r = i / CH, ch = i % CH;
+        cp_async16(dst + sw<HD>(r, ch), src + (long long)r * row_stride + ch * 8, r < rows_valid);
+    }
+}
+
+template <int HD, bool CAUSAL>
+__global__ void __launch_bounds__(kAttnThreads) attn_fwd_kernel(const AttnArgs a) {
+    __shared__ __align__(128) bf16 sq[kAttnBM * HD];
+    __shared__ __align__(128) bf16 sk[kAttnBN * HD];
+    __shared__ __align__(128) bf16 sv[kAttnBN * HD];
+    const int4 sinfo = a.seqs[blockIdx.z];
+    const int q_len = sinfo.y, kv_len = sinfo.w;
+    const int qb = blockIdx.x * kAttnBM;
+    if (qb >= q_len) return;
+    const int head = blockIdx.y, kvh = head / a.group;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const bf16* qp = a.q + (long long)(sinfo.x + qb) * a.q_row + (long long)head * a.q_head;
+    const bf16* kp = a.k + (long long)blockIdx.z * a.k_seq + (long long)kvh * a.k_head + (long long)sinfo.z * a.k_row;
+    const bf16* vp = a.v + (long long)blockIdx.z * a.v_seq + (long long)kvh * a.v_head + (long long)sinfo.z * a.v_row;
+    const int q_rows = q_len - qb < kAttnBM ? q_len - qb : kAttnBM;
+    const int shift = kv_len - q_len;                       // query i sees keys j <= i + shift
+    int kv_end = kv_len;
+    if (CAUSAL) { const int lim = qb + q_rows + shift; kv_end = lim < kv_len ? lim : kv_len; }
+
+    load_tile<HD>(sq, qp, a.q_row, q_rows, tid);
+    cp_async_wait_all();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldsm_x4(qf[ks], sq + sw<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows g and g + 8 of this warp's 16
+    const int row0 = qb + warp * 16 + g, row1 = row0 + 8;
+
+    for (int kb = 0; kb < kv_end; kb += kAttnBN) {
+        __syncthreads();                                     // everyone is done with the previous K/V block
+        const int rows_valid = kv_len - kb < kAttnBN ? kv_len - kb : kAttnBN;
+        load_tile<HD>(sk, kp + (long long)kb * a.k_row, a.k_row, rows_valid, tid);
+        load_tile<HD>(sv, vp + (long long)kb * a.v_row, a.v_row, rows_valid, tid);
+        cp_async_wait_all();
+        __syncthreads();
+        // ---- S = Q K^T
+        float s[kAttnBN / 8][4];
+#pragma unroll
+        for (int i = 0; i < kAttnBN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < kAttnBN / 16; ++np) {
+                uint32_t kf[4];
+                ldsm_x4(kf, sk + sw<HD>(np * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
+                mma16816(s[2 * np], qf[ks], kf[0], kf[1]);
+                mma16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        // ---- mask, scale, online softmax
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kAttnBN / 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + i * 8 + 2 * t + (e & 1), r = (e < 2) ? row0 : row1;
+                const bool vis = j < kv_len && (!CAUSAL || j <= r + shift);
+                s[i][e] = vis ? s[i][e] * a.scale_log2 : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
+        m0 = mn0; m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+        uint32_t pf[kAttnBN / 16][4];
+#pragma unroll
+        for (int i = 0; i < kAttnBN / 8; ++i) {
+            const float p0 = exp2f(s[i][0] - ms0), p1 = exp2f(s[i][1] - ms0), p2 = exp2f(s[i][2] - ms1), p3 = exp2f(s[i][3] - ms1);
+            ps0 += p0 + p1; ps1 += p2 + p3;
+            pf[i / 2][(i & 1) * 2] = pack_bf16x2(p0, p1);
+            pf[i / 2][(i & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+        }
+        l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        // ---- O += P V
+#pragma unroll
+        for (int ks = 0; ks < kAttnBN / 16; ++ks) {
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t vf[4];
+                ldsm_x4_t(vf, sv + sw<HD>(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4)));
+                mma16816(o[2 * dp], pf[ks], vf[0], vf[1]);
+                mma16816(o[2 * dp + 1], pf[ks], vf[2], vf[3]);
+            }
+        }
+    }
+    // ---- normalise and store
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    bf16* op = a.o + (long long)sinfo.x * a.o_row + (long long)head * a.o_head;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * t;
+        if (row0 < q_len) *reinterpret_cast<uint32_t*>(op + (long long)row0 * a.o_row + d) = pack_bf16x2(o[i][0] * i0, o[i][1] * i0);
+        if (row1 < q_len) *reinterpret_cast<uint32_t*>(op + (long long)row1 * a.o_row + d) = pack_bf16x2(o[i][2] * i1, o[i][3] * i1);
+    }
+}
+
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+}  // namespace ittai
+
+using namespace ittai;
+
+extern "C" int ittai_attention_launch(const IttaiAttention* p, void* stream) {
+    if (!p || !p->q || !p->k || !p->v || !p->o || !p->seqs) { set_error("attention: null pointer"); return ITTAI_E_ARG; }
+    if (p->head_dim != 64 && p->head_dim != 128) { set_error("attention: head_dim %d (64 or 128)", p->head_dim); return ITTAI_E_ARG; }
+    if (p->n_seqs < 1 || p->n_heads < 1 || p->group < 1 || p->max_q_len < 1) { set_error("attention: bad sizes"); return ITTAI_E_ARG; }
+    const long long strides[] = {p->q_row, p->q_head, p->k_row, p->k_head, p->k_seq, p->v_row, p->v_head, p->v_seq, p->o_row};
+    for (long long s : strides) if (s % 8) { set_error("attention: strides must be multiples of 8 elements"); return ITTAI_E_ARG; }
+    AttnArgs a;
+    a.q = (const bf16*)p->q; a.k = (const bf16*)p->k; a.v = (const bf16*)p->v; a.o = (bf16*)p->o;
+    a.q_row = p->q_row; a.q_head = p->q_head; a.k_row = p->k_row; a.k_head = p->k_head; a.k_seq = p->k_seq;
+    a.v_row = p->v_row; a.v_head = p->v_head; a.v_seq = p->v_seq; a.o_row = p->o_row; a.o_head = p->o_head;
+    a.seqs = (const int4*)p->seqs; a.group = p->group;
+    a.scale_log2 = 1.4426950408889634f / sqrtf((float)p->head_dim);
+    const dim3 grid((p->max_q_len + kAttnBM - 1) / kAttnBM, p->n_heads, p->n_seqs);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (p->head_dim == 128) {
+        if (p->causal) attn_fwd_kernel<128, true><<<grid, kAttnThreads, 0, st>>>(a);
+        else attn_fwd_kernel<128, false><<<grid, kAttnThreads, 0, st>>>(a);
+    } else {
+        if (p->causal) attn_fwd_kernel<64, true><<<grid, kAttnThreads, 0, st>>>(a);
+        else attn_fwd_kernel<64, false><<<grid, kAttnThreads, 0, st>>>(a);
+    }
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_fwd_kernel");
+}

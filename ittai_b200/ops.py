@@ -44,3 +44,34 @@ def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Ten
         g.residual, g.ld_res = residual.data_ptr(), residual.stride(0)
     _C.check(_C.lib().ittai_gemm_bf16_launch(C.byref(g), _stream(a)))
     return out
+
+
+def attention(q, k, v, o, seqs: torch.Tensor, *, n_heads: int, group: int, head_dim: int, causal: bool, max_q_len: int,
+              q_strides, k_strides, v_strides, o_strides) -> None:
+    """Flash attention over sequences described by ``seqs`` (int32 [n, 4] device: q row0, q rows, kv row0, kv rows).
+
+    ``q_strides`` = (row, head), ``k_strides`` / ``v_strides`` = (row, head, seq), ``o_strides`` = (row, head), in elements;
+    q, k, v, o are any bf16 tensors whose ``data_ptr`` is the origin those strides refer to."""
+    a = _C.Attention()
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    a.q_row, a.q_head = q_strides
+    a.k_row, a.k_head, a.k_seq = k_strides
+    a.v_row, a.v_head, a.v_seq = v_strides
+    a.o_row, a.o_head = o_strides
+    a.seqs = seqs.data_ptr()
+    a.n_seqs, a.n_heads, a.group, a.head_dim, a.causal, a.max_q_len = seqs.shape[0], n_heads, group, head_dim, int(causal), max_q_len
+    _C.check(_C.lib().ittai_attention_launch(C.byref(a), _stream(q)))
+
+
+def rmsnorm_rows(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    out = torch.empty_like(x) if out is None else out
+    _C.check(_C.lib().ittai_rmsnorm_rows(x.data_ptr(), x.stride(0), gain.data_ptr(), out.data_ptr(), out.stride(0), x.shape[0], eps, _stream(x)))
+    return out
+
+
+def layernorm_rows(x: torch.Tensor, gain: torch.Tensor, beta: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    out = torch.empty_like(x) if out is None else out
+    assert gain.dtype == torch.float32 and beta.dtype == torch.float32
+    _C.check(_C.lib().ittai_layernorm_rows(x.data_ptr(), x.stride(0), gain.data_ptr(), beta.data_ptr(), out.data_ptr(), out.stride(0),
+                                          x.shape[0], x.shape[1], eps, _stream(x)))
+    return out

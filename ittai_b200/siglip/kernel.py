@@ -1,0 +1,170 @@
+"""SigLIP vision tower on the B200 kernels, behind the reference's ``Engine`` / ``Siglip2Embedder`` surface
+(reference ``src/ittai/siglip/kernel.py:532-723``).
+
+What runs where: patch gather, LayerNorm and attention are row-wise / flash kernels; every Linear (patch embedding,
+qkv, out-proj, fc1 + GELU-tanh, fc2 + residual, and the MAP head's projections) is the tcgen05 GEMM with its fused
+epilogue; the whole forward, MAP pooling head included, is one CUDA graph.  The reference keeps the post-LayerNorm and
+the MAP head in torch (``:626-629``) and computes in fp16 with fp16 accumulation (``:42,73``); here everything is bf16
+storage with fp32 accumulation, and the rounding points are the eager modules'.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _C, ops
+
+
+def _vision_model(m):
+    return m.vision_model if hasattr(m, "vision_model") else m
+
+
+class Engine:
+    """``Engine(vm, B)``: fixed batch ``B``; ``forward({"pixel_values": fp32 [B,3,H,W]})`` returns bf16 ``[B, D]`` pooled
+    embeddings (a persistent buffer, like the reference's ``self.embeds``).  The reference's tuning arguments
+    (``tile_n, stages, warps, fold_k, group_m, kv_block``) are accepted and ignored: there is one sm_100a kernel."""
+
+    @torch.no_grad()
+    def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True):
+        vm = _vision_model(vm)
+        cfg, emb = vm.config, vm.embeddings
+        if not isinstance(emb.patch_embedding, torch.nn.Conv2d):
+            raise NotImplementedError("variable-resolution (NaFlex) patch embedding is not built; fixed-resolution Conv2d towers only")
+        self.vm, self.B = vm, B
+        self.D, self.F, self.H, self.L = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_hidden_layers
+        self.p, self.eps, self.img = cfg.patch_size, cfg.layer_norm_eps, cfg.image_size
+        self.hd = self.D // self.H
+        self.S0 = emb.num_patches
+        if self.hd != 64 or self.D % 128 or self.F % 128 or (3 * self.p * self.p) % 64:
+            raise NotImplementedError("this build covers head_dim 64 and widths that are multiples of 128 (ViT-B/16)")
+        dev = next(vm.parameters()).device
+        self.dev = dev
+        D, S, M = self.D, self.S0, B * self.S0
+        self.M = M
+        bf = lambda t: t.detach().to(dev, torch.bfloat16).contiguous()
+        f32 = lambda t: t.detach().to(dev, torch.float32).contiguous()
+        self.wpe, self.bpe = bf(emb.patch_embedding.weight.reshape(D, -1)), f32(emb.patch_embedding.bias)
+        # position table repeated per image: the patch-embedding GEMM adds it as its residual (reference :569-571)
+        self.pos = bf(emb.position_embedding.weight).repeat(B, 1)
+        self.layers = []
+        for lyr in vm.encoder.layers:
+            a, m = lyr.self_attn, lyr.mlp
+            self.layers.append(dict(
+                ln1=(f32(lyr.layer_norm1.weight), f32(lyr.layer_norm1.bias)), ln2=(f32(lyr.layer_norm2.weight), f32(lyr.layer_norm2.bias)),
+                wqkv=bf(torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight])),
+                bqkv=f32(torch.cat([a.q_proj.bias, a.k_proj.bias, a.v_proj.bias])),
+                wo=bf(a.out_proj.weight), bo=f32(a.out_proj.bias), w1=bf(m.fc1.weight), b1=f32(m.fc1.bias),
+                w2=bf(m.fc2.weight), b2=f32(m.fc2.bias)))
+        self.post = (f32(vm.post_layernorm.weight), f32(vm.post_layernorm.bias))
+        h = vm.head
+        inw, inb = h.attention.in_proj_weight, h.attention.in_proj_bias
+        # the probe is a parameter, so its query projection does not depend on the image: computed once, as the eager
+        # module would (bf16 Linear)
+        self.probe_q = bf(torch.nn.functional.linear(h.probe[0].to(torch.bfloat16), inw[:D].to(torch.bfloat16), inb[:D].to(torch.bfloat16)))
+        self.wkv, self.bkv = bf(inw[D:]), f32(inb[D:])
+        self.who, self.bho = bf(h.attention.out_proj.weight), f32(h.attention.out_proj.bias)
+        self.hln = (f32(h.layernorm.weight), f32(h.layernorm.bias))
+        self.hw1, self.hb1, self.hw2, self.hb2 = bf(h.mlp.fc1.weight), f32(h.mlp.fc1.bias), bf(h.mlp.fc2.weight), f32(h.mlp.fc2.bias)
+        z = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
+        self.pixels = torch.empty(B, 3, self.img, self.img, dtype=torch.float32, device=dev)
+        self.patches, self.x, self.y = z(M, 3 * self.p * self.p), z(M, D), z(M, D)
+        self.qkv, self.attn, self.h = z(M, 3 * D), z(M, D), z(M, self.F)
+        self.kv, self.pool_a, self.pool_r, self.pool_y, self.pool_h = z(M, 2 * D), z(B, D), z(B, D), z(B, D), z(B, self.F)
+        self.embeds = z(B, D)
+        self.seqs = torch.tensor([[b * S, S, b * S, S] for b in range(B)], dtype=torch.int32, device=dev)
+        self.pool_seqs = torch.tensor([[b, 1, b * S, S] for b in range(B)], dtype=torch.int32, device=dev)
+        self.status = ops.new_status(dev)
+        self.graph = None if graph else False
+
+    def _body(self):
+        D, S, B, H, hd, eps = self.D, self.S0, self.B, self.H, self.hd, self.eps
+        L, st = _C.lib(), self.status
+        _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p,
+                                       ops._stream(self.pixels)))
+        ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x)
+        for w in self.layers:
+            ops.layernorm_rows(self.x, *w["ln1"], eps, out=self.y)
+            ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
+            ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
+                          causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
+                          o_strides=(D, hd))
+            ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x)
+            ops.layernorm_rows(self.x, *w["ln2"], eps, out=self.y)
+            ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)
+            ops.gemm(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x)
+        # post-LayerNorm + MAP head: probe attends over the tokens, then LayerNorm + MLP with a residual
+        ops.layernorm_rows(self.x, *self.post, eps, out=self.y)
+        ops.gemm(self.y, self.wkv, st, bias=self.bkv, out=self.kv)
+        ops.attention(self.probe_q, self.kv, self.kv[:, D:], self.pool_a, self.pool_seqs, n_heads=H, group=1, head_dim=hd,
+                      causal=False, max_q_len=1, q_strides=(0, hd), k_strides=(2 * D, hd, 0), v_strides=(2 * D, hd, 0),
+                      o_strides=(D, hd))
+        ops.gemm(self.pool_a, self.who, st, bias=self.bho, out=self.pool_r)
+        ops.layernorm_rows(self.pool_r, *self.hln, eps, out=self.pool_y)
+        ops.gemm(self.pool_y, self.hw1, st, bias=self.hb1, epi=_C.EPI_GELU, out=self.pool_h)
+        ops.gemm(self.pool_h, self.hw2, st, bias=self.hb2, residual=self.pool_r, out=self.embeds)
+
+    @torch.no_grad()
+    def forward(self, inp):
+        """``inp["pixel_values"]``: ``[B, 3, H, W]`` on any device; copied into the engine's buffer, then one graph replay."""
+        if "spatial_shapes" in inp:
+            raise NotImplementedError("variable-resolution (NaFlex) inputs are not built")
+        px = inp["pixel_values"]
+        assert tuple(px.shape) == tuple(self.pixels.shape), f"expected {tuple(self.pixels.shape)}, got {tuple(px.shape)}"
+        self.pixels.copy_(px, non_blocking=True)
+        if self.graph is None:
+            self.status.zero_()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._body()
+            torch.cuda.current_stream().wait_stream(s)
+            ops.check_status(self.status)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._body()
+        if self.graph:
+            self.graph.replay()
+        else:
+            self._body()
+        return self.embeds
+
+    def check(self) -> None:
+        """Synchronise and raise if any GEMM pipeline wait ran out since construction."""
+        ops.check_status(self.status)
+
+    def flops(self, formula: str = "reference") -> float:
+        """FLOPs of one forward.  ``reference``: the reference benchmark's formula (``benchmarks/siglip.py:35``), which
+        leaves out the patch embedding and the MAP head; ``full`` counts them."""
+        B, L, S, D, F = self.B, self.L, self.S0, self.D, self.F
+        ref = B * L * (2 * S * D * (4 * D + 2 * F) + 4 * S * S * D)
+        if formula == "reference":
+            return float(ref)
+        head = 2 * S * D * 2 * D + 4 * S * D + 2 * D * D + 4 * D * F
+        return float(ref + B * (2 * S * D * 3 * self.p * self.p + head))
+
+
+class Siglip2Embedder:
+    """``Siglip2Embedder(model, batch_size=64)``: ``model`` is a Hugging Face SigLIP vision module (or a model that has
+    ``.vision_model``), or a hub id when a checkpoint cache is available.  Attributes as in the reference: ``.processor``
+    (``None`` without a checkpoint), ``.vm``, ``.engine``; ``.embed(pixel_values)`` batches and pads like the reference's
+    ``embed`` (``:715-723``: the last batch repeats its final image)."""
+
+    def __init__(self, model_id="google/siglip2-base-patch16-224", batch_size=64, device="cuda"):
+        self.processor = None
+        if isinstance(model_id, str):
+            from transformers import AutoImageProcessor, AutoModel
+            self.processor = AutoImageProcessor.from_pretrained(model_id)
+            model_id = AutoModel.from_pretrained(model_id, dtype=torch.bfloat16)
+        self.vm = _vision_model(model_id).to(device, torch.bfloat16).eval()
+        self.B, self.device = batch_size, device
+        self.engine = Engine(self.vm, batch_size)
+
+    @torch.no_grad()
+    def embed(self, images):
+        """``images``: fp32 ``[N, 3, H, W]`` pixel values, or PIL images when a processor is loaded."""
+        px = images if torch.is_tensor(images) else self.processor(images=images, return_tensors="pt")["pixel_values"]
+        out = []
+        for k in range(0, len(px), self.B):
+            n = min(self.B, len(px) - k)
+            batch = torch.cat([px[k:k + n], px[k + n - 1:k + n].expand(self.B - n, *px.shape[1:])])
+            out.append(self.engine.forward({"pixel_values": batch})[:n].clone())
+        return torch.cat(out)

@@ -1,0 +1,134 @@
+"""Attention and row-wise kernels of the prefill / SigLIP paths against fp32 torch references (GPU).
+
+Tolerances: one bf16 rounding of the output (2^-8 relative) plus, for attention, the bf16 rounding of the probabilities
+before the PV product: |err| <= 2^-6 |want| + 2^-6 rms(want)."""
+import ctypes as C
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+gpu = pytest.mark.gpu
+
+
+def _check(got, want, what, rel=2.0 ** -6):
+    got, want = got.float(), want.float()
+    tol = rel * want.abs() + 2.0 ** -6 * want.pow(2).mean().sqrt()
+    bad = (got - want).abs() > tol
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} outside tolerance, max err {(got - want).abs().max():.4g}"
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+@gpu
+@pytest.mark.parametrize("B,S", [(1, 196), (3, 196), (2, 77)])
+def test_attention_dense_packed_qkv(B, S):
+    """SigLIP layout: one [B*S, 3*768] matrix holding q | k | v, 12 heads of 64, no mask inside a sequence."""
+    from ittai_b200 import ops
+    H, hd, D = 12, 64, 768
+    qkv = _rand(B * S, 3 * D, seed=1)
+    out = torch.zeros(B * S, D, dtype=torch.bfloat16, device="cuda")
+    seqs = torch.tensor([[b * S, S, b * S, S] for b in range(B)], dtype=torch.int32, device="cuda")
+    ops.attention(qkv, qkv[:, D:], qkv[:, 2 * D:], out, seqs, n_heads=H, group=1, head_dim=hd, causal=False, max_q_len=S,
+                  q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0), o_strides=(D, hd))
+    q, k, v = (qkv[:, i * D:(i + 1) * D].float().view(B, S, H, hd).transpose(1, 2) for i in range(3))
+    want = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B * S, D)
+    _check(out, want, f"dense attention B={B} S={S}")
+
+
+@gpu
+@pytest.mark.parametrize("q_len,prefix", [(300, 0), (64, 0), (130, 70), (1, 500)])
+def test_attention_causal_gqa_cache_layout(q_len, prefix):
+    """Qwen3 layout: q in a [T, 4096] qkv matrix (16 heads of 128), k/v in a cache [B, 8, cap, 128], causal with a prefix."""
+    from ittai_b200 import ops
+    NH, NKV, hd, cap, B = 16, 8, 128, 640, 2
+    kv_len = prefix + q_len
+    qkv = _rand(B * q_len, 4096, seed=2)
+    kc, vc = _rand(B, NKV, cap, hd, seed=3), _rand(B, NKV, cap, hd, seed=4)
+    out = torch.zeros(B * q_len, NH * hd, dtype=torch.bfloat16, device="cuda")
+    seqs = torch.tensor([[b * q_len, q_len, 0, kv_len] for b in range(B)], dtype=torch.int32, device="cuda")
+    ops.attention(qkv, kc, vc, out, seqs, n_heads=NH, group=2, head_dim=hd, causal=True, max_q_len=q_len,
+                  q_strides=(4096, hd), k_strides=(hd, cap * hd, NKV * cap * hd), v_strides=(hd, cap * hd, NKV * cap * hd),
+                  o_strides=(NH * hd, hd))
+    q = qkv[:, :NH * hd].float().view(B, q_len, NH, hd).transpose(1, 2)
+    k = kc[:, :, :kv_len].float().repeat_interleave(2, 1)
+    v = vc[:, :, :kv_len].float().repeat_interleave(2, 1)
+    mask = torch.arange(kv_len, device="cuda")[None, :] <= torch.arange(q_len, device="cuda")[:, None] + prefix
+    want = F.scaled_dot_product_attention(q, k, v, attn_mask=mask).transpose(1, 2).reshape(B * q_len, NH * hd)
+    _check(out, want, f"causal attention q_len={q_len} prefix={prefix}")
+
+
+@gpu
+def test_norm_rows():
+    from ittai_b200 import ops
+    x = _rand(777, 1024, scale=3.0, seed=5)
+    g = _rand(1024, seed=6)
+    xf = x.float()
+    rb = lambda t: t.to(torch.bfloat16).float()
+    want = rb(rb(xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6)) * g.float())
+    got = ops.rmsnorm_rows(x, g, 1e-6)
+    assert (got.float() != want).float().mean() < 1e-3 and (got.float() - want).abs().max() <= 2.0 ** -6 * want.abs().max()
+    x7 = _rand(500, 768, scale=2.0, seed=7)
+    gain, beta = torch.randn(768, device="cuda"), torch.randn(768, device="cuda")
+    _check(ops.layernorm_rows(x7, gain, beta, 1e-6), F.layer_norm(x7.float(), (768,), gain, beta, 1e-6), "layernorm", rel=2.0 ** -7)
+
+
+@gpu
+def test_qk_rope_scatter_matches_oracle(tiny_hf):
+    from ittai_b200 import _C
+    from ittai_b200.qwen3.decoder import rope_table
+    from oracle import qwen3_ref as ref
+    model, dims = tiny_hf
+    T, cap, B = 37, 64, 2
+    qkv = _rand(T, 4096, seed=8)
+    sd = model.state_dict()
+    qn, kn = sd["model.layers.0.self_attn.q_norm.weight"].cuda(), sd["model.layers.0.self_attn.k_norm.weight"].cuda()
+    pos = torch.arange(T, dtype=torch.int32, device="cuda") % 20 + 3
+    seq = (torch.arange(T, device="cuda") >= 20).to(torch.int32)
+    kc = torch.zeros(B, 8, cap, 128, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    rope = rope_table(cap, "cuda")
+    want_in = qkv.clone()
+    _C.check(_C.lib().ittai_qwen3_qk_rope_scatter(qkv.data_ptr(), qn.data_ptr(), kn.data_ptr(), rope.data_ptr(), pos.data_ptr(),
+                                                   seq.data_ptr(), kc.data_ptr(), vc.data_ptr(), T, cap, 1e-6, None))
+    cos, sin = ref.rope_table(cap, dims)
+    cs, sn = cos[pos.cpu().long()][:, None, :], sin[pos.cpu().long()][:, None, :]
+    x = want_in.float().cpu()
+    q = ref.rope(ref.rmsnorm(x[:, :2048].view(T, 16, 128), qn.float().cpu(), 1e-6), cs, sn)
+    k = ref.rope(ref.rmsnorm(x[:, 2048:3072].view(T, 8, 128), kn.float().cpu(), 1e-6), cs, sn)
+    v = x[:, 3072:].view(T, 8, 128)
+    got_q = qkv[:, :2048].float().cpu().view(T, 16, 128)
+    assert (got_q != q).float().mean() < 2e-3 and (got_q - q).abs().max() <= 2.0 ** -6 * q.abs().max()
+    for t in range(T):
+        b, p = int(seq[t]), int(pos[t])
+        assert torch.equal(vc[b, :, p].float().cpu(), v[t])
+        assert (kc[b, :, p].float().cpu() - k[t]).abs().max() <= 2.0 ** -6 * k.abs().max()
+    written = torch.zeros(B, cap, dtype=torch.bool)
+    written[seq.cpu().long(), pos.cpu().long()] = True
+    assert (kc.float().cpu().abs().sum((1, 3)) > 0).eq(written).all(), "a cache row outside (seq, pos) was written"
+
+
+@gpu
+def test_im2col_embed_pool():
+    from ittai_b200 import _C
+    L = _C.lib()
+    px = torch.randn(3, 3, 224, 224, device="cuda")
+    out = torch.empty(3 * 196, 768, dtype=torch.bfloat16, device="cuda")
+    _C.check(L.ittai_siglip_im2col(px.data_ptr(), out.data_ptr(), 3, 224, 224, 16, None))
+    want = px.unfold(2, 16, 16).unfold(3, 16, 16).permute(0, 2, 3, 1, 4, 5).reshape(3 * 196, 768).to(torch.bfloat16)
+    assert torch.equal(out, want)
+    table = _rand(500, 1024, seed=9)
+    ids = torch.tensor([3, 499, 0, 17], dtype=torch.int32, device="cuda")
+    rows = torch.empty(4, 1024, dtype=torch.bfloat16, device="cuda")
+    _C.check(L.ittai_embed_rows(ids.data_ptr(), table.data_ptr(), rows.data_ptr(), 4, 500, None))
+    assert torch.equal(rows, table[ids.long()])
+    gain = _rand(1024, seed=10)
+    pooled = torch.empty(2, 1024, device="cuda")
+    sel = torch.tensor([1, 3], dtype=torch.int32, device="cuda")
+    _C.check(L.ittai_qwen3_final_pool(rows.data_ptr(), sel.data_ptr(), gain.data_ptr(), pooled.data_ptr(), 2, 1e-6, None))
+    x = rows[sel.long()].float()
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * gain.float()
+    assert torch.allclose(pooled, F.normalize(y, dim=-1), atol=1e-5)

@@ -1,0 +1,75 @@
+"""SigLIP ViT-B/16 path: oracle pinned by the golden fixture (CPU), CUDA engine against the oracle (GPU).
+
+Gate (BASELINE north star): pooled-embedding cosine >= 0.9995 against the reference's eager path."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import siglip_hf as hf
+from oracle import siglip_ref as ref
+
+gpu = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def vit():
+    return hf.build_hf(seed=2)
+
+
+def _golden(golden_dir):
+    return torch.load(f"{golden_dir}/siglip_b16.pt", weights_only=True)
+
+
+def test_restatement_matches_golden(vit, golden_dir):
+    g = _golden(golden_dir)
+    px = hf.pixels(4, seed=3)
+    pooled, last = ref.SiglipRef(vit).forward(px)
+    assert F.cosine_similarity(pooled, g["pooled_bf16"].float(), dim=-1).min() >= 0.9995
+    assert F.cosine_similarity(pooled, g["pooled_fp32"].float(), dim=-1).min() >= 0.9995
+    assert F.cosine_similarity(last[0, ::49].flatten(), g["last_hidden_fp32_img0"].float().flatten(), dim=0) >= 0.9995
+
+
+def test_hf_rebuild_reproduces_golden(vit, golden_dir):
+    g = _golden(golden_dir)
+    with torch.no_grad():
+        out = vit(pixel_values=hf.pixels(4, seed=3).to(torch.bfloat16)).pooler_output
+    assert F.cosine_similarity(out.float(), g["pooled_bf16"].float(), dim=-1).min() >= 0.99999
+
+
+@gpu
+@pytest.mark.parametrize("B", [1, 4])
+def test_engine_matches_golden_and_oracle(vit, golden_dir, B):
+    from ittai_b200.siglip.kernel import Engine
+    g = _golden(golden_dir)
+    px = hf.pixels(4, seed=3)[:B]
+    vm = hf.build_hf(seed=2, device="cuda")
+    eng = Engine(vm, B)
+    out = eng.forward({"pixel_values": px}).float().cpu()
+    eng.check()
+    assert F.cosine_similarity(out, g["pooled_bf16"].float()[:B], dim=-1).min() >= 0.9995
+    assert F.cosine_similarity(out, g["pooled_fp32"].float()[:B], dim=-1).min() >= 0.9995
+    want, _ = ref.SiglipRef(vit).forward(px)
+    assert F.cosine_similarity(out, want, dim=-1).min() >= 0.9995
+    assert (out - want).abs().max() <= 0.05 * want.abs().max()
+    # a second call replays the captured graph and returns the same values
+    assert torch.equal(eng.forward({"pixel_values": px}).float().cpu(), out)
+
+
+@gpu
+def test_engine_batch64_against_eager_on_device():
+    """BASELINE config 3 at batch 64: the checker is the eager tower run on the same GPU."""
+    from ittai_b200.siglip.kernel import Siglip2Embedder
+    vm = hf.build_hf(seed=2, device="cuda")
+    px = hf.pixels(64, seed=3)
+    with torch.no_grad():
+        want = vm(pixel_values=px.cuda().to(torch.bfloat16)).pooler_output.float().cpu()
+    emb = Siglip2Embedder(vm, batch_size=64)
+    out = emb.embed(px).float().cpu()
+    emb.engine.check()
+    cos = F.cosine_similarity(out, want, dim=-1)
+    print("siglip B=64 min cos", cos.min().item())
+    assert cos.min() >= 0.9995
+    # ragged tail: 70 images -> one full batch and one padded batch
+    px70 = torch.cat([px, px[:6]])
+    out70 = emb.embed(px70).float().cpu()
+    assert out70.shape == (70, 768) and torch.equal(out70[:64], out) and torch.equal(out70[64:], out[:6])
