@@ -167,7 +167,7 @@ enum {
 };
 
 /* out[M, N] = a[M, K] * w[N, K]^T with fp32 accumulation.  a, w, residual, out are bf16 row-major; bias is fp32.
- * N must be a multiple of 128 and K of 64; leading dimensions of 0 mean "dense".  `status` must be zeroed by the
+ * N must be a multiple of 256 and K of 64; leading dimensions of 0 mean "dense".  `status` must be zeroed by the
  * caller before a sequence of launches and decoded afterwards. */
 typedef struct IttaiGemm {
     int32_t m, n, k, epi;
@@ -208,11 +208,12 @@ int ittai_rmsnorm_rows(const void* x, int ld_x, const void* gain, void* y, int l
  * GEMM by the reference: src/ittai/siglip/kernel.py:284-288,523-525). */
 int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, const void* beta, void* y, int ld_y, int rows, int width,
                          float eps, void* stream);
-/* Qwen3 prefill: per-head RMSNorm + RoPE of q (in place in qkv[T, 4096]) and k, and the scatter of k and v into one layer
- * of the cache ([B, 8, kv_cap, 128]) at (seq[t], pos[t]).  The reference's qkv epilogue: src/ittai/qwen3/base.py:84-109. */
+/* Qwen3 prefill: per-head RMSNorm + RoPE (position pos[t]) of q (in place in qkv[T, 4096]) and k, and the scatter of k
+ * and v into one layer of the cache ([B, 8, kv_cap, 128]) at row slot[t] of sequence seq[t].  The reference's qkv
+ * epilogue: src/ittai/qwen3/base.py:84-109. */
 int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void* kn, const void* rope, const int32_t* pos,
-                                const int32_t* seq, void* kcache_layer, void* vcache_layer, int n_tokens, int kv_cap,
-                                float eps, void* stream);
+                                const int32_t* seq, const int32_t* slot, void* kcache_layer, void* vcache_layer,
+                                int n_tokens, int kv_cap, float eps, void* stream);
 /* fp32 pixels [B, 3, H, W] -> bf16 patch rows [B * (H/p) * (W/p), 3 p p] in (channel, row, col) order
  * (the torch unfold of src/ittai/siglip/kernel.py:633-637). */
 int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, void* stream);

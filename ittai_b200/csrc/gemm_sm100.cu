@@ -4,23 +4,27 @@
 // GEMM epilogues fuse (src/ittai/qwen3/base.py:110-129, src/ittai/siglip/kernel.py:266-333): bias, residual add,
 // GELU-tanh, SwiGLU on interleaved gate/up columns.
 //
-// One CTA computes one 128 x 128 output tile.  Warp 0 (one lane) streams 128 x 64 operand tiles through a ring of
-// shared-memory stages with TMA (128-byte swizzle); warp 1 allocates 128 TMEM columns and (one lane) issues four
-// tcgen05.mma (M128 N128 K16) per stage, releasing the stage with tcgen05.commit; warps 2-5 read the accumulator with
-// tcgen05.ld (each warp its own 32 TMEM lanes = 32 output rows) and run the epilogue.  Every wait is bounded; a wait
-// that runs out sets the status word, all roles fall through to the common exit and TMEM is freed.
+// Persistent kernel, one CTA per SM, looping over 128 x 256 output tiles (tile t = blockIdx.x + i * gridDim.x, N
+// fastest so that the CTAs of a wave share A tiles through L2, the reference's "N-tile outer, M-block inner" grouping:
+// src/ittai/qwen3/engine.py:53-63).  Warp 0 (one lane) streams 128 x 64 A tiles and 256 x 64 W tiles through a ring of
+// shared-memory stages with TMA (128-byte swizzle); warp 1 owns all 512 TMEM columns as two 256-column accumulators
+// and (one lane) issues four tcgen05.mma (M128 N256 K16) per stage, releasing the stage with tcgen05.commit; warps 2-5
+// read a finished accumulator with tcgen05.ld (each warp its own 32 TMEM lanes = 32 output rows) and run the epilogue
+// while the MMA warp already fills the other accumulator.  Every wait is bounded; a wait that runs out raises the
+// abort flag, all roles fall through to the common exit and TMEM is freed.
 #include <cuda.h>
 
 #include "tcgen05.cuh"
 
 namespace ittai {
 
-constexpr int GM = 128, GN = 128, GK = 64;
-constexpr int kGemmStages = 6;
+constexpr int GM = 128, GN = 256, GK = 64;
+constexpr int kGemmStages = 4;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kStageBytesA = GM * GK * 2, kStageBytesB = GN * GK * 2;
 constexpr uint32_t kGemmSmem = kGemmStages * (kStageBytesA + kStageBytesB) + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr uint32_t kGemmSpin = 1u << 24;
+constexpr uint32_t kTmemCols = 512;
 
 struct GemmArgs {
     int M, N, K;
@@ -33,8 +37,66 @@ struct GemmArgs {
     uint32_t* status;        // device status words
 };
 
+// GELU-tanh as the reference writes it (src/ittai/siglip/kernel.py:289-291); the hardware tanh approximation is good
+// to about 2^-11, well inside the bf16 rounding of the result.
 __device__ __forceinline__ float gelu_tanh(float y) {
-    return 0.5f * y * (1.0f + tanhf(0.7978845608028654f * (y + 0.044715f * y * y * y)));
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (y + 0.044715f * y * y * y)));
+    return 0.5f * y * (1.0f + th);
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One 32-column slice of an accumulator row: bias, activation, residual, rounding, 128-bit stores.
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, const uint32_t (&r)[32], int row, int col) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    if (g.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(g.bias + col + i);
+            v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+        }
+    }
+    if (g.epi == ITTAI_EPI_SWIGLU) {
+        // adjacent columns are (gate, up): act = bf16(bf16(silu(bf16 gate)) * bf16 up)
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            const float g0 = bf16r(v[2 * i]), u0 = bf16r(v[2 * i + 1]);
+            const float g1 = bf16r(v[2 * i + 2]), u1 = bf16r(v[2 * i + 3]);
+            o[i / 2] = pack_bf16x2(bf16r(g0 / (1.0f + expf(-g0))) * u0, bf16r(g1 / (1.0f + expf(-g1))) * u1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col / 2);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        return;
+    }
+    if (g.epi == ITTAI_EPI_GELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(bf16r(v[i]));   // the Linear output is rounded before the activation
+    }
+    if (g.residual != nullptr) {
+        // out = bf16(residual + bf16(acc [+ bias])): the module output is rounded before the add
+        const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.ld_res + col);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 rr = rs[i];
+            const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[i * 8 + 2 * j] = bf_lo(w[j]) + bf16r(v[i * 8 + 2 * j]);
+                v[i * 8 + 2 * j + 1] = bf_hi(w[j]) + bf16r(v[i * 8 + 2 * j + 1]);
+            }
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        dst[i] = make_uint4(pack_bf16x2(v[i * 8], v[i * 8 + 1]), pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]),
+                            pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]), pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]));
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -42,28 +104,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     extern __shared__ __align__(1024) unsigned char gsm_raw[];
     unsigned char* gsm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sa = gsm;                                         // [stages][128 rows][128 B]
-    unsigned char* sb = gsm + kGemmStages * kStageBytesA;
+    unsigned char* sb = gsm + kGemmStages * kStageBytesA;            // [stages][256 rows][128 B]
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(sb + kGemmStages * kStageBytesB);
-    unsigned long long* full = bars;                                 // [stages]
-    unsigned long long* empty = bars + kGemmStages;                  // [stages]
-    unsigned long long* acc_full = bars + 2 * kGemmStages;           // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kGemmStages + 1);
+    unsigned long long* full = bars;                                 // [stages]  TMA -> MMA
+    unsigned long long* empty = bars + kGemmStages;                  // [stages]  MMA -> TMA
+    unsigned long long* acc_full = bars + 2 * kGemmStages;           // [2]       MMA -> epilogue
+    unsigned long long* acc_empty = bars + 2 * kGemmStages + 2;      // [2]       epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kGemmStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = g.N / GN;
-    const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+    const int tiles_n = g.N / GN, tiles_m = (g.M + GM - 1) / GM, n_tiles = tiles_m * tiles_n;
     const int n_kb = g.K / GK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
     }
-    if (warp == 1) tmem_alloc(tmem_slot, GN);          // 128 fp32 columns x 128 lanes
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -71,99 +133,76 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- TMA producer
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % kGemmStages, use = kb / kGemmStages;
-                if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1, kGemmSpin)) { *abort_flag = 1; break; }
-                if (*abort_flag) break;
-                mbar_expect_tx(&full[s], kStageBytesA + kStageBytesB);
-                tma_load_2d(sa + s * kStageBytesA, &tm_a, kb * GK, tile_m * GM, &full[s]);
-                tma_load_2d(sb + s * kStageBytesB, &tm_b, kb * GK, tile_n * GN, &full[s]);
+            // ---- TMA producer: one running k-block counter across all of this CTA's tiles
+            int it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
+                const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kGemmStages, use = it / kGemmStages;
+                    if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1, kGemmSpin)) { *abort_flag = 1; break; }
+                    if (*abort_flag) break;
+                    mbar_expect_tx(&full[s], kStageBytesA + kStageBytesB);
+                    tma_load_2d(sa + s * kStageBytesA, &tm_a, kb * GK, tile_m * GM, &full[s]);
+                    tma_load_2d(sb + s * kStageBytesB, &tm_b, kb * GK, tile_n * GN, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer
             constexpr uint32_t idesc = umma_idesc_bf16(GM, GN);
+            int it = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < n_kb && ok; ++kb) {
-                const int s = kb % kGemmStages, use = kb / kGemmStages;
-                ok = mbar_wait_bounded(&full[s], use & 1, kGemmSpin) && !*abort_flag;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1, round = local >> 1;
+                // the epilogue must have drained this accumulator (passes at once on its first use)
+                ok = (round == 0 || mbar_wait_bounded(&acc_empty[buf], (round - 1) & 1, kGemmSpin)) && !*abort_flag;
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * kStageBytesB);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * GN);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kGemmStages, use = it / kGemmStages;
+                    ok = mbar_wait_bounded(&full[s], use & 1, kGemmSpin) && !*abort_flag;
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * kStageBytesB);
 #pragma unroll
-                for (int k = 0; k < GK / 16; ++k)      // 16 bf16 = 32 bytes = 2 descriptor address units per step
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);                // the stage is free once these MMAs have read it
+                    for (int k = 0; k < GK / 16; ++k)      // 16 bf16 = 32 bytes = 2 descriptor address units per step
+                        umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);                // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);               // accumulator complete
             }
             if (!ok) *abort_flag = 1;
-            umma_commit(acc_full);                     // accumulator complete (or as far as it got)
         }
     } else {
         // ---- epilogue: warp w owns TMEM lanes 32*(w%4)..+31 = rows of the tile
-        const bool ok = mbar_wait_bounded(acc_full, 0, kGemmSpin);
-        tc_fence_after();
-        if (!ok) *abort_flag = 1;
         const int q = warp & 3;
-        const int row = tile_m * GM + q * 32 + lane;
-        if (ok && !*abort_flag) {
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1, round = local >> 1;
+            const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
+            bool ok = true;
+            {   // bounded wait that also gives up when another role aborted
+                uint32_t spins = 0;
+                while (!mbar_try_wait(&acc_full[buf], round & 1)) {
+                    if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kGemmSpin)) { ok = false; break; }
+                }
+            }
+            if (!ok) { *abort_flag = 1; break; }
+            tc_fence_after();
+            const int row = tile_m * GM + q * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < GN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + c0), r);
                 tmem_ld_wait();
-                if (row < g.M) {
-                    const int col = tile_n * GN + c0;
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                    if (g.bias != nullptr) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float4 b4 = *reinterpret_cast<const float4*>(g.bias + col + i);
-                            v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
-                        }
-                    }
-                    if (g.epi == ITTAI_EPI_SWIGLU) {
-                        // adjacent columns are (gate, up): act = bf16(bf16(silu(bf16 gate)) * bf16 up)
-                        uint32_t o[8];
-#pragma unroll
-                        for (int i = 0; i < 16; i += 2) {
-                            const float g0 = bf16r(v[2 * i]), u0 = bf16r(v[2 * i + 1]);
-                            const float g1 = bf16r(v[2 * i + 2]), u1 = bf16r(v[2 * i + 3]);
-                            o[i / 2] = pack_bf16x2(bf16r(g0 / (1.0f + expf(-g0))) * u0, bf16r(g1 / (1.0f + expf(-g1))) * u1);
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col / 2);
-                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-                    } else {
-                        if (g.epi == ITTAI_EPI_GELU) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(bf16r(v[i]));   // the Linear output is rounded before the activation
-                        }
-                        if (g.residual != nullptr) {
-                            // out = bf16(residual + bf16(acc [+ bias])): the module output is rounded before the add
-                            const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.ld_res + col);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const uint4 rr = rs[i];
-                                const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    v[i * 8 + 2 * j] = bf_lo(w[j]) + bf16r(v[i * 8 + 2 * j]);
-                                    v[i * 8 + 2 * j + 1] = bf_hi(w[j]) + bf16r(v[i * 8 + 2 * j + 1]);
-                                }
-                            }
-                        }
-                        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            dst[i] = make_uint4(pack_bf16x2(v[i * 8], v[i * 8 + 1]), pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]),
-                                                pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]), pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]));
-                    }
-                }
+                if (row < g.M) epilogue_chunk(g, r, row, tile_n * GN + c0);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
@@ -177,7 +216,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         __syncthreads();
     }
-    if (warp == 1) tmem_dealloc(tmem_base, GN);
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ---- host side ---------------------------------------------------------------------------------------------
@@ -200,13 +239,13 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tensor map over a row-major bf16 matrix [rows, cols] with leading dimension ld: boxes of 128 rows x 64 columns.
-static int make_tmap(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
+// Tensor map over a row-major bf16 matrix [rows, cols] with leading dimension ld: boxes of box_rows rows x 64 columns.
+static int make_tmap(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return ITTAI_E_CUDA; }
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)GK, (cuuint32_t)GM};
+    const cuuint32_t box[2] = {(cuuint32_t)GK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -232,16 +271,18 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
         return ITTAI_E_ARG;
     }
     CUtensorMap tm_a, tm_b;
-    int rc = make_tmap(&tm_a, a->a, a->m, a->k, ld_a);
+    int rc = make_tmap(&tm_a, a->a, a->m, a->k, ld_a, GM);
     if (rc != ITTAI_OK) return rc;
-    rc = make_tmap(&tm_b, a->w, a->n, a->k, ld_w);
+    rc = make_tmap(&tm_b, a->w, a->n, a->k, ld_w, GN);
     if (rc != ITTAI_OK) return rc;
-    static thread_local int attr_dev = -1;
+    static thread_local int attr_dev = -1, n_sms = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
+        e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
         attr_dev = dev;
     }
     GemmArgs g;
@@ -253,7 +294,7 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.ld_out = ld_out;
     g.status = a->status;
     const int tiles = ((a->m + GM - 1) / GM) * (a->n / GN);
-    gemm_bf16_kernel<<<tiles, kGemmThreads, kGemmSmem, st>>>(tm_a, tm_b, g);
+    gemm_bf16_kernel<<<tiles < n_sms ? tiles : n_sms, kGemmThreads, kGemmSmem, st>>>(tm_a, tm_b, g);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch gemm_bf16_kernel");
     return ITTAI_OK;

@@ -84,11 +84,13 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_rows_kernel(const bf16*
 }
 
 // Qwen3 prefill: per token and head, RMSNorm over the 128 head dims + half-split RoPE in bf16 steps (the arithmetic of
-// the decode phase), Q rotated in place in the qkv matrix, K and V written to the cache rows of (sequence, position).
+// the decode phase), Q rotated in place in the qkv matrix, K and V written to cache row slot[t] of sequence seq[t]
+// (the rotary position pos[t] and the cache row differ when sequences are packed into one cache).
 // One warp per (token, head): heads 0..15 = q, 16..23 = k, 24..31 = v.
 __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ qn,
                                                                         const bf16* __restrict__ kn, const bf16* __restrict__ rope,
                                                                         const int* __restrict__ pos, const int* __restrict__ seq,
+                                                                        const int* __restrict__ slot,
                                                                         bf16* __restrict__ kc, bf16* __restrict__ vc, int n_tokens,
                                                                         int kv_cap, float eps) {
     constexpr int HD = ITTAI_Q3_HD, NKV = ITTAI_Q3_NKV, DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV;
@@ -96,12 +98,12 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
     const int t = gw >> 5, head = gw & 31;
     if (t >= n_tokens) return;
     bf16* row = qkv + (size_t)t * DQKV + head * HD;
-    const int p = pos[t], b = seq[t];
+    const int p = pos[t], b = seq[t], sl = slot[t];   // rotary position, cache sequence, cache row
     // elements 2*lane, 2*lane+1 and their rotation partners 64 + the same
     const uint32_t ua = *reinterpret_cast<const uint32_t*>(row + 2 * lane), ub = *reinterpret_cast<const uint32_t*>(row + HD / 2 + 2 * lane);
     if (head >= 24) {
         const int g = head - 24;
-        bf16* dst = vc + (((size_t)b * NKV + g) * kv_cap + p) * HD;
+        bf16* dst = vc + (((size_t)b * NKV + g) * kv_cap + sl) * HD;
         *reinterpret_cast<uint32_t*>(dst + 2 * lane) = ua;
         *reinterpret_cast<uint32_t*>(dst + HD / 2 + 2 * lane) = ub;
         return;
@@ -123,7 +125,7 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
         lo[j] = bf16r(bf16r(x[j] * cs) + bf16r(-x[j + 2] * sn));
         hi[j] = bf16r(bf16r(x[j + 2] * cs) + bf16r(x[j] * sn));
     }
-    bf16* dst = is_k ? kc + (((size_t)b * NKV + (head - 16)) * kv_cap + p) * HD : row;
+    bf16* dst = is_k ? kc + (((size_t)b * NKV + (head - 16)) * kv_cap + sl) * HD : row;
     *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16x2(lo[0], lo[1]);
     *reinterpret_cast<uint32_t*>(dst + HD / 2 + 2 * lane) = pack_bf16x2(hi[0], hi[1]);
     (void)DQ; (void)DKV;
@@ -208,11 +210,11 @@ extern "C" int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, c
 }
 
 extern "C" int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void* kn, const void* rope, const int32_t* pos,
-                                           const int32_t* seq, void* kcache_layer, void* vcache_layer, int n_tokens, int kv_cap,
-                                           float eps, void* stream) {
-    if (!qkv || !qn || !kn || !rope || !pos || !seq || !kcache_layer || !vcache_layer || n_tokens < 1) { set_error("qk_rope_scatter: bad argument"); return ITTAI_E_ARG; }
+                                           const int32_t* seq, const int32_t* slot, void* kcache_layer, void* vcache_layer,
+                                           int n_tokens, int kv_cap, float eps, void* stream) {
+    if (!qkv || !qn || !kn || !rope || !pos || !seq || !slot || !kcache_layer || !vcache_layer || n_tokens < 1) { set_error("qk_rope_scatter: bad argument"); return ITTAI_E_ARG; }
     qk_rope_scatter_kernel<<<row_grid((long long)n_tokens * 32), kRowThreads, 0, (cudaStream_t)stream>>>(
-        (bf16*)qkv, (const bf16*)qn, (const bf16*)kn, (const bf16*)rope, pos, seq, (bf16*)kcache_layer, (bf16*)vcache_layer, n_tokens, kv_cap, eps);
+        (bf16*)qkv, (const bf16*)qn, (const bf16*)kn, (const bf16*)rope, pos, seq, slot, (bf16*)kcache_layer, (bf16*)vcache_layer, n_tokens, kv_cap, eps);
     return launched("qk_rope_scatter_kernel");
 }
 

@@ -25,3 +25,7 @@ def decode_bytes_per_token(kv_len: int, n_layers: int = L, vocab: int = VOCAB) -
     weights = n_layers * layer + 2 * vocab * D + gains
     kv_row = n_layers * 2 * NKV * HD * 2
     return weights + kv_row * kv_len + kv_row + 2 * D
+
+# names the reference also exports (reference ``src/ittai/qwen3/config.py:8-14``); the op ids double as phase ids here
+OP_QKV, OP_OPROJ, OP_GU, OP_DOWN, OP_EMB, OP_ATTN, OP_FINAL = range(7)
+BM, QB = 128, 64          # rows per GEMM tile / per attention query block

@@ -100,6 +100,7 @@ class Qwen3Decoder:
         self.lengths = [0] * self.B          # host mirror of `pos`, for capacity checks without a device read
         self._keep = None
         self._phase_clk = None
+        self._core = None                    # dense prefill buffers, created at the first long prompt
 
     # ---- plumbing -------------------------------------------------------------------------------
     def _params(self, n_steps, n_forced, forced, out_ids, step_ns, write_logits=True) -> _C.Qwen3Decode:
@@ -145,18 +146,50 @@ class Qwen3Decoder:
 
     # ---- public API -----------------------------------------------------------------------------
     @torch.no_grad()
-    def prefill(self, ids) -> torch.Tensor:
+    def prefill(self, ids, tensor_cores: bool | None = None) -> torch.Tensor:
         """Feed prompts ``ids`` ([B, T] ints, equal lengths) into the cache; returns the first greedy id per sequence.
 
-        The prompt is fed token by token through the decode kernel (ids forced, lm_head only on the last one).
+        Long prompts go through the tensor-core prefill (tcgen05 GEMMs + flash attention over all tokens at once) for
+        every token but the last; the last token, or a short prompt as a whole, is fed through the decode kernel with
+        its ids forced (lm_head only on the final one), which also yields the logits and the first generated id.
+        ``tensor_cores`` forces one path (default: tensor cores from 32 prompt tokens on).
         """
         ids = torch.as_tensor(ids, dtype=torch.int32)
         if ids.dim() == 1:
             ids = ids[None]
         assert ids.shape[0] == self.B, "one prompt per sequence of the batch"
+        T = ids.shape[1]
+        if tensor_cores is None:
+            tensor_cores = T >= 32
+        if tensor_cores and T > 1:
+            self._prefill_dense(ids[:, :T - 1])
+            ids = ids[:, T - 1:]
         forced = ids.t().contiguous().to(self.dev, non_blocking=True)       # [T, B]
         out, _ = self._launch(forced.shape[0], forced=forced)
         return out[-1]
+
+    def _prefill_dense(self, ids: torch.Tensor) -> None:
+        """Append ``ids`` ([B, n]) to every sequence's cache with the dense prefill kernels."""
+        from .engine import PrefillCore
+        B, n = ids.shape
+        if max(self.lengths) + n > self.cap:
+            raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths)} cached + {n} prompt tokens")
+        if self._core is None or self._core.M < B * n:
+            self._core = PrefillCore(self.w, self.L, max(B * n, 256), self.dev)
+        i32 = lambda x: torch.as_tensor(x, dtype=torch.int32).to(self.dev, non_blocking=True)
+        base = torch.tensor(self.lengths, dtype=torch.int32)
+        pos = (base[:, None] + torch.arange(n, dtype=torch.int32)[None, :]).reshape(-1)
+        seq = torch.arange(B, dtype=torch.int32)[:, None].expand(B, n).reshape(-1)
+        seqs = torch.tensor([[b * n, n, 0, self.lengths[b] + n] for b in range(B)], dtype=torch.int32)
+        pos_d = i32(pos)
+        cap = self.cap
+        self._core.status.zero_()
+        self._core.run(B * n, i32(ids.reshape(-1)), pos_d, i32(seq), pos_d, i32(seqs), n, self.rope,
+                       lambda l: (self.kcache[l], self.vcache[l]), cap, (HD, cap * HD, NKV * cap * HD))
+        self.pos += n
+        self.lengths = [x + n for x in self.lengths]
+        from .. import ops
+        ops.check_status(self._core.status)
 
     @torch.no_grad()
     def decode(self, n_steps: int, timed: bool = False, check: bool = True):

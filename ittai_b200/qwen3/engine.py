@@ -1,0 +1,155 @@
+"""Qwen3-0.6B prefill on the tensor-core kernels, behind the reference's ``Engine`` surface
+(reference ``src/ittai/qwen3/engine.py:13-187``).
+
+``Engine.forward(input_ids)`` packs variable-length sequences into one activation matrix, runs 28 layers of
+RMSNorm -> QKV GEMM -> QK-norm + RoPE -> causal GQA attention -> O-proj + residual -> RMSNorm -> gate/up GEMM with
+SwiGLU -> down-proj + residual, and returns the L2-normalised final-norm of every sequence's last token, the
+embedding head of the reference (``src/ittai/qwen3/base.py:131-145``).  ``PrefillCore`` is the layer loop itself; the
+decoder reuses it to fill its KV cache from a prompt.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from .. import _C, ops
+from .config import BM, D, DQ, DQKV, EPS, FF, HD, NH, NKV, QB
+from .decoder import _strip, pack_weights, rope_table
+
+
+def rope_perm(n_heads):
+    """Row permutation that makes half-split RoPE pairs adjacent (reference ``src/ittai/qwen3/engine.py:13-14``).
+
+    Kept for callers that import it; this build stores Q/K rows in the eager order and rotates (i, i + 64) directly."""
+    return np.concatenate([[hh * HD + i, hh * HD + i + HD // 2] for hh in range(n_heads) for i in range(HD // 2)])
+
+
+def build_tasks(seqlens, *unused):
+    """Host description of one packed forward: per-token positions, sequence ids and cache rows, and the per-sequence
+    (first row, rows, first key row, key rows) records the attention kernel walks.
+
+    The reference's ``build_tasks`` (``src/ittai/qwen3/engine.py:17-84``) emits a flat task list with dependency flags
+    for its single persistent kernel; here every phase is its own launch inside one CUDA graph, so the "task list" is
+    just the packing metadata.  Extra positional arguments of the reference's signature are accepted and ignored.
+    Returns (pos, seq, slot, seqs, T) as int32 numpy arrays."""
+    seqlens = [int(x) for x in seqlens]
+    cu = np.concatenate([[0], np.cumsum(seqlens)]).astype(np.int64)
+    T = int(cu[-1])
+    pos = np.concatenate([np.arange(n) for n in seqlens]).astype(np.int32) if T else np.zeros(0, np.int32)
+    seq = np.zeros(T, np.int32)                       # one packed key/value store: every token lives in "sequence 0"
+    slot = np.arange(T, dtype=np.int32)
+    seqs = np.array([[cu[s], seqlens[s], cu[s], seqlens[s]] for s in range(len(seqlens))], dtype=np.int32).reshape(-1, 4)
+    return pos, seq, slot, seqs, T
+
+
+class PrefillCore:
+    """The 28-layer loop over a packed ``[T, 1024]`` activation matrix.  Owns the activation buffers (torch tensors, as
+    the reference's Engine owns its buffers: ``src/ittai/qwen3/engine.py:123-134``); weights and the key/value store are
+    borrowed."""
+
+    def __init__(self, w: dict, n_layers: int, max_tokens: int, device):
+        self.w, self.L, self.M, self.dev = w, n_layers, max_tokens, device
+        z = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=device)
+        self.h, self.xn, self.qkv, self.attn, self.act = z(max_tokens, D), z(max_tokens, D), z(max_tokens, DQKV), z(max_tokens, DQ), z(max_tokens, FF)
+        self.status = ops.new_status(device)
+
+    def run(self, T, tokens, pos, seq, slot, seqs, max_q_len, rope, kv_layer, kv_cap, k_strides):
+        """``tokens/pos/seq/slot``: int32 device ``[T]``; ``seqs``: int32 device ``[n, 4]``; ``kv_layer(l)`` returns the
+        (K, V) tensors of layer ``l`` laid out ``[B, 8, kv_cap, 128]``; ``k_strides`` = (row, head, seq) in elements."""
+        L, st, w = _C.lib(), self.status, self.w
+        h, xn, qkv, attn, act = self.h[:T], self.xn[:T], self.qkv[:T], self.attn[:T], self.act[:T]
+        s = ops._stream(h)
+        _C.check(L.ittai_embed_rows(tokens.data_ptr(), w["embed"].data_ptr(), h.data_ptr(), T, w["embed"].shape[0], s))
+        for l in range(self.L):
+            kc, vc = kv_layer(l)
+            ops.rmsnorm_rows(h, w["ln1"][l], EPS, out=xn)
+            ops.gemm(xn, w["wqkv"][l], st, out=qkv)
+            _C.check(L.ittai_qwen3_qk_rope_scatter(qkv.data_ptr(), w["qn"][l].data_ptr(), w["kn"][l].data_ptr(), rope.data_ptr(),
+                                                   pos.data_ptr(), seq.data_ptr(), slot.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                   T, kv_cap, EPS, s))
+            ops.attention(qkv, kc, vc, attn, seqs, n_heads=NH, group=NH // NKV, head_dim=HD, causal=True, max_q_len=max_q_len,
+                          q_strides=(DQKV, HD), k_strides=k_strides, v_strides=k_strides, o_strides=(DQ, HD))
+            ops.gemm(attn, w["wo"][l], st, residual=h, out=h)
+            ops.rmsnorm_rows(h, w["ln2"][l], EPS, out=xn)
+            ops.gemm(xn, w["wgu"][l], st, epi=_C.EPI_SWIGLU, out=act)
+            ops.gemm(act, w["wd"][l], st, residual=h, out=h)
+        return h
+
+
+class Engine:
+    """``Engine(sd, max_tokens, max_seqs, ...)`` with ``forward(input_ids: list[list[int]]) -> fp32 [B, 1024]``, a view of
+    a persistent buffer (callers clone, as with the reference: ``src/ittai/qwen3/model.py:88``).  The tuning arguments
+    of the reference (``arch, tile_n, stages, kv_block, group_m, warps``) are accepted and ignored."""
+
+    @torch.no_grad()
+    def __init__(self, sd, max_tokens, max_seqs, arch=None, tile_n=None, stages=None, kv_block=None, group_m=None, warps=8,
+                 device="cuda", graph=True):
+        sd = _strip(sd if isinstance(sd, dict) else sd.state_dict())
+        self.dev = torch.device(device)
+        self.M, self.Bmax = (max_tokens + BM - 1) // BM * BM, max_seqs
+        self.L = 1 + max(int(k.split(".")[1]) for k in sd if k.startswith("layers."))
+        self.w = pack_weights(sd, self.L, self.dev)
+        self.embed, self.fin_w = self.w["embed"], self.w["fin_w"]
+        self.rope = rope_table(self.M, self.dev)
+        self.core = PrefillCore(self.w, self.L, self.M, self.dev)
+        z = lambda *s, dt: torch.zeros(*s, dtype=dt, device=self.dev)
+        # one packed key/value store reused by every layer: the embedding pass keeps no cache
+        self.kbuf, self.vbuf = z(1, NKV, self.M, HD, dt=torch.bfloat16), z(1, NKV, self.M, HD, dt=torch.bfloat16)
+        self.tokens, self.pos, self.seq, self.slot = (z(self.M, dt=torch.int32) for _ in range(4))
+        self.seqs, self.last = z(max_seqs, 4, dt=torch.int32), z(max_seqs, dt=torch.int32)
+        self.out = z(max_seqs, D, dt=torch.float32)
+        self.use_graph, self._graphs, self._meta = graph, {}, {}
+
+    def _tasks(self, seqlens):
+        """Packing metadata, cached per tuple of lengths like the reference's task lists (``engine.py:144-151``)."""
+        key = tuple(seqlens)
+        if key not in self._meta:
+            pos, seq, slot, seqs, T = build_tasks(seqlens)
+            dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
+            self._meta[key] = (dev(pos), dev(seq), dev(slot), dev(seqs), dev(seqs[:, 0] + seqs[:, 1] - 1), T)
+        return self._meta[key]
+
+    def _body(self, T, B, max_len):
+        kv = lambda l: (self.kbuf, self.vbuf)
+        h = self.core.run(T, self.tokens, self.pos, self.seq, self.slot, self.seqs[:B], max_len, self.rope, kv, self.M,
+                          (HD, self.M * HD, 0))
+        _C.check(_C.lib().ittai_qwen3_final_pool(h.data_ptr(), self.last.data_ptr(), self.fin_w.data_ptr(), self.out.data_ptr(), B, EPS,
+                                                 ops._stream(h)))
+
+    @torch.no_grad()
+    def forward(self, input_ids):
+        seqlens = [len(x) for x in input_ids]
+        T, B = sum(seqlens), len(seqlens)
+        assert T <= self.M and B <= self.Bmax and min(seqlens) > 0
+        pos, seq, slot, seqs, last, _ = self._tasks(seqlens)
+        self.tokens[:T].copy_(torch.tensor([t for s in input_ids for t in s], dtype=torch.int32), non_blocking=True)
+        self.pos[:T].copy_(pos, non_blocking=True)
+        self.seq[:T].copy_(seq, non_blocking=True)
+        self.slot[:T].copy_(slot, non_blocking=True)
+        self.seqs[:B].copy_(seqs, non_blocking=True)
+        self.last[:B].copy_(last, non_blocking=True)
+        key = tuple(seqlens)
+        if not self.use_graph:
+            self._body(T, B, max(seqlens))
+        else:
+            if key not in self._graphs:
+                if len(self._graphs) >= 8:
+                    self._graphs.pop(next(iter(self._graphs)))
+                self.core.status.zero_()
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    self._body(T, B, max(seqlens))
+                torch.cuda.current_stream().wait_stream(s)
+                ops.check_status(self.core.status)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._body(T, B, max(seqlens))
+                self._graphs[key] = g
+            self._graphs[key].replay()
+        return self.out[:B]
+
+    def check(self) -> None:
+        ops.check_status(self.core.status)

@@ -1,0 +1,64 @@
+"""``Qwen3Embedder``: the reference's user-facing wrapper (reference ``src/ittai/qwen3/model.py:13-90``) over the B200 engine.
+
+Differences forced by running offline: the first argument may be a Hugging Face Qwen3 module (or its state dict) instead
+of a hub id, ``embed`` also takes ready-made token-id lists, and there is no autotune pass (one sm_100a kernel set, no
+configuration grid); the reference's validation gate (minimum cosine > 0.999 against the eager model,
+``model.py:63-68``) is available as ``validate``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .engine import Engine
+
+
+class Qwen3Embedder:
+    def __init__(self, model_id="Qwen/Qwen3-Embedding-0.6B", max_tokens=8192, max_seqs=256, device="cuda"):
+        self.tok = None
+        if isinstance(model_id, str):
+            from transformers import AutoModel, AutoTokenizer
+            self.tok = AutoTokenizer.from_pretrained(model_id, padding_side="left")
+            self.model = AutoModel.from_pretrained(model_id, dtype=torch.bfloat16, device_map=device).eval()
+        else:
+            self.model = model_id
+        self.sd = self.model if isinstance(self.model, dict) else self.model.state_dict()
+        self.max_tokens, self.max_seqs, self.device, self.model_id = max_tokens, max_seqs, device, model_id
+        self.engine = Engine(self.sd, max_tokens, max_seqs, device=device)
+
+    def _ids(self, texts, max_length):
+        if len(texts) and not isinstance(texts[0], str):
+            return [list(map(int, t))[:max_length] for t in texts]
+        if self.tok is None:
+            raise RuntimeError("no tokenizer loaded: pass lists of token ids")
+        return [self.tok(t, truncation=True, max_length=max_length)["input_ids"] for t in texts]
+
+    @torch.no_grad()
+    def embed(self, texts, max_length=2048):
+        """Greedy packing under ``max_tokens`` / ``max_seqs`` exactly as the reference batches (``model.py:79-90``)."""
+        ids = self._ids(texts, max_length)
+        out, k = [], 0
+        while k < len(ids):
+            n, tot = 0, 0
+            while k + n < len(ids) and n < self.max_seqs and tot + len(ids[k + n]) <= self.max_tokens:
+                tot += len(ids[k + n]); n += 1
+            assert n > 0, "sequence longer than max_tokens"
+            out.append(self.engine.forward(ids[k: k + n]).clone())
+            k += n
+        return torch.cat(out)
+
+    @torch.no_grad()
+    def validate(self, ids, threshold=0.999):
+        """Minimum cosine of the engine's embeddings against the eager module's last-token pooling; raises below ``threshold``."""
+        if isinstance(self.model, dict):
+            raise RuntimeError("validation needs the eager module, not a state dict")
+        dev = next(self.model.parameters()).device
+        body = self.model.model if hasattr(self.model, "lm_head") else self.model
+        ref = []
+        for s in ids:
+            hs = body(input_ids=torch.tensor([s], device=dev)).last_hidden_state
+            ref.append(F.normalize(hs[0, -1].float(), dim=-1))
+        cos = F.cosine_similarity(self.embed(ids).to(dev), torch.stack(ref), dim=-1).min().item()
+        if cos <= threshold:
+            raise RuntimeError(f"engine output fails validation: min cosine {cos:.5f} <= {threshold}")
+        return cos

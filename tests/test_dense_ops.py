@@ -93,7 +93,7 @@ def test_qk_rope_scatter_matches_oracle(tiny_hf):
     rope = rope_table(cap, "cuda")
     want_in = qkv.clone()
     _C.check(_C.lib().ittai_qwen3_qk_rope_scatter(qkv.data_ptr(), qn.data_ptr(), kn.data_ptr(), rope.data_ptr(), pos.data_ptr(),
-                                                   seq.data_ptr(), kc.data_ptr(), vc.data_ptr(), T, cap, 1e-6, None))
+                                                   seq.data_ptr(), pos.data_ptr(), kc.data_ptr(), vc.data_ptr(), T, cap, 1e-6, None))
     cos, sin = ref.rope_table(cap, dims)
     cs, sn = cos[pos.cpu().long()][:, None, :], sin[pos.cpu().long()][:, None, :]
     x = want_in.float().cpu()

@@ -22,7 +22,7 @@ def _rand(*shape, scale=1.0, seed=0):
 
 
 @gpu
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 128, 512), (200, 256, 768), (1000, 2304, 768), (4096, 1024, 3072)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (1, 256, 512), (64, 768, 768), (200, 256, 768), (1000, 2304, 768), (4096, 1024, 3072), (12544, 768, 3072)])
 def test_gemm_plain(m, n, k):
     from ittai_b200 import ops
     a, w = _rand(m, k, seed=1), _rand(n, k, scale=0.05, seed=2)
@@ -36,7 +36,7 @@ def test_gemm_plain(m, n, k):
 def test_gemm_row_identity():
     """A = rows of the identity picks out columns of W: catches a wrong swizzle or K-step in the operand descriptors."""
     from ittai_b200 import ops
-    k, n = 256, 128
+    k, n = 256, 256
     a = torch.eye(k, device="cuda", dtype=torch.bfloat16)
     w = _rand(n, k, seed=3)
     st = ops.new_status("cuda")
@@ -69,14 +69,14 @@ def test_gemm_bias_gelu_residual_swiglu():
 def test_gemm_strided_views():
     """Operands and output as column slices of wider buffers (leading dimension > width)."""
     from ittai_b200 import ops
-    big_a, big_w = _rand(256, 1024, seed=7), _rand(384, 1024, scale=0.05, seed=8)
+    big_a, big_w = _rand(256, 1024, seed=7), _rand(512, 1024, scale=0.05, seed=8)
     a, w = big_a[:, 256:768], big_w[:, 512:1024]
-    out_big = torch.zeros(256, 1024, dtype=torch.bfloat16, device="cuda")
+    out_big = torch.zeros(256, 1024, dtype=torch.bfloat16, device="cuda")  # columns 128..640 receive the product
     st = ops.new_status("cuda")
-    ops.gemm(a, w, st, out=out_big[:, 128:512])
+    ops.gemm(a, w, st, out=out_big[:, 128:640])
     ops.check_status(st)
-    _check(out_big[:, 128:512], a.float() @ w.float().t(), "strided")
-    assert (out_big[:, :128] == 0).all() and (out_big[:, 512:] == 0).all()
+    _check(out_big[:, 128:640], a.float() @ w.float().t(), "strided")
+    assert (out_big[:, :128] == 0).all() and (out_big[:, 640:] == 0).all()
 
 
 def test_gemm_argument_errors():
