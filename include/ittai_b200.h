@@ -151,6 +151,18 @@ int ittai_qwen3_decode_workspace_bytes(int batch, size_t* bytes);
  * engine.py:153-155 (`_graph_body`) for the decode loop the reference does not have. */
 int ittai_qwen3_decode_launch(const IttaiQwen3Decode* p, void* stream);
 
+/* The same launch for callers that cannot allocate device memory at call time (a process whose GPU memory was all handed
+ * to a pool at start-up, a host runtime without a device allocator, a loop that cannot afford cudaMalloc's device-wide
+ * synchronisation).  p->workspace is ignored: the scratch is a static device array inside the library, at most
+ * ITTAI_STATIC_DECODE_MAX_BATCH sequences (about 2.3 MB, held by every GPU that loads the library until the process
+ * exits); a larger p->batch is rejected with ITTAI_E_ARG.  The call itself allocates nothing (no cudaMalloc / cudaFree,
+ * no allocating library routine).  Its first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress): make that first call outside any stream capture.  All calls share the one array and it keeps
+ * the previous call's contents; the launch clears the words that must start at zero, and two calls whose kernels overlap
+ * on the GPU (different streams, or different threads) race on it.  No counterpart in the reference. */
+#define ITTAI_STATIC_DECODE_MAX_BATCH 2
+int ittai_qwen3_decode_launch_static(const IttaiQwen3Decode* p, void* stream);
+
 /* Runs ONE phase (ITTAI_PH_*) of layer `layer` as its own kernel with the same grid and the same device
  * code as the persistent kernel, for unit parity tests and per-phase profiling.  `pos`/`next_id` are
  * read, not advanced. */

@@ -21,6 +21,7 @@ PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 EXPORTS = (
     "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
     "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
+    "ittai_qwen3_decode_launch_static",
     "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows",
     "ittai_qwen3_qk_rope_scatter", "ittai_siglip_im2col", "ittai_embed_rows", "ittai_qwen3_final_pool",
 )
@@ -86,6 +87,7 @@ def lib() -> C.CDLL:
     L.ittai_qwen3_decode_workspace_bytes.argtypes = [C.c_int, C.POINTER(C.c_size_t)]
     L.ittai_qwen3_decode_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
     L.ittai_qwen3_phase_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_int, C.c_int, C.c_void_p]
+    L.ittai_qwen3_decode_launch_static.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
     L.ittai_gemm_bf16_launch.argtypes = [C.POINTER(Gemm), C.c_void_p]
     L.ittai_attention_launch.argtypes = [C.POINTER(Attention), C.c_void_p]
     vp, i32, f32 = C.c_void_p, C.c_int, C.c_float

@@ -1064,3 +1064,60 @@ extern "C" int ittai_qwen3_phase_launch(const IttaiQwen3Decode* p, int phase, in
     if (p && (layer < 0 || layer >= p->n_layers)) { ittai::set_error("layer %d outside 0..%d", layer, p->n_layers - 1); return ITTAI_E_ARG; }
     return ittai::launch(p, phase, layer, stream);
 }
+
+// ---- decode launch for callers that cannot allocate device memory ---------------------------------------------
+// Some hosts of this library have no way to get scratch memory at call time: a serving process that handed the whole
+// GPU to its own pool at start-up (so a later cudaMalloc fails or fragments it), a C or Rust runtime that binds this
+// ABI without an allocator of its own, or a latency-critical loop in which cudaMalloc's device-wide synchronisation is
+// not acceptable.  For them the decode kernel's workspace (flagged words, split-K partials, argmax candidates,
+// abort flag) lives in this file-scope device array instead of a caller buffer.  Every GPU that loads the library
+// holds these bytes until the process exits.
+namespace ittai {
+
+constexpr int kStaticMaxBatch = ITTAI_STATIC_DECODE_MAX_BATCH;
+// q3_ws_layout(kStaticMaxBatch) rounded up: 128 B sync + (512+2048+1024+512+1536) words per sequence + partials + candidates
+constexpr size_t kStaticScratchBytes = 256 + (size_t)kStaticMaxBatch * 5632 * 8 + 1280 +
+                                       (size_t)Q3_MAX_CTAS * Q3_PART_WORDS * 8 + 2 * (size_t)Q3_MAX_CTAS * ITTAI_MAX_BATCH * 8;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+// In host code `g_decode_scratch` is only a handle for the runtime, not a device address: the address the kernel needs
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+static void* g_scratch_addr[64] = {nullptr};
+
+static int static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) { set_error("device ordinal %d outside 0..63", dev); return ITTAI_E_DEVICE; }
+    if (g_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_decode_scratch)");
+        g_scratch_addr[dev] = ptr;
+    }
+    *out = g_scratch_addr[dev];
+    return ITTAI_OK;
+}
+
+}  // namespace ittai
+
+extern "C" int ittai_qwen3_decode_launch_static(const IttaiQwen3Decode* p, void* stream) {
+    if (!p) { ittai::set_error("null IttaiQwen3Decode"); return ITTAI_E_ARG; }
+    if (p->batch > ittai::kStaticMaxBatch) {
+        ittai::set_error("batch %d exceeds the built-in scratch, which holds at most %d sequences (%zu bytes); "
+                         "use ittai_qwen3_decode_launch with a caller workspace", p->batch, ittai::kStaticMaxBatch,
+                         ittai::kStaticScratchBytes);
+        return ITTAI_E_ARG;
+    }
+    ittai::Q3Workspace ws;
+    if (p->batch >= 1 && ittai::q3_ws_layout(p->batch, nullptr, &ws) > ittai::kStaticScratchBytes) {
+        ittai::set_error("built-in scratch of %zu bytes is smaller than the workspace batch %d needs", ittai::kStaticScratchBytes, p->batch);
+        return ITTAI_E_ARG;
+    }
+    void* scratch = nullptr;
+    const int rc = ittai::static_scratch(&scratch);
+    if (rc != ITTAI_OK) return rc;
+    IttaiQwen3Decode q = *p;
+    q.workspace = scratch;       // the launch below zeroes the words that must start at zero, as for a caller buffer
+    return ittai::launch(&q, -1, 0, stream);
+}

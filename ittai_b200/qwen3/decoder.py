@@ -201,6 +201,22 @@ class Qwen3Decoder:
         return (out.t(), ns) if timed else out.t()
 
     @torch.no_grad()
+    def decode_static(self, n_steps: int) -> torch.Tensor:
+        """``decode`` through ``ittai_qwen3_decode_launch_static``: the kernel's scratch is the library's built-in
+        device array instead of this object's workspace tensor (for hosts that cannot allocate device memory; batch
+        at most 2).  Returns int32 ``[B, n_steps]``.  Calls that overlap on the GPU share that one array and race."""
+        if max(self.lengths) + n_steps > self.cap:
+            raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths)} cached + {n_steps} steps")
+        out_ids = torch.empty(n_steps, self.B, dtype=torch.int32, device=self.dev)
+        p = self._params(n_steps, 0, None, out_ids, None)
+        p.workspace = None
+        self._keep = (p, out_ids)
+        _C.check(self.lib.ittai_qwen3_decode_launch_static(C.byref(p), self._stream()))
+        self.lengths = [n + n_steps for n in self.lengths]
+        self.check_status()
+        return out_ids.t()
+
+    @torch.no_grad()
     def decode_profiled(self, n_steps: int) -> torch.Tensor:
         """Decode ``n_steps`` tokens recording CTA 0's SM cycle counter for every phase.
 
