@@ -21,7 +21,6 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred
     const int n = pred ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
@@ -35,26 +34,28 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kAttnBM = 64, kAttnBN = 64, kAttnThreads = 128;
+constexpr int kAttnBN = 64;     // keys per step; query rows per CTA = 16 per warp, 4 warps (head_dim 128) or 8 (head_dim 64)
 
 // element offset of 16-byte chunk `ch` of row `r` in a [rows][HD] tile whose chunks are XOR-swizzled by the row
 template <int HD>
 __device__ __forceinline__ int sw(int r, int ch) { return r * HD + ((ch ^ (r & 7)) << 3); }
 
-template <int HD>
+template <int HD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, long long row_stride, int rows_valid, int tid) {
     constexpr int CH = HD / 8;
-    for (int i = tid; i < 64 * CH; i += kAttnThreads) {
+    for (int i = tid; i < ROWS * CH; i += THREADS) {
         const int r = i / CH, ch = i % CH;
         cp_async16(dst + sw<HD>(r, ch), src + (long long)r * row_stride + ch * 8, r < rows_valid);
     }
 }
 
-template <int HD, bool CAUSAL>
-__global__ void __launch_bounds__(kAttnThreads) attn_fwd_kernel(const AttnArgs a) {
-    __shared__ __align__(128) bf16 sq[kAttnBM * HD];
-    __shared__ __align__(128) bf16 sk[kAttnBN * HD];
-    __shared__ __align__(128) bf16 sv[kAttnBN * HD];
+template <int HD, bool CAUSAL, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attn_fwd_kernel(const AttnArgs a) {
+    constexpr int kAttnBM = 16 * WARPS, kAttnThreads = 32 * WARPS;
+    // shared memory: Q tile, then two (K, V) tile pairs so that block kb+1 streams in while block kb is multiplied
+    extern __shared__ __align__(128) unsigned char attn_smem[];
+    bf16* sq = reinterpret_cast<bf16*>(attn_smem);
+    bf16* skv = sq + kAttnBM * HD;                                    // [2][K | V][64 * HD]
     const int4 sinfo = a.seqs[blockIdx.z];
     const int q_len = sinfo.y, kv_len = sinfo.w;
     const int qb = blockIdx.x * kAttnBM;
@@ -68,9 +69,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_fwd_kernel(const AttnArgs a
     const int shift = kv_len - q_len;                       // query i sees keys j <= i + shift
     int kv_end = kv_len;
     if (CAUSAL) { const int lim = qb + q_rows + shift; kv_end = lim < kv_len ? lim : kv_len; }
+    const bool warp_live = warp * 16 < q_rows;              // a warp whose 16 rows are all padding only helps loading
 
-    load_tile<HD>(sq, qp, a.q_row, q_rows, tid);
-    cp_async_wait_all();
+    auto load_kv = [&](int kb, int buf) {
+        const int rows_valid = kv_len - kb < kAttnBN ? kv_len - kb : kAttnBN;
+        load_tile<HD, kAttnBN, kAttnThreads>(skv + (size_t)buf * 2 * kAttnBN * HD, kp + (long long)kb * a.k_row, a.k_row, rows_valid, tid);
+        load_tile<HD, kAttnBN, kAttnThreads>(skv + (size_t)buf * 2 * kAttnBN * HD + kAttnBN * HD, vp + (long long)kb * a.v_row, a.v_row, rows_valid, tid);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile<HD, kAttnBM, kAttnThreads>(sq, qp, a.q_row, q_rows, tid);
+    if (kv_end > 0) load_kv(0, 0); else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     uint32_t qf[HD / 16][4];
 #pragma unroll
@@ -83,70 +92,80 @@ __global__ void __launch_bounds__(kAttnThreads) attn_fwd_kernel(const AttnArgs a
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows g and g + 8 of this warp's 16
     const int row0 = qb + warp * 16 + g, row1 = row0 + 8;
 
-    for (int kb = 0; kb < kv_end; kb += kAttnBN) {
-        __syncthreads();                                     // everyone is done with the previous K/V block
+    int buf = 0;
+    for (int kb = 0; kb < kv_end; kb += kAttnBN, buf ^= 1) {
+        // block kb is in `buf` (waited for below or before the loop); start fetching the next one into the other half
+        if (kb + kAttnBN < kv_end) load_kv(kb + kAttnBN, buf ^ 1);
+        const bf16* sk = skv + (size_t)buf * 2 * kAttnBN * HD;
+        const bf16* sv = sk + kAttnBN * HD;
         const int rows_valid = kv_len - kb < kAttnBN ? kv_len - kb : kAttnBN;
-        load_tile<HD>(sk, kp + (long long)kb * a.k_row, a.k_row, rows_valid, tid);
-        load_tile<HD>(sv, vp + (long long)kb * a.v_row, a.v_row, rows_valid, tid);
-        cp_async_wait_all();
-        __syncthreads();
-        // ---- S = Q K^T
-        float s[kAttnBN / 8][4];
+        const int n16 = (rows_valid + 15) / 16;              // 16-key groups that hold at least one real key
+        if (warp_live) {
+            // ---- S = Q K^T
+            float s[kAttnBN / 8][4];
 #pragma unroll
-        for (int i = 0; i < kAttnBN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            for (int i = 0; i < kAttnBN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
+            for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
-            for (int np = 0; np < kAttnBN / 16; ++np) {
-                uint32_t kf[4];
-                ldsm_x4(kf, sk + sw<HD>(np * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
-                mma16816(s[2 * np], qf[ks], kf[0], kf[1]);
-                mma16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+                for (int np = 0; np < kAttnBN / 16; ++np) {
+                    if (np < n16) {
+                        uint32_t kf[4];
+                        ldsm_x4(kf, sk + sw<HD>(np * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
+                        mma16816(s[2 * np], qf[ks], kf[0], kf[1]);
+                        mma16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+                    }
+                }
+            }
+            // ---- mask, scale, online softmax
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kAttnBN / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = kb + i * 8 + 2 * t + (e & 1), r = (e < 2) ? row0 : row1;
+                    const bool vis = j < kv_len && (!CAUSAL || j <= r + shift);
+                    s[i][e] = vis ? s[i][e] * a.scale_log2 : -INFINITY;
+                }
+                mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
+            m0 = mn0; m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+            uint32_t pf[kAttnBN / 16][4];
+#pragma unroll
+            for (int i = 0; i < kAttnBN / 8; ++i) {
+                const float p0 = exp2f(s[i][0] - ms0), p1 = exp2f(s[i][1] - ms0), p2 = exp2f(s[i][2] - ms1), p3 = exp2f(s[i][3] - ms1);
+                ps0 += p0 + p1; ps1 += p2 + p3;
+                pf[i / 2][(i & 1) * 2] = pack_bf16x2(p0, p1);
+                pf[i / 2][(i & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+            }
+            l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+            // ---- O += P V
+#pragma unroll
+            for (int ks = 0; ks < kAttnBN / 16; ++ks) {
+                if (ks < n16) {
+#pragma unroll
+                    for (int dp = 0; dp < HD / 16; ++dp) {
+                        uint32_t vf[4];
+                        ldsm_x4_t(vf, sv + sw<HD>(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4)));
+                        mma16816(o[2 * dp], pf[ks], vf[0], vf[1]);
+                        mma16816(o[2 * dp + 1], pf[ks], vf[2], vf[3]);
+                    }
+                }
             }
         }
-        // ---- mask, scale, online softmax
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < kAttnBN / 8; ++i) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = kb + i * 8 + 2 * t + (e & 1), r = (e < 2) ? row0 : row1;
-                const bool vis = j < kv_len && (!CAUSAL || j <= r + shift);
-                s[i][e] = vis ? s[i][e] * a.scale_log2 : -INFINITY;
-            }
-            mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
-            mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
-        m0 = mn0; m1 = mn1;
-        float ps0 = 0.f, ps1 = 0.f;
-        uint32_t pf[kAttnBN / 16][4];
-#pragma unroll
-        for (int i = 0; i < kAttnBN / 8; ++i) {
-            const float p0 = exp2f(s[i][0] - ms0), p1 = exp2f(s[i][1] - ms0), p2 = exp2f(s[i][2] - ms1), p3 = exp2f(s[i][3] - ms1);
-            ps0 += p0 + p1; ps1 += p2 + p3;
-            pf[i / 2][(i & 1) * 2] = pack_bf16x2(p0, p1);
-            pf[i / 2][(i & 1) * 2 + 1] = pack_bf16x2(p2, p3);
-        }
-        l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
-        // ---- O += P V
-#pragma unroll
-        for (int ks = 0; ks < kAttnBN / 16; ++ks) {
-#pragma unroll
-            for (int dp = 0; dp < HD / 16; ++dp) {
-                uint32_t vf[4];
-                ldsm_x4_t(vf, sv + sw<HD>(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4)));
-                mma16816(o[2 * dp], pf[ks], vf[0], vf[1]);
-                mma16816(o[2 * dp + 1], pf[ks], vf[2], vf[3]);
-            }
-        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");   // the next block has landed
+        __syncthreads();                                      // and everyone is done reading this one
     }
+    if (!warp_live) return;
     // ---- normalise and store
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -158,6 +177,22 @@ __global__ void __launch_bounds__(kAttnThreads) attn_fwd_kernel(const AttnArgs a
         if (row0 < q_len) *reinterpret_cast<uint32_t*>(op + (long long)row0 * a.o_row + d) = pack_bf16x2(o[i][0] * i0, o[i][1] * i0);
         if (row1 < q_len) *reinterpret_cast<uint32_t*>(op + (long long)row1 * a.o_row + d) = pack_bf16x2(o[i][2] * i1, o[i][3] * i1);
     }
+}
+
+template <int HD, bool CAUSAL, int WARPS>
+static int attn_launch(const AttnArgs& a, int max_q_len, int n_heads, int n_seqs, cudaStream_t st) {
+    constexpr size_t smem = (size_t)(16 * WARPS + 4 * kAttnBN) * HD * 2;
+    const dim3 grid((max_q_len + 16 * WARPS - 1) / (16 * WARPS), n_heads, n_seqs);
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<HD, CAUSAL, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_dev = dev;
+    }
+    attn_fwd_kernel<HD, CAUSAL, WARPS><<<grid, WARPS * 32, smem, st>>>(a);
+    return 0;
 }
 
 void set_error(const char* fmt, ...);
@@ -179,15 +214,13 @@ extern "C" int ittai_attention_launch(const IttaiAttention* p, void* stream) {
     a.v_row = p->v_row; a.v_head = p->v_head; a.v_seq = p->v_seq; a.o_row = p->o_row; a.o_head = p->o_head;
     a.seqs = (const int4*)p->seqs; a.group = p->group;
     a.scale_log2 = 1.4426950408889634f / sqrtf((float)p->head_dim);
-    const dim3 grid((p->max_q_len + kAttnBM - 1) / kAttnBM, p->n_heads, p->n_seqs);
     cudaStream_t st = (cudaStream_t)stream;
-    if (p->head_dim == 128) {
-        if (p->causal) attn_fwd_kernel<128, true><<<grid, kAttnThreads, 0, st>>>(a);
-        else attn_fwd_kernel<128, false><<<grid, kAttnThreads, 0, st>>>(a);
-    } else {
-        if (p->causal) attn_fwd_kernel<64, true><<<grid, kAttnThreads, 0, st>>>(a);
-        else attn_fwd_kernel<64, false><<<grid, kAttnThreads, 0, st>>>(a);
-    }
+    const int ql = p->max_q_len, nh = p->n_heads, ns = p->n_seqs;
+    int rc;
+    if (p->head_dim == 128) rc = p->causal ? attn_launch<128, true, 4>(a, ql, nh, ns, st) : attn_launch<128, false, 4>(a, ql, nh, ns, st);
+    else if (ql <= 64) rc = p->causal ? attn_launch<64, true, 4>(a, ql, nh, ns, st) : attn_launch<64, false, 4>(a, ql, nh, ns, st);
+    else rc = p->causal ? attn_launch<64, true, 8>(a, ql, nh, ns, st) : attn_launch<64, false, 8>(a, ql, nh, ns, st);
+    if (rc != 0) return cuda_fail((cudaError_t)rc, "cudaFuncSetAttribute(attn_fwd_kernel)");
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_fwd_kernel");
 }

@@ -20,7 +20,7 @@ namespace ittai {
 
 constexpr int GM = 128, GN = 256, GK = 64;
 constexpr int kGemmStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;        // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t kStageBytesA = GM * GK * 2, kStageBytesB = GN * GK * 2;
 constexpr uint32_t kGemmSmem = kGemmStages * (kStageBytesA + kStageBytesB) + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr uint32_t kGemmSpin = 1u << 24;
@@ -119,7 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
@@ -177,8 +177,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (!ok) *abort_flag = 1;
         }
     } else {
-        // ---- epilogue: warp w owns TMEM lanes 32*(w%4)..+31 = rows of the tile
-        const int q = warp & 3;
+        // ---- epilogue: warp w may touch TMEM lanes 32*(w%4)..+31 = 32 rows of the tile; the two warps that share a lane
+        //      quarter split the 256 columns, so every scheduler has two epilogue warps to interleave
+        const int q = warp & 3, col_half = (warp - 2) >> 2;
         int local = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             const int buf = local & 1, round = local >> 1;
@@ -194,7 +195,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after();
             const int row = tile_m * GM + q * 32 + lane;
 #pragma unroll 1
-            for (int c0 = 0; c0 < GN; c0 += 32) {
+            for (int c0 = col_half * (GN / 2); c0 < (col_half + 1) * (GN / 2); c0 += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + c0), r);
                 tmem_ld_wait();

@@ -39,17 +39,18 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_rows_kernel(const bf16* _
     }
 }
 
-// y = bf16((x - mean) * rsqrt(var + eps) * gain + beta); width a multiple of 8, at most 2048; gain/beta fp32.
+// y = bf16((x - mean) * rsqrt(var + eps) * gain + beta); width a multiple of 8, at most NCH * 256; gain/beta fp32.
+template <int NCH>
 __global__ void __launch_bounds__(kRowThreads) layernorm_rows_kernel(const bf16* __restrict__ x, int ld_x, const float* __restrict__ gain,
                                                                        const float* __restrict__ beta, bf16* __restrict__ y, int ld_y,
                                                                        int rows, int width, float eps) {
     const int row = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     const int n_chunks = width / 8;
-    float v[8][8];
+    float v[NCH][8];
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < NCH; ++i) {
         const int ch = lane + 32 * i;
         if (ch < n_chunks) {
             const uint4 q = *reinterpret_cast<const uint4*>(x + (size_t)row * ld_x + ch * 8);
@@ -61,14 +62,14 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_rows_kernel(const bf16*
     const float mean = warp_sum(s) / (float)width;
     float sq = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < NCH; ++i)
         if (lane + 32 * i < n_chunks) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; sq += d * d; }
         }
     const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < NCH; ++i) {
         const int ch = lane + 32 * i;
         if (ch < n_chunks) {
             const float4 g0 = *reinterpret_cast<const float4*>(gain + ch * 8), g1 = *reinterpret_cast<const float4*>(gain + ch * 8 + 4);
@@ -204,8 +205,11 @@ extern "C" int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, c
         set_error("layernorm_rows: width must be a multiple of 8 up to 2048");
         return ITTAI_E_ARG;
     }
-    layernorm_rows_kernel<<<row_grid(rows), kRowThreads, 0, (cudaStream_t)stream>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta,
-                                                                                   (bf16*)y, ld_y, rows, width, eps);
+    const int grid = row_grid(rows);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (width <= 768) layernorm_rows_kernel<3><<<grid, kRowThreads, 0, st>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
+    else if (width <= 1280) layernorm_rows_kernel<5><<<grid, kRowThreads, 0, st>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
+    else layernorm_rows_kernel<8><<<grid, kRowThreads, 0, st>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
     return launched("layernorm_rows_kernel");
 }
 
