@@ -24,20 +24,18 @@ constexpr int D = ITTAI_Q3_D, NKV = ITTAI_Q3_NKV, HD = ITTAI_Q3_HD, FF = ITTAI_Q
 constexpr int DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV, DGU = ITTAI_Q3_DGU;
 constexpr int kTile = 128;                       // cache positions per attention tile = one ring entry of K and one of V
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kCombMax = 640;                    // floats the merge step gathers (worst case over split counts)
 constexpr int kStreamPhases = 5;                 // phases of a layer that read streamed data (the head reads HBM directly)
 
 // ---- shared-memory plan (dynamic): header | activations or attention scratch | weight ring -----------------
 struct SmemHdr {
     StreamShared stream;
-    float red[32];
+    float red[kWarps * ITTAI_MAX_BATCH];         // per-warp partial sums of the norm
     int pos0[ITTAI_MAX_BATCH];                   // cache lengths at kernel entry
     int pos_s[ITTAI_MAX_BATCH];
     int tok_s[ITTAI_MAX_BATCH];
     float bestv[kWarps];
     int besti[kWarps];
     float sub[64 * ITTAI_MAX_BATCH];             // per-sub-row partial dot products
-    float comb[kCombMax];                        // split-K partials gathered by the merge step
     float candv[Q3_MAX_CTAS];                    // argmax candidates of every CTA
     int candi[Q3_MAX_CTAS];
 };
@@ -191,15 +189,34 @@ __device__ __forceinline__ const bf16* stream_acquire(Cta& c, uint32_t n, bool& 
 
 // ---- RMSNorm of one row (already in registers, one bf16 pair per thread) into shared memory --------------
 // xs[i] = bf16(bf16(x*rstd) * gain): the value the following Linear sees in the eager model.
-// `gw` is this thread's pair of gains, loaded by the caller BEFORE it waits for the input: a global load issued after
-// the wait would put a full memory round trip on the critical path of every layer.
-__device__ __forceinline__ void norm_pair_to_smem(Cta& c, uint32_t u, uint32_t gw, float* xs_row) {
+// NB rows (one bf16 pair per thread each) -> xs[b][i] = bf16(bf16(x*rstd) * gain), the value the following Linear sees in
+// the eager model.  `gw` is this thread's pair of gains, loaded by the caller BEFORE it waits for the input: a global
+// load issued after the wait would put a full memory round trip on the critical path of every layer.  `ok` is this
+// thread's verdict on the waits that produced `u`; the first barrier both publishes the per-warp sums of squares and
+// collects the verdicts.  Returns false (uniformly) when any thread's wait failed.
+template <int NB>
+__device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[NB], uint32_t gw, bool ok) {
     static_assert(kThreads * 2 == D, "one bf16 pair per thread");
-    const float x0 = bf_lo(u), x1 = bf_hi(u);
-    const float tot = block_sum(x0 * x0 + x1 * x1, c.hdr->red);
-    const float rstd = 1.0f / sqrtf(tot * (1.0f / D) + c.p.eps);
-    xs_row[2 * c.tid] = bf16r(bf16r(x0 * rstd) * bf_lo(gw));
-    xs_row[2 * c.tid + 1] = bf16r(bf16r(x1 * rstd) * bf_hi(gw));
+    static_assert(NB * kWarps <= 32 * 4, "per-warp partial sums must fit the scratch");
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        const float x0 = bf_lo(u[b]), x1 = bf_hi(u[b]);
+        const float v = warp_sum(x0 * x0 + x1 * x1);
+        if (c.lane == 0) c.hdr->red[b * kWarps + c.warp] = v;
+    }
+    if (cta_or(!ok)) return false;
+    c.t_ready = clock64();
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < kWarps; ++i) tot += c.hdr->red[b * kWarps + i];
+        const float rstd = 1.0f / sqrtf(tot * (1.0f / D) + c.p.eps);
+        c.xs[b * FF + 2 * c.tid] = bf16r(bf16r(bf_lo(u[b]) * rstd) * bf_lo(gw));
+        c.xs[b * FF + 2 * c.tid + 1] = bf16r(bf16r(bf_hi(u[b]) * rstd) * bf_hi(gw));
+    }
+    cta_sync();
+    return true;
 }
 
 // Waits for NB rows of K bf16 values in flagged-word format and spreads them into xs as fp32.
@@ -312,11 +329,7 @@ __device__ bool phase_qkv(Cta& c, int l) {
         if (l == 0) u[b] = ldcg32(reinterpret_cast<const bf16*>(p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * c.tid);
         else ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_QKV);
     }
-    if (!all_ok(ok)) return false;
-    c.t_ready = clock64();
-#pragma unroll
-    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], gw, c.xs + b * FF);
-    cta_sync();
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     int p0, p1;
@@ -550,32 +563,42 @@ __device__ bool phase_attn(Cta& c, int l) {
     while (nc * 2 <= n_splits && nc < 16) nc *= 2;
     const int dpc = HD / nc, W = 4 + 2 * dpc;
     if (it.active && it.s < nc) {
+        // a warp per pair of adjacent outputs, lanes = splits: each lane fetches (m, l, o, o) of its split in one round
+        // trip, then three warp reductions finish the pair
         const int b = it.b, g = it.g, d0 = it.s * dpc;
         const uint64_t* base = c.ws.part + (size_t)(b * NKV + g) * n_splits * Q3_PART_WORDS;
         bool ok = true;
-        for (int idx = c.tid; idx < n_splits * W; idx += kThreads) {
-            const int k = idx / W, j = idx % W;
-            const int src = j < 4 ? j : 4 + ((j - 4) / dpc) * HD + d0 + (j - 4) % dpc;
-            uint32_t u = 0;
-            ok = ok && wait_word(c.w, base + (size_t)k * Q3_PART_WORDS + src, tag, u, 16 + ITTAI_PH_ATTN);
-            c.hdr->comb[idx] = __uint_as_float(u);
+        for (int pr = c.warp; pr < dpc; pr += kWarps) {
+            const int h = pr / (dpc / 2), dd = (pr % (dpc / 2)) * 2;
+            float m = -INFINITY, l = 0.f, o0 = 0.f, o1 = 0.f;
+            if (c.lane < n_splits) {
+                const uint64_t* pk = base + (size_t)c.lane * Q3_PART_WORDS;
+                const uint64_t* w4[4] = {pk + h, pk + 2 + h, pk + 4 + h * HD + d0 + dd, pk + 4 + h * HD + d0 + dd + 1};
+                uint32_t spins = 0;
+                for (;;) {
+                    const uint64_t v0 = ld_flagged(w4[0]), v1 = ld_flagged(w4[1]), v2 = ld_flagged(w4[2]), v3 = ld_flagged(w4[3]);
+                    if ((uint32_t)(v0 >> 32) == tag && (uint32_t)(v1 >> 32) == tag && (uint32_t)(v2 >> 32) == tag && (uint32_t)(v3 >> 32) == tag) {
+                        m = __uint_as_float((uint32_t)v0); l = __uint_as_float((uint32_t)v1);
+                        o0 = __uint_as_float((uint32_t)v2); o1 = __uint_as_float((uint32_t)v3);
+                        break;
+                    }
+                    if (((++spins) & 1023u) == 0u) {
+                        if (ld_relaxed(&c.w.sync[1]) != 0u) { ok = false; break; }
+                        if (spins >= c.w.limit) {
+                            report_status(c.w.status, c.w.sync, ITTAI_ST_FLAG_TIMEOUT, 16 + ITTAI_PH_ATTN, blockIdx.x, (uint32_t)(v0 >> 32), tag);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+            const float M = warp_max(m);
+            const float wk = exp2f(m - (M == -INFINITY ? 0.f : M));
+            const float Ls = warp_sum(l * wk), O0 = warp_sum(o0 * wk), O1 = warp_sum(o1 * wk);
+            if (c.lane == 0)
+                st_flagged(c.ws.attn + (size_t)b * (DQ / 2) + ((2 * g + h) * HD + d0 + dd) / 2, pack_bf16x2(O0 / Ls, O1 / Ls), tag);
         }
         if (!all_ok(ok)) return false;
-        const bool valid = c.tid < 2 * dpc;
-        const int tt = valid ? c.tid : 0, h = tt / dpc, dd = tt % dpc;
-        float M = -INFINITY;
-        for (int k = 0; k < n_splits; ++k) M = fmaxf(M, c.hdr->comb[k * W + h]);
-        float Ls = 0.f, O = 0.f;
-        for (int k = 0; k < n_splits; ++k) {
-            const float wk = exp2f(c.hdr->comb[k * W + h] - M);
-            Ls = fmaf(c.hdr->comb[k * W + 2 + h], wk, Ls);
-            O = fmaf(c.hdr->comb[k * W + 4 + h * dpc + dd], wk, O);
-        }
-        const float out = O / Ls;
-        const float nb = __shfl_down_sync(0xffffffffu, out, 1);
-        if (valid && (dd & 1) == 0)
-            st_flagged(c.ws.attn + (size_t)b * (DQ / 2) + ((2 * g + h) * HD + d0 + dd) / 2, pack_bf16x2(out, nb), tag);
-        cta_sync();
     }
     return true;
 }
@@ -663,11 +686,7 @@ __device__ bool phase_gu(Cta& c, int l) {
     bool ok = true;
 #pragma unroll
     for (int b = 0; b < NB; ++b) ok = ok && wait_word(c.w, c.ws.hmid + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_GU);
-    if (!all_ok(ok)) return false;
-    c.t_ready = clock64();
-#pragma unroll
-    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], gw, c.xs + b * FF);
-    cta_sync();
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     int u0, u1;
@@ -717,11 +736,7 @@ __device__ bool phase_head(Cta& c) {
 #pragma unroll
     for (int b = 0; b < NB; ++b)
         ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag_of(c, c.step, p.n_layers), u[b], ITTAI_PH_HEAD);
-    if (!all_ok(ok)) return false;
-    c.t_ready = clock64();
-#pragma unroll
-    for (int b = 0; b < NB; ++b) norm_pair_to_smem(c, u[b], gw, c.xs + b * FF);
-    cta_sync();
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     bf16* logits = reinterpret_cast<bf16*>(p.logits);
