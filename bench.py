@@ -106,6 +106,38 @@ class ClockSampler:
                             "samples": len(sm)}
 
 
+SIGLIP_BATCH = 64
+# dram__bytes_read.sum + dram__bytes_write.sum of q3_decode_kernel<1> per decoded token at cache length 4096, from the ncu
+# capture of an 8-token launch summarised under profiles/ (traffic grows with tokens, so it is scaled by the step's 256)
+NCU_DRAM_BYTES_PER_TOKEN = (13.328536e9 + 33.232896e6) / 8
+
+
+def siglip_leg(dev, rank, barrier, iters: int = 20):
+    """SigLIP ViT-B/16-224 batch-64 forward (random-init bf16 tower, N(0,1) pixels resident on the device): images per
+    second over `iters` graph replays after 3 warm-ups, timed with CUDA events between barriers."""
+    from transformers import SiglipVisionConfig, SiglipVisionModel
+    from ittai_b200.siglip.kernel import Engine
+    cfg = SiglipVisionConfig(hidden_size=768, intermediate_size=3072, num_hidden_layers=12, num_attention_heads=12, image_size=224,
+                             patch_size=16, hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6)
+    torch.manual_seed(2 + rank)
+    vm = SiglipVisionModel(cfg).to(torch.bfloat16).eval().to(dev)
+    eng = Engine(vm, SIGLIP_BATCH)
+    px = torch.randn(SIGLIP_BATCH, 3, 224, 224, generator=torch.Generator().manual_seed(3 + rank)).to(dev)
+    inp = {"pixel_values": px}
+    for _ in range(3):
+        eng.forward(inp)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        eng.forward(inp)
+    e1.record()
+    barrier()
+    eng.check()
+    return {"ms": e0.elapsed_time(e1), "iters": iters, "images": iters * SIGLIP_BATCH, "flops_reference_formula": iters * eng.flops("reference"),
+            "launches_per_forward": 2 + 12 * 7 + 8}
+
+
 def cpu_reference(steps: int, warmup: int):
     """The reference's eager PyTorch path on host cores: batch-1 decode at cache length 4096 (see oracle/qwen3_hf.py)."""
     from oracle import qwen3_hf as hf
@@ -136,6 +168,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
+    ap.add_argument("--no-siglip", action="store_true", help="skip the SigLIP images/s leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -147,6 +180,7 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun), got WORLD_SIZE={world}")
 
     import torch.distributed as dist
+    from ittai_b200 import replicas
     from ittai_b200.qwen3 import Qwen3Decoder, decode_bytes_per_token
 
     torch.cuda.set_device(local)
@@ -215,16 +249,14 @@ def main():
     dec.check_status()
     e2e_ms = e0.elapsed_time(e1)
 
-    t = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = t.tolist()
+    sig = siglip_leg(dev, rank, barrier) if not args.no_siglip else None
+    (total_ms, e2e_ms, sig_ms), toks = replicas.aggregate([total_ms, e2e_ms, sig["ms"] if sig else 0.0],
+                                                          units=args.steps * DECODE, device=dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    toks = world * args.steps * DECODE
     value = toks / (total_ms / 1e3)
     peaks, peak_kind = measured_peaks()
     mean_bytes = sum(decode_bytes_per_token(PROMPT + i) for i in range(DECODE)) / DECODE
@@ -236,16 +268,26 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"qwen3-0.6b random-init bf16, batch 1, {PROMPT}-token prompt, kv capacity {CAP}, "
                                f"{DECODE} greedy decode steps per step", "l2": "inputs larger than L2 (1.66 GB streamed per token)",
-                   "replicas": world},
+                   "replicas": world, "parallelism": f"{world} independent replicas, no data-path collective"},
         "us_per_token": {"median": float(per_tok_us.median()), "p99": float(per_tok_us.quantile(0.99)),
                          "mean_kernel": kern_ms_avg * 1e3 / DECODE},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_kind": peak_kind,
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_TOKEN * DECODE / 1e9,
+                     "traffic_unit": "GB per launch (ncu dram read+write of an 8-token launch, scaled by tokens)", "peak_kind": peak_kind,
                      "frac_of_nominal_8TBs": achieved / 8000.0, "bytes_per_token": mean_bytes},
         "e2e": {"value": toks / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * DECODE},
         "gpu_launches": launches,
         "clocks": clk.summary,
     }
+    if sig:
+        flops = sig["flops_reference_formula"]
+        tf = world * flops / (sig_ms / 1e3) / 1e12
+        line["siglip"] = {"metric": "siglip_vit_b16_224_images_per_s", "value": world * sig["images"] / (sig_ms / 1e3), "unit": "img/s",
+                          "batch": SIGLIP_BATCH, "ms_per_batch": sig_ms / sig["iters"], "dtype": "bf16",
+                          "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                       "frac": tf / world / peaks["bf16_tflops"], "peak_kind": peak_kind,
+                                       "flops": "reference benchmark formula: B*L*(2*S*D*(4D+2F) + 4*S*S*D)"},
+                          "gpu_launches_per_forward": sig["launches_per_forward"]}
     if not args.no_cpu_baseline and world == 1:
         r, sample = cpu_reference(8, 2)
         line["cpu_baseline"] = {"value": r["tok_s"], "unit": UNIT, "cores": r["threads"], "kind": "reference", "sample": sample}
