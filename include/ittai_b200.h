@@ -208,6 +208,8 @@ typedef struct IttaiAttention {
     int64_t q_row, q_head, k_row, k_head, k_seq, v_row, v_head, v_seq, o_row, o_head;
     const int32_t* seqs;   /* [n_seqs][4] device: first q row, q rows, first k/v row, k/v rows */
     int32_t n_seqs, n_heads, group, head_dim, causal, max_q_len;
+    int32_t max_kv_len;    /* largest kv_rows over the sequences, or 0 if unknown (enables the short-sequence kernel) */
+    int32_t reserved0;
 } IttaiAttention;
 int ittai_attention_launch(const IttaiAttention* a, void* stream);
 

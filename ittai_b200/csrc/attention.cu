@@ -179,6 +179,133 @@ __global__ void __launch_bounds__(WARPS * 32) attn_fwd_kernel(const AttnArgs a) 
     }
 }
 
+// Short sequences (at most 256 keys, dense): one CTA per (sequence, head) keeps the whole K and V in shared memory,
+// loaded once, and every warp runs its 16 query rows against all keys with no CTA-wide barrier after the load: 13 warps
+// for SigLIP's 196 tokens, two CTAs per SM.  K and V are read from HBM once per head instead of once per query block.
+constexpr int kShortKeys = 256;
+template <int HD>
+__global__ void __launch_bounds__(512) attn_short_kernel(const AttnArgs a, int warps) {
+    extern __shared__ __align__(128) unsigned char attn_smem[];
+    const int4 sinfo = a.seqs[blockIdx.z];
+    const int q_len = sinfo.y, kv_len = sinfo.w;
+    const int head = blockIdx.y, kvh = head / a.group;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int q_rows_pad = warps * 16, threads = warps * 32;
+    bf16* sq = reinterpret_cast<bf16*>(attn_smem);
+    bf16* sk = sq + q_rows_pad * HD;
+    bf16* sv = sk + kShortKeys * HD;
+    const bf16* qp = a.q + (long long)sinfo.x * a.q_row + (long long)head * a.q_head;
+    const bf16* kp = a.k + (long long)blockIdx.z * a.k_seq + (long long)kvh * a.k_head + (long long)sinfo.z * a.k_row;
+    const bf16* vp = a.v + (long long)blockIdx.z * a.v_seq + (long long)kvh * a.v_head + (long long)sinfo.z * a.v_row;
+    constexpr int CH = HD / 8;
+    const int kv_pad = (kv_len + 15) & ~15;
+    for (int i = tid; i < q_rows_pad * CH; i += threads) {
+        const int r = i / CH, ch = i % CH;
+        cp_async16(sq + sw<HD>(r, ch), qp + (long long)r * a.q_row + ch * 8, r < q_len);
+    }
+    for (int i = tid; i < kv_pad * CH; i += threads) {
+        const int r = i / CH, ch = i % CH;
+        cp_async16(sk + sw<HD>(r, ch), kp + (long long)r * a.k_row + ch * 8, r < kv_len);
+        cp_async16(sv + sw<HD>(r, ch), vp + (long long)r * a.v_row + ch * 8, r < kv_len);
+    }
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (warp * 16 >= q_len) return;
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldsm_x4(qf[ks], sq + sw<HD>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    for (int kb = 0; kb < kv_len; kb += kAttnBN) {
+        const int rows_valid = kv_len - kb < kAttnBN ? kv_len - kb : kAttnBN;
+        const int n16 = (rows_valid + 15) / 16;
+        float s[kAttnBN / 8][4];
+#pragma unroll
+        for (int i = 0; i < kAttnBN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < kAttnBN / 16; ++np) {
+                if (np < n16) {
+                    uint32_t kf[4];
+                    ldsm_x4(kf, sk + sw<HD>(kb + np * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
+                    mma16816(s[2 * np], qf[ks], kf[0], kf[1]);
+                    mma16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+                }
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kAttnBN / 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + i * 8 + 2 * t + (e & 1);
+                s[i][e] = j < kv_len ? s[i][e] * a.scale_log2 : -INFINITY;
+            }
+            mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);       // every block holds a real key, so mn is finite
+        m0 = mn0; m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+        uint32_t pf[kAttnBN / 16][4];
+#pragma unroll
+        for (int i = 0; i < kAttnBN / 8; ++i) {
+            const float p0 = exp2f(s[i][0] - mn0), p1 = exp2f(s[i][1] - mn0), p2 = exp2f(s[i][2] - mn1), p3 = exp2f(s[i][3] - mn1);
+            ps0 += p0 + p1; ps1 += p2 + p3;
+            pf[i / 2][(i & 1) * 2] = pack_bf16x2(p0, p1);
+            pf[i / 2][(i & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+        }
+        l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+#pragma unroll
+        for (int ks = 0; ks < kAttnBN / 16; ++ks) {
+            if (ks < n16) {
+#pragma unroll
+                for (int dp = 0; dp < HD / 16; ++dp) {
+                    uint32_t vf[4];
+                    ldsm_x4_t(vf, sv + sw<HD>(kb + ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4)));
+                    mma16816(o[2 * dp], pf[ks], vf[0], vf[1]);
+                    mma16816(o[2 * dp + 1], pf[ks], vf[2], vf[3]);
+                }
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    const int row0 = warp * 16 + g, row1 = row0 + 8;
+    bf16* op = a.o + (long long)sinfo.x * a.o_row + (long long)head * a.o_head;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * t;
+        if (row0 < q_len) *reinterpret_cast<uint32_t*>(op + (long long)row0 * a.o_row + d) = pack_bf16x2(o[i][0] * i0, o[i][1] * i0);
+        if (row1 < q_len) *reinterpret_cast<uint32_t*>(op + (long long)row1 * a.o_row + d) = pack_bf16x2(o[i][2] * i1, o[i][3] * i1);
+    }
+}
+
+static int attn_short_launch(const AttnArgs& a, int max_q_len, int n_heads, int n_seqs, cudaStream_t st) {
+    const int warps = (max_q_len + 15) / 16;
+    const size_t smem = (size_t)(warps * 16 + 2 * kShortKeys) * 64 * 2;
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_short_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((16 * 16 + 2 * kShortKeys) * 64 * 2));
+        if (e != cudaSuccess) return (int)e;
+        attr_dev = dev;
+    }
+    attn_short_kernel<64><<<dim3(1, n_heads, n_seqs), warps * 32, smem, st>>>(a, warps);
+    return 0;
+}
+
 template <int HD, bool CAUSAL, int WARPS>
 static int attn_launch(const AttnArgs& a, int max_q_len, int n_heads, int n_seqs, cudaStream_t st) {
     constexpr size_t smem = (size_t)(16 * WARPS + 4 * kAttnBN) * HD * 2;
@@ -218,6 +345,7 @@ extern "C" int ittai_attention_launch(const IttaiAttention* p, void* stream) {
     const int ql = p->max_q_len, nh = p->n_heads, ns = p->n_seqs;
     int rc;
     if (p->head_dim == 128) rc = p->causal ? attn_launch<128, true, 4>(a, ql, nh, ns, st) : attn_launch<128, false, 4>(a, ql, nh, ns, st);
+    else if (!p->causal && ql > 64 && ql <= 256 && p->max_kv_len > 0 && p->max_kv_len <= kShortKeys) rc = attn_short_launch(a, ql, nh, ns, st);
     else if (ql <= 64) rc = p->causal ? attn_launch<64, true, 4>(a, ql, nh, ns, st) : attn_launch<64, false, 4>(a, ql, nh, ns, st);
     else rc = p->causal ? attn_launch<64, true, 8>(a, ql, nh, ns, st) : attn_launch<64, false, 8>(a, ql, nh, ns, st);
     if (rc != 0) return cuda_fail((cudaError_t)rc, "cudaFuncSetAttribute(attn_fwd_kernel)");

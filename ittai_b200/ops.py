@@ -47,7 +47,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Ten
 
 
 def attention(q, k, v, o, seqs: torch.Tensor, *, n_heads: int, group: int, head_dim: int, causal: bool, max_q_len: int,
-              q_strides, k_strides, v_strides, o_strides) -> None:
+              q_strides, k_strides, v_strides, o_strides, max_kv_len: int = 0) -> None:
     """Flash attention over sequences described by ``seqs`` (int32 [n, 4] device: q row0, q rows, kv row0, kv rows).
 
     ``q_strides`` = (row, head), ``k_strides`` / ``v_strides`` = (row, head, seq), ``o_strides`` = (row, head), in elements;
@@ -60,6 +60,7 @@ def attention(q, k, v, o, seqs: torch.Tensor, *, n_heads: int, group: int, head_
     a.o_row, a.o_head = o_strides
     a.seqs = seqs.data_ptr()
     a.n_seqs, a.n_heads, a.group, a.head_dim, a.causal, a.max_q_len = seqs.shape[0], n_heads, group, head_dim, int(causal), max_q_len
+    a.max_kv_len = max_kv_len
     _C.check(_C.lib().ittai_attention_launch(C.byref(a), _stream(q)))
 
 

@@ -33,7 +33,7 @@ def test_attention_dense_packed_qkv(B, S):
     out = torch.zeros(B * S, D, dtype=torch.bfloat16, device="cuda")
     seqs = torch.tensor([[b * S, S, b * S, S] for b in range(B)], dtype=torch.int32, device="cuda")
     ops.attention(qkv, qkv[:, D:], qkv[:, 2 * D:], out, seqs, n_heads=H, group=1, head_dim=hd, causal=False, max_q_len=S,
-                  q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0), o_strides=(D, hd))
+                  q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0), o_strides=(D, hd), max_kv_len=S)
     q, k, v = (qkv[:, i * D:(i + 1) * D].float().view(B, S, H, hd).transpose(1, 2) for i in range(3))
     want = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B * S, D)
     _check(out, want, f"dense attention B={B} S={S}")
