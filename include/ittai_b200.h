@@ -62,7 +62,7 @@ enum {
                                      status[2]=CTA, status[3]=tag seen, status[4]=tag expected */
     ITTAI_ST_BAD_TOKEN = 3,       /* status[1]=token id, status[2]=step, status[3]=position, status[4]=sequence */
     ITTAI_ST_STREAM_TIMEOUT = 4,  /* a weight-stream copy did not land: status[1]=entry, status[2]=CTA */
-    ITTAI_ST_GEMM_TIMEOUT = 5     /* a pipeline wait of the tensor-core GEMM ran out: status[1]=CTA */
+    ITTAI_ST_GEMM_TIMEOUT = 5     /* a pipeline wait of a tensor-core kernel (GEMM, attention) ran out: status[1]=CTA */
 };
 
 /* Phases of one decoded token, in execution order inside a layer (ids used by ittai_qwen3_phase_launch). */
@@ -209,7 +209,14 @@ typedef struct IttaiAttention {
     const int32_t* seqs;   /* [n_seqs][4] device: first q row, q rows, first k/v row, k/v rows */
     int32_t n_seqs, n_heads, group, head_dim, causal, max_q_len;
     int32_t max_kv_len;    /* largest kv_rows over the sequences, or 0 if unknown (enables the short-sequence kernel) */
+    /* The tensor-memory kernel (head_dim 64, dense, 65..256 queries and at most 224 keys per sequence, heads adjacent in
+     * a row: q_head = k_head = v_head = 64, k_seq = v_seq = 0) addresses q, k and v through TMA tensor maps and needs the
+     * row counts of the matrices they point into, plus status words for its bounded waits.  Leave the three at 0/NULL
+     * to stay on the register-tile kernels. */
+    int32_t q_rows_total;  /* rows of the matrix behind q (every sequence's q_row0 + q rows lies inside) */
+    int32_t kv_rows_total; /* rows of the matrices behind k and v */
     int32_t reserved0;
+    uint32_t* status;      /* [ITTAI_STATUS_WORDS] device words, or NULL */
 } IttaiAttention;
 int ittai_attention_launch(const IttaiAttention* a, void* stream);
 

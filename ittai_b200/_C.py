@@ -65,7 +65,8 @@ class Attention(C.Structure):
         ("v_row", C.c_int64), ("v_head", C.c_int64), ("v_seq", C.c_int64), ("o_row", C.c_int64), ("o_head", C.c_int64),
         ("seqs", C.c_void_p),
         ("n_seqs", C.c_int32), ("n_heads", C.c_int32), ("group", C.c_int32), ("head_dim", C.c_int32),
-        ("causal", C.c_int32), ("max_q_len", C.c_int32), ("max_kv_len", C.c_int32), ("reserved0", C.c_int32),
+        ("causal", C.c_int32), ("max_q_len", C.c_int32), ("max_kv_len", C.c_int32), ("q_rows_total", C.c_int32),
+        ("kv_rows_total", C.c_int32), ("reserved0", C.c_int32), ("status", C.c_void_p),
     ]
 
 

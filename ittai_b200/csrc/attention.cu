@@ -324,6 +324,8 @@ static int attn_launch(const AttnArgs& a, int max_q_len, int n_heads, int n_seqs
 
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
+bool attn_tc_supported(const IttaiAttention* p);          // attention_sm100.cu
+int attn_tc_launch(const IttaiAttention* p, cudaStream_t st);
 
 }  // namespace ittai
 
@@ -335,6 +337,7 @@ extern "C" int ittai_attention_launch(const IttaiAttention* p, void* stream) {
     if (p->n_seqs < 1 || p->n_heads < 1 || p->group < 1 || p->max_q_len < 1) { set_error("attention: bad sizes"); return ITTAI_E_ARG; }
     const long long strides[] = {p->q_row, p->q_head, p->k_row, p->k_head, p->k_seq, p->v_row, p->v_head, p->v_seq, p->o_row};
     for (long long s : strides) if (s % 8) { set_error("attention: strides must be multiples of 8 elements"); return ITTAI_E_ARG; }
+    if (attn_tc_supported(p)) return attn_tc_launch(p, (cudaStream_t)stream);
     AttnArgs a;
     a.q = (const bf16*)p->q; a.k = (const bf16*)p->k; a.v = (const bf16*)p->v; a.o = (bf16*)p->o;
     a.q_row = p->q_row; a.q_head = p->q_head; a.k_row = p->k_row; a.k_head = p->k_head; a.k_seq = p->k_seq;

@@ -47,11 +47,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Ten
 
 
 def attention(q, k, v, o, seqs: torch.Tensor, *, n_heads: int, group: int, head_dim: int, causal: bool, max_q_len: int,
-              q_strides, k_strides, v_strides, o_strides, max_kv_len: int = 0) -> None:
+              q_strides, k_strides, v_strides, o_strides, max_kv_len: int = 0, q_rows_total: int = 0, kv_rows_total: int = 0,
+              status: torch.Tensor | None = None) -> None:
     """Flash attention over sequences described by ``seqs`` (int32 [n, 4] device: q row0, q rows, kv row0, kv rows).
 
     ``q_strides`` = (row, head), ``k_strides`` / ``v_strides`` = (row, head, seq), ``o_strides`` = (row, head), in elements;
-    q, k, v, o are any bf16 tensors whose ``data_ptr`` is the origin those strides refer to."""
+    q, k, v, o are any bf16 tensors whose ``data_ptr`` is the origin those strides refer to.  ``q_rows_total``,
+    ``kv_rows_total`` (rows of the matrices behind q and k/v) and ``status`` enable the tensor-memory kernel for short
+    dense sequences; it reports a timed-out wait through ``status`` (see ``check_status``)."""
     a = _C.Attention()
     a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
     a.q_row, a.q_head = q_strides
@@ -60,7 +63,8 @@ def attention(q, k, v, o, seqs: torch.Tensor, *, n_heads: int, group: int, head_
     a.o_row, a.o_head = o_strides
     a.seqs = seqs.data_ptr()
     a.n_seqs, a.n_heads, a.group, a.head_dim, a.causal, a.max_q_len = seqs.shape[0], n_heads, group, head_dim, int(causal), max_q_len
-    a.max_kv_len = max_kv_len
+    a.max_kv_len, a.q_rows_total, a.kv_rows_total = max_kv_len, q_rows_total, kv_rows_total
+    a.status = status.data_ptr() if status is not None else None
     _C.check(_C.lib().ittai_attention_launch(C.byref(a), _stream(q)))
 
 

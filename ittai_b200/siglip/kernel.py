@@ -86,7 +86,7 @@ class Engine:
             ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
             ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
                           causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
-                          o_strides=(D, hd), max_kv_len=S)
+                          o_strides=(D, hd), max_kv_len=S, q_rows_total=self.M, kv_rows_total=self.M, status=st)
             ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x)
             ops.layernorm_rows(self.x, *w["ln2"], eps, out=self.y)
             ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)

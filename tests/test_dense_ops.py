@@ -40,6 +40,30 @@ def test_attention_dense_packed_qkv(B, S):
 
 
 @gpu
+@pytest.mark.parametrize("lens", [[196] * 5, [224, 65, 130, 200], [128, 129], [70]])
+def test_attention_tensor_memory_kernel(lens):
+    """The tcgen05 kernel (row totals + status words given): ragged sequences packed in one q | k | v matrix, with rows
+    past the last sequence left as NaN-free garbage.  Same reference and tolerance as the register-tile kernels."""
+    from ittai_b200 import ops
+    H, hd, D = 12, 64, 768
+    T = sum(lens)
+    qkv = _rand(T + 3, 3 * D, seed=5)
+    out = torch.zeros(T + 3, D, dtype=torch.bfloat16, device="cuda")
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    seqs = torch.tensor([[s, n, s, n] for s, n in zip(starts, lens)], dtype=torch.int32, device="cuda")
+    st = ops.new_status(qkv.device)
+    ops.attention(qkv, qkv[:, D:], qkv[:, 2 * D:], out, seqs, n_heads=H, group=1, head_dim=hd, causal=False, max_q_len=max(lens),
+                  q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0), o_strides=(D, hd),
+                  max_kv_len=max(lens), q_rows_total=T + 3, kv_rows_total=T + 3, status=st)
+    ops.check_status(st)
+    for s, n in zip(starts, lens):
+        q, k, v = (qkv[s:s + n, i * D:(i + 1) * D].float().view(n, H, hd).transpose(0, 1) for i in range(3))
+        want = F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(n, D)
+        _check(out[s:s + n], want, f"tensor-memory attention rows {s}..{s + n}")
+    assert not out[T:].any(), "rows past the last sequence were written"
+
+
+@gpu
 @pytest.mark.parametrize("q_len,prefix", [(300, 0), (64, 0), (130, 70), (1, 500)])
 def test_attention_causal_gqa_cache_layout(q_len, prefix):
     """Qwen3 layout: q in a [T, 4096] qkv matrix (16 heads of 128), k/v in a cache [B, 8, cap, 128], causal with a prefix."""
