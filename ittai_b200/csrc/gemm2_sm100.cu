@@ -1,0 +1,347 @@
+// Two-SM bf16 GEMM: C[M,N] = A[M,K] * W[N,K]^T (+ fused epilogue) with tcgen05.mma.cta_group::2.  A cluster of two CTAs
+// owns a 256 x 256 output tile: each CTA loads 128 rows of A and 128 rows of W per 64-wide k-block (32 KB instead of the
+// 48 KB a lone CTA needs for its 128 x 256 tile, which is what bounds the one-SM kernel: the L2 cannot feed 96 bytes
+// per clock to every SM), the leader CTA issues M256 N256 K16 MMAs that read both CTAs' shared memory, and each CTA
+// keeps the accumulator rows of its own 128 rows of A in its own tensor memory (two 256-column buffers, so the epilogue of
+// one tile overlaps the main loop of the next).
+//
+// Roles per CTA: warp 0 (one lane) TMA producer for this CTA's half of every stage, completion counted on the LEADER's
+// full barrier; warp 1 allocates tensor memory and, in the leader only, issues the MMAs, releasing stages and
+// publishing accumulators with multicast commits that arrive in both CTAs; warps 2-9 are the epilogue, 32 columns at a
+// time: accumulator -> bias / activation / rounding in the row-per-thread layout tcgen05.ld gives -> residual add from
+// a TMA-prefetched tile -> a swizzled staging tile in shared memory -> TMA store (row-per-thread global stores write
+// half sectors of 32 different lines per instruction and slow the main loop's loads down).  The peer's epilogue warps
+// arrive on the leader's accumulator-free barrier through the cluster's shared window.  Every wait is bounded.
+#include <cuda.h>
+
+#include "gemm_epilogue.cuh"
+#include "tmap.h"
+
+namespace ittai {
+
+constexpr int PM = 256, PN = 256, PK = 64;   // pair tile
+#ifndef ITTAI_GEMM2_STAGES
+#define ITTAI_GEMM2_STAGES 5
+#endif
+constexpr int kStages2 = ITTAI_GEMM2_STAGES;
+#ifndef ITTAI_EPI_WARPS
+#define ITTAI_EPI_WARPS 8
+#endif
+constexpr int kEpiWarps = ITTAI_EPI_WARPS;         // 8 or 16: 2 or 4 warps per TMEM lane quarter
+constexpr int kEpiCols = PN / (kEpiWarps / 4);    // accumulator columns per epilogue warp
+constexpr int kThreads2 = 64 + 32 * kEpiWarps;
+constexpr uint32_t kHalfA = 128 * PK * 2, kHalfB = 128 * PK * 2;                // per CTA per stage
+constexpr uint32_t kStageOut = 3 * 2048;                                         // per epilogue warp: three tiles of 32 rows x 64 B
+constexpr uint32_t kSmem2 = kStages2 * (kHalfA + kHalfB) + kEpiWarps * kStageOut + 4096 /*bias slices*/ + 1024 /*alignment*/ + 512 /*barriers*/;
+constexpr uint32_t kSpin2 = 1u << 24;
+#ifdef ITTAI_TILE_MFAST
+#define TILE_M(t) ((t) % tiles_m)
+#define TILE_N(t) ((t) / tiles_m)
+#else
+#define TILE_M(t) ((t) / tiles_n)
+#define TILE_N(t) ((t) % tiles_n)
+#endif
+#ifdef ITTAI_EPI_SKIP_STG
+#define EPI_STORE_LIMIT (g.M - 1000000)
+#else
+#define EPI_STORE_LIMIT g.M
+#endif
+constexpr uint32_t kTmemCols2 = 512;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Address of the same shared-memory object in CTA `rank` of the cluster, in the cluster's shared window.
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(p)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load into this CTA's shared memory whose completion bytes are counted on a barrier that may live in the
+// peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(tmap), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(void* smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs once every MMA issued so far has finished.
+__device__ __forceinline__ void umma_commit_pair(void* bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads2, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res, const GemmArgs g) {
+    extern __shared__ __align__(1024) unsigned char gsm_raw[];
+    unsigned char* gsm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sa = gsm;                                         // [stages][128 rows][128 B]
+    unsigned char* sb = gsm + kStages2 * kHalfA;                     // [stages][128 rows][128 B]
+    unsigned char* sout = sb + kStages2 * kHalfB;                    // [epilogue warps] staging tiles, then their bias slices
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sout + kEpiWarps * kStageOut + 4096);
+    unsigned long long* full = bars;                                 // [stages]  both producers -> leader's MMA
+    unsigned long long* empty = bars + kStages2;                     // [stages]  MMA -> this CTA's producer
+    unsigned long long* acc_full = bars + 2 * kStages2;              // [2]       MMA -> this CTA's epilogue
+    unsigned long long* acc_empty = bars + 2 * kStages2 + 2;         // [2]       both epilogues -> leader's MMA
+    unsigned long long* res_bars = bars + 2 * kStages2 + 4;          // [epilogue warps][2] residual chunk landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 4 + 2 * kEpiWarps);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                         // 0 = leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_n = g.N / PN, tiles_m = (g.M + PM - 1) / PM, n_tiles = tiles_m * tiles_n;
+    const int n_kb = g.K / PK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * kEpiWarps); }
+        for (int b = 0; b < 2 * kEpiWarps; ++b) mbar_init(&res_bars[b], 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, kTmemCols2);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                              // the peer's barriers exist before anything targets them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer for this CTA's halves; one running k-block counter across all of the pair's tiles
+            int it = 0;
+            for (int tile = pair; tile < n_tiles && !*abort_flag; tile += n_pairs) {
+                const int tile_m = TILE_M(tile), tile_n = TILE_N(tile);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kStages2, use = it / kStages2;
+                    if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1, kSpin2)) { *abort_flag = 1; break; }
+                    if (*abort_flag) break;
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * (kHalfA + kHalfB));
+                    const uint32_t leader_full = map_to_cta(&full[s], 0);
+                    tma_load_2d_pair(sa + s * kHalfA, &tm_a, kb * PK, tile_m * PM + (int)rank * 128, leader_full);
+                    tma_load_2d_pair(sb + s * kHalfB, &tm_b, kb * PK, tile_n * PN + (int)rank * 128, leader_full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (leader only)
+            constexpr uint32_t idesc = umma_idesc_bf16(PM, PN);
+            int it = 0, local = 0;
+            bool ok = true;
+            GEMM_PROF(long long t_start = clock64(); long long w_full = 0; long long w_acc = 0;)
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
+                const int buf = local & 1, round = local >> 1;
+                GEMM_PROF(long long t0 = clock64();)
+                ok = (round == 0 || mbar_wait_bounded(&acc_empty[buf], (round - 1) & 1, kSpin2)) && !*abort_flag;
+                GEMM_PROF(w_acc += clock64() - t0;)
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * PN);
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kStages2, use = it / kStages2;
+                    GEMM_PROF(long long t1 = clock64();)
+                    ok = mbar_wait_bounded(&full[s], use & 1, kSpin2) && !*abort_flag;
+                    GEMM_PROF(w_full += clock64() - t1;)
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = umma_desc_sw128(sa + s * kHalfA), db = umma_desc_sw128(sb + s * kHalfB);
+#pragma unroll
+                    for (int k = 0; k < PK / 16; ++k)
+                        umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);               // both CTAs' producers may refill the stage
+                }
+                if (!ok) break;
+                umma_commit_pair(&acc_full[buf]);              // both CTAs' epilogues may read their rows
+            }
+            if (!ok) *abort_flag = 1;
+            GEMM_PROF(g.clk[blockIdx.x * 8 + 0] = clock64() - t_start; g.clk[blockIdx.x * 8 + 1] = w_full; g.clk[blockIdx.x * 8 + 2] = w_acc;)
+        }
+    } else {
+        // ---- epilogue: warp w may touch TMEM lanes 32*(w%4)..+31 = 32 rows of this CTA's half tile; the two warps that
+        //      share a lane quarter split the 256 columns
+        const int ew = warp - 2, q = warp & 3, cq = ew >> 2;         // TMEM lane quarter, column slice (kEpiCols columns)
+        unsigned char* so = sout + ew * kStageOut;                   // three [32 rows][64 B] tiles, 64-byte swizzle
+        float* sbias = reinterpret_cast<float*>(sout + kEpiWarps * kStageOut) + ew * kEpiCols;   // this warp's bias values
+        unsigned long long* res_bar = res_bars + 2 * ew;
+        const bool swiglu = g.epi == ITTAI_EPI_SWIGLU, has_res = g.residual != nullptr;
+        const int swz = (lane >> 1) & 3;                             // 64-byte swizzle of this thread's staging row
+        constexpr uint32_t kChunks = kEpiCols / 32;                  // 32-column chunks per tile for this warp
+        // With a residual, tile 0 stages the output and tiles 1-2 receive residual chunks by TMA, two chunks ahead of
+        // their use and across tile boundaries: chunk n of this warp's running sequence is chunk n % kChunks of its
+        // (n / kChunks)-th tile and lands in buffer n % 2.  Without one, the three tiles rotate as output staging.
+        auto prefetch_res = [&](uint32_t n) {
+            const int t = pair + (int)(n / kChunks) * n_pairs;
+            if (t < n_tiles) {
+                mbar_expect_tx(&res_bar[n & 1], 2048);
+                tma_load_2d(so + 2048 + (n & 1) * 2048, &tm_res, TILE_N(t) * PN + kEpiCols * cq + 32 * (int)(n % kChunks),
+                            TILE_M(t) * PM + (int)rank * 128 + q * 32, &res_bar[n & 1]);
+            }
+        };
+        if (has_res && lane == 0) { prefetch_res(0); prefetch_res(1); }
+        uint32_t cc = 0;
+        int local = 0;
+        GEMM_PROF(long long e_busy = 0; long long e_wait = 0;)
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
+            const int buf = local & 1, round = local >> 1;
+            const int tile_m = TILE_M(tile), tile_n = TILE_N(tile);
+            const int row0 = tile_m * PM + (int)rank * 128 + q * 32;  // first row of this warp
+            const int col0 = tile_n * PN + kEpiCols * cq;             // first accumulator column of this warp
+            // the bias slice does not depend on the accumulator: fetched before waiting for it
+            if (g.bias != nullptr && lane < kEpiCols / 4) *reinterpret_cast<float4*>(sbias + 4 * lane) = *reinterpret_cast<const float4*>(g.bias + col0 + 4 * lane);
+            __syncwarp();
+            bool ok = true;
+            GEMM_PROF(long long t0 = clock64();)
+            {
+                uint32_t spins = 0;
+                while (!mbar_try_wait(&acc_full[buf], round & 1)) {
+                    if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kSpin2)) { ok = false; break; }
+                }
+            }
+            if (!ok) { *abort_flag = 1; break; }
+            GEMM_PROF(long long t1 = clock64(); e_wait += t1 - t0;)
+            tc_fence_after();
+#pragma unroll 1
+            for (uint32_t ch = 0; ch < kChunks && ok; ++ch, ++cc) {
+                // 32 accumulator columns of this thread's row -> bias, activation, rounding -> 16 packed words
+                uint32_t r[32], o[16];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + kEpiCols * cq + 32 * ch), r);
+                tmem_ld_wait();
+                epilogue_pack(g, r, g.bias != nullptr ? sbias + 32 * ch : nullptr, o);
+                if (swiglu) {
+                    // 16 output columns per thread, stored straight from the row layout
+                    if (row0 + lane < g.M) {
+                        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)(row0 + lane) * g.ld_out + (col0 + 32 * ch) / 2);
+                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    continue;
+                }
+                if (has_res) {
+                    // out = bf16(residual + bf16(module output)); this thread's row piece of the TMA-filled buffer
+                    const uint32_t b = cc & 1;
+                    uint32_t spins = 0;
+                    while (!mbar_try_wait(&res_bar[b], (cc >> 1) & 1)) {
+                        if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kSpin2)) { ok = false; break; }
+                    }
+                    if (!ok) { *abort_flag = 1; break; }
+                    const unsigned char* rrow = so + 2048 + b * 2048 + lane * 64;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 rs = *reinterpret_cast<const uint4*>(rrow + ((j ^ swz) << 4));
+                        o[4 * j] = pack_bf16x2(bf_lo(rs.x) + bf_lo(o[4 * j]), bf_hi(rs.x) + bf_hi(o[4 * j]));
+                        o[4 * j + 1] = pack_bf16x2(bf_lo(rs.y) + bf_lo(o[4 * j + 1]), bf_hi(rs.y) + bf_hi(o[4 * j + 1]));
+                        o[4 * j + 2] = pack_bf16x2(bf_lo(rs.z) + bf_lo(o[4 * j + 2]), bf_hi(rs.z) + bf_hi(o[4 * j + 2]));
+                        o[4 * j + 3] = pack_bf16x2(bf_lo(rs.w) + bf_lo(o[4 * j + 3]), bf_hi(rs.w) + bf_hi(o[4 * j + 3]));
+                    }
+                    __syncwarp();                                     // every lane has consumed the buffer: refill it
+                    if (lane == 0) prefetch_res(cc + 2);
+                }
+                // the store that last used this staging tile must have finished reading it
+                unsigned char* sto = has_res ? so : so + (cc % 3u) * 2048;
+                if (lane == 0) { if (has_res) tma_store_wait_read<0>(); else tma_store_wait_read<2>(); }
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    *reinterpret_cast<uint4*>(sto + lane * 64 + ((j ^ swz) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) { tma_store_2d(&tm_out, sto, col0 + 32 * (int)ch, row0); tma_store_commit(); }
+            }
+            if (!ok) break;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[buf], 0));
+            GEMM_PROF(e_busy += clock64() - t1;)
+        }
+        if (lane == 0) tma_store_wait_all();                          // shared memory stays valid until the stores are done
+        GEMM_PROF(if (threadIdx.x == 64) { g.clk[blockIdx.x * 8 + 3] = e_busy; g.clk[blockIdx.x * 8 + 4] = e_wait; })
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            if (atomicCAS(&g.status[0], 0u, (uint32_t)ITTAI_ST_GEMM_TIMEOUT) == 0u) { g.status[1] = blockIdx.x; g.status[2] = (uint32_t)n_kb; }
+            // let copies that may still be in flight land before the shared memory is handed back
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {}
+        }
+        __syncthreads();
+    }
+    // neither CTA leaves while the other may still read its shared memory or signal its barriers
+    cluster_sync_all();
+    if (warp == 1) { __syncwarp(); tmem_dealloc_pair(tmem_base, kTmemCols2); }
+}
+
+int cuda_fail(cudaError_t e, const char* what);
+
+int gemm2_bf16_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmArgs& g, cudaStream_t st) {
+    // the epilogue stores 32-row x 32-column boxes through TMA (rows past M are dropped) and fetches the residual the same way
+    CUtensorMap tm_out, tm_res;
+    const bool swiglu = g.epi == ITTAI_EPI_SWIGLU;
+    int rc = make_tmap_bf16(&tm_out, g.out, g.M, swiglu ? g.N / 2 : g.N, g.ld_out, 32, 32);
+    if (rc != ITTAI_OK) return rc;
+    if (g.residual != nullptr) rc = make_tmap_bf16(&tm_res, g.residual, g.M, g.N, g.ld_res, 32, 32);
+    else tm_res = tm_out;
+    if (rc != ITTAI_OK) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads2);
+    cfg.dynamicSmemBytes = kSmem2;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static thread_local int attr_dev = -1, max_pairs = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem2);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm2)");
+        int n_sms = 0;
+        e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
+        cfg.gridDim = dim3(n_sms & ~1);
+        int n_clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&n_clusters, gemm2_bf16_kernel, &cfg);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveClusters(gemm2)");
+        max_pairs = n_clusters < 1 ? 1 : (n_clusters > n_sms / 2 ? n_sms / 2 : n_clusters);
+        attr_dev = dev;
+    }
+    const int tiles = ((g.M + PM - 1) / PM) * (g.N / PN);
+    cfg.gridDim = dim3(2 * (tiles < max_pairs ? tiles : max_pairs));
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, tm_a, tm_b, tm_out, tm_res, g);
+    if (e != cudaSuccess) return cuda_fail(e, "launch gemm2_bf16_kernel");
+    return ITTAI_OK;
+}
+
+}  // namespace ittai

@@ -14,7 +14,8 @@
 // abort flag, all roles fall through to the common exit and TMEM is freed.
 #include <cuda.h>
 
-#include "tcgen05.cuh"
+#include "gemm_epilogue.cuh"
+#include "tmap.h"
 
 namespace ittai {
 
@@ -25,79 +26,6 @@ constexpr uint32_t kStageBytesA = GM * GK * 2, kStageBytesB = GN * GK * 2;
 constexpr uint32_t kGemmSmem = kGemmStages * (kStageBytesA + kStageBytesB) + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr uint32_t kGemmSpin = 1u << 24;
 constexpr uint32_t kTmemCols = 512;
-
-struct GemmArgs {
-    int M, N, K;
-    int epi;                 // ITTAI_EPI_*
-    const float* bias;       // [N] or nullptr
-    const bf16* residual;    // [M, ld_res] or nullptr
-    int ld_res;
-    bf16* out;               // [M, ld_out]  (SwiGLU: N/2 columns)
-    int ld_out;
-    uint32_t* status;        // device status words
-};
-
-// GELU-tanh as the reference writes it (src/ittai/siglip/kernel.py:289-291); the hardware tanh approximation is good
-// to about 2^-11, well inside the bf16 rounding of the result.
-__device__ __forceinline__ float gelu_tanh(float y) {
-    float th;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (y + 0.044715f * y * y * y)));
-    return 0.5f * y * (1.0f + th);
-}
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// One 32-column slice of an accumulator row: bias, activation, residual, rounding, 128-bit stores.
-__device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, const uint32_t (&r)[32], int row, int col) {
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    if (g.bias != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-            const float4 b4 = *reinterpret_cast<const float4*>(g.bias + col + i);
-            v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
-        }
-    }
-    if (g.epi == ITTAI_EPI_SWIGLU) {
-        // adjacent columns are (gate, up): act = bf16(bf16(silu(bf16 gate)) * bf16 up)
-        uint32_t o[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-            const float g0 = bf16r(v[2 * i]), u0 = bf16r(v[2 * i + 1]);
-            const float g1 = bf16r(v[2 * i + 2]), u1 = bf16r(v[2 * i + 3]);
-            o[i / 2] = pack_bf16x2(bf16r(g0 / (1.0f + expf(-g0))) * u0, bf16r(g1 / (1.0f + expf(-g1))) * u1);
-        }
-        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col / 2);
-        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-        return;
-    }
-    if (g.epi == ITTAI_EPI_GELU) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(bf16r(v[i]));   // the Linear output is rounded before the activation
-    }
-    if (g.residual != nullptr) {
-        // out = bf16(residual + bf16(acc [+ bias])): the module output is rounded before the add
-        const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.ld_res + col);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 rr = rs[i];
-            const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                v[i * 8 + 2 * j] = bf_lo(w[j]) + bf16r(v[i * 8 + 2 * j]);
-                v[i * 8 + 2 * j + 1] = bf_hi(w[j]) + bf16r(v[i * 8 + 2 * j + 1]);
-            }
-        }
-    }
-    uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)row * g.ld_out + col);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-        dst[i] = make_uint4(pack_bf16x2(v[i * 8], v[i * 8 + 1]), pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]),
-                            pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]), pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]));
-}
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmArgs g) {
@@ -153,16 +81,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t idesc = umma_idesc_bf16(GM, GN);
             int it = 0, local = 0;
             bool ok = true;
+            GEMM_PROF(long long t_start = clock64(); long long w_full = 0; long long w_acc = 0;)
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1, round = local >> 1;
                 // the epilogue must have drained this accumulator (passes at once on its first use)
+                GEMM_PROF(long long t0 = clock64();)
                 ok = (round == 0 || mbar_wait_bounded(&acc_empty[buf], (round - 1) & 1, kGemmSpin)) && !*abort_flag;
+                GEMM_PROF(w_acc += clock64() - t0;)
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * GN);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kGemmStages, use = it / kGemmStages;
+                    GEMM_PROF(long long t1 = clock64();)
                     ok = mbar_wait_bounded(&full[s], use & 1, kGemmSpin) && !*abort_flag;
+                    GEMM_PROF(w_full += clock64() - t1;)
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * kStageBytesB);
@@ -175,16 +108,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 umma_commit(&acc_full[buf]);               // accumulator complete
             }
             if (!ok) *abort_flag = 1;
+            GEMM_PROF(g.clk[blockIdx.x * 8 + 0] = clock64() - t_start; g.clk[blockIdx.x * 8 + 1] = w_full; g.clk[blockIdx.x * 8 + 2] = w_acc;)
         }
     } else {
         // ---- epilogue: warp w may touch TMEM lanes 32*(w%4)..+31 = 32 rows of the tile; the two warps that share a lane
         //      quarter split the 256 columns, so every scheduler has two epilogue warps to interleave
         const int q = warp & 3, col_half = (warp - 2) >> 2;
         int local = 0;
+        GEMM_PROF(long long e_busy = 0; long long e_wait = 0;)
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             const int buf = local & 1, round = local >> 1;
             const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
             bool ok = true;
+            GEMM_PROF(long long t0 = clock64();)
             {   // bounded wait that also gives up when another role aborted
                 uint32_t spins = 0;
                 while (!mbar_try_wait(&acc_full[buf], round & 1)) {
@@ -192,6 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
             if (!ok) { *abort_flag = 1; break; }
+            GEMM_PROF(long long t1 = clock64(); e_wait += t1 - t0;)
             tc_fence_after();
             const int row = tile_m * GM + q * 32 + lane;
 #pragma unroll 1
@@ -204,7 +141,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            GEMM_PROF(e_busy += clock64() - t1;)
         }
+        GEMM_PROF(if (threadIdx.x == 64) { g.clk[blockIdx.x * 8 + 3] = e_busy; g.clk[blockIdx.x * 8 + 4] = e_wait; })
     }
     tc_fence_before();
     __syncthreads();
@@ -224,36 +163,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// Tensor map over a row-major bf16 matrix [rows, cols] with leading dimension ld: boxes of box_rows rows x 64 columns.
-static int make_tmap(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return ITTAI_E_CUDA; }
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)GK, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %d)", (int)r, rows, cols, ld); return ITTAI_E_CUDA; }
-    return ITTAI_OK;
-}
+int gemm2_bf16_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmArgs& g, cudaStream_t st);   // gemm2_sm100.cu
 
 int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     if (!a || !a->a || !a->w || !a->out || !a->status) { set_error("null pointer in IttaiGemm"); return ITTAI_E_ARG; }
@@ -271,10 +181,12 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
         set_error("gemm operands must be 16-byte aligned with leading dimensions that are multiples of 8");
         return ITTAI_E_ARG;
     }
+    // more than one 128-row tile: the two-SM kernel (each CTA of a pair loads 128 rows of A and 128 rows of W per stage)
+    const bool pair = a->m > GM;
     CUtensorMap tm_a, tm_b;
-    int rc = make_tmap(&tm_a, a->a, a->m, a->k, ld_a, GM);
+    int rc = make_tmap_bf16(&tm_a, a->a, a->m, a->k, ld_a, GM);
     if (rc != ITTAI_OK) return rc;
-    rc = make_tmap(&tm_b, a->w, a->n, a->k, ld_w, GN);
+    rc = make_tmap_bf16(&tm_b, a->w, a->n, a->k, ld_w, pair ? GN / 2 : GN);
     if (rc != ITTAI_OK) return rc;
     static thread_local int attr_dev = -1, n_sms = 0;
     int dev = 0;
@@ -294,6 +206,11 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.out = reinterpret_cast<bf16*>(a->out);
     g.ld_out = ld_out;
     g.status = a->status;
+#ifdef ITTAI_GEMM_PROFILE
+    extern long long* g_gemm_clk;
+    g.clk = g_gemm_clk;
+#endif
+    if (pair) return gemm2_bf16_launch(tm_a, tm_b, g, st);
     const int tiles = ((a->m + GM - 1) / GM) * (a->n / GN);
     gemm_bf16_kernel<<<tiles < n_sms ? tiles : n_sms, kGemmThreads, kGemmSmem, st>>>(tm_a, tm_b, g);
     cudaError_t e = cudaGetLastError();

@@ -25,16 +25,17 @@ inline EncodeTiledFn tmap_encode_fn() {
     return fn;
 }
 
-// [rows, cols] bf16 with leading dimension ld (elements); boxes of box_rows rows x 64 columns; out-of-range reads give 0.
-inline int make_tmap_bf16(CUtensorMap* tm, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+// [rows, cols] bf16 with leading dimension ld (elements); boxes of box_rows rows x box_cols columns (64 columns with the
+// 128-byte swizzle, 32 columns with the 64-byte swizzle); out-of-range reads give 0, out-of-range writes are dropped.
+inline int make_tmap_bf16(CUtensorMap* tm, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols = 64) {
     EncodeTiledFn fn = tmap_encode_fn();
     if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return ITTAI_E_CUDA; }
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld); return ITTAI_E_CUDA; }
     return ITTAI_OK;

@@ -58,6 +58,8 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Orders this thread's earlier generic-proxy writes before later async-proxy (TMA) accesses to the same memory.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Same, restricted to this CTA's shared memory: enough before a TMA store or an MMA reads what this thread just wrote there.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // The compute threads' view: ring base and the count of entries they have released (uniform over those threads).
 struct Stream {
