@@ -5,6 +5,7 @@
 // Tensor-core path: warp-level mma.sync m16n8k16 (bf16 in, fp32 accumulate) on ldmatrix fragments from swizzled
 // shared memory.  Attention is a few percent of SigLIP's FLOPs and a third of a 4k prefill's.
 #include "common.cuh"
+#include "launch.h"
 
 namespace ittai {
 
@@ -51,6 +52,8 @@ __device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, long long 
 
 template <int HD, bool CAUSAL, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) attn_fwd_kernel(const AttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int kAttnBM = 16 * WARPS, kAttnThreads = 32 * WARPS;
     // shared memory: Q tile, then two (K, V) tile pairs so that block kb+1 streams in while block kb is multiplied
     extern __shared__ __align__(128) unsigned char attn_smem[];
@@ -185,6 +188,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_fwd_kernel(const AttnArgs a) 
 constexpr int kShortKeys = 256;
 template <int HD>
 __global__ void __launch_bounds__(512) attn_short_kernel(const AttnArgs a, int warps) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char attn_smem[];
     const int4 sinfo = a.seqs[blockIdx.z];
     const int q_len = sinfo.y, kv_len = sinfo.w;
@@ -302,7 +307,7 @@ static int attn_short_launch(const AttnArgs& a, int max_q_len, int n_heads, int 
         if (e != cudaSuccess) return (int)e;
         attr_dev = dev;
     }
-    attn_short_kernel<64><<<dim3(1, n_heads, n_seqs), warps * 32, smem, st>>>(a, warps);
+    launch_pdl(attn_short_kernel<64>, dim3(1, n_heads, n_seqs), dim3(warps * 32), smem, st, 1, a, warps);
     return 0;
 }
 
@@ -318,7 +323,7 @@ static int attn_launch(const AttnArgs& a, int max_q_len, int n_heads, int n_seqs
         if (e != cudaSuccess) return (int)e;
         attr_dev = dev;
     }
-    attn_fwd_kernel<HD, CAUSAL, WARPS><<<grid, WARPS * 32, smem, st>>>(a);
+    launch_pdl(attn_fwd_kernel<HD, CAUSAL, WARPS>, grid, dim3(WARPS * 32), smem, st, 1, a);
     return 0;
 }
 

@@ -14,6 +14,7 @@
 // TMEM is freed.
 #include "tcgen05.cuh"
 #include "tmap.h"
+#include "launch.h"
 
 namespace ittai {
 
@@ -70,8 +71,9 @@ __device__ __forceinline__ uint32_t p_col(int c0) { return c0 < kTcHalf ? (uint3
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const AttnTcArgs a) {
+    pdl_trigger();
     const int head = blockIdx.x, mt = blockIdx.y, kvh = head / a.group;
-    const int4 sinfo = a.seqs[blockIdx.z];
+    const int4 sinfo = a.seqs[blockIdx.z];                 // written by the host long before: safe ahead of pdl_wait
     const int q_len = sinfo.y, kv_len = sinfo.w;
     if (mt * 128 >= q_len) return;                         // the whole CTA: nothing allocated yet
 
@@ -99,6 +101,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         *abort_flag = 0;
         fence_mbar_init();
         // the loads start before TMEM is allocated; nobody else touches the barriers until the CTA-wide sync below
+        pdl_wait();                                        // Q, K, V come from the kernel before this one
         mbar_expect_tx(bar_load, 128 * 128 + kTcKeys * 128);
         tma_load_2d(sm + kOffQ, &tm_q, head * kTcHD, sinfo.x + mt * 128, bar_load);
         tma_load_2d(sm + kOffK, &tm_k, kvh * kTcHD, sinfo.z, bar_load);
@@ -109,6 +112,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
     ATTN_STAMP(1);
 
@@ -150,11 +154,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int c_lo = hf * kTcHalf, c_hi = min(c_lo + kTcHalf, n_keys);
         // Both passes walk this warp's score columns 16 at a time with the next chunk's TMEM load in flight.
         // ---- pass 1: row maximum
-        float mx = -INFINITY;
+        float mx = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains: the row maximum is latency-bound
         auto take_max = [&](const uint32_t (&v)[16], int c0) {
             if (c0 + 16 <= kv_len) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < 16; i += 4) {
+                    mx = fmaxf(mx, __uint_as_float(v[i])); mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(v[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) if (c0 + i < kv_len) mx = fmaxf(mx, __uint_as_float(v[i]));
@@ -174,6 +181,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 take_max(vb, c0 + 16);
             }
         }
+        mx = fmaxf(fmaxf(mx, mx1), fmaxf(mx2, mx3));
         xmax[hf * 128 + r] = mx;
         mbar_arrive_cta(bar_mx);
         ok = mbar_wait_abortable(bar_mx, 0, abort_flag) && mbar_wait_abortable(bar_v, 0, abort_flag);
@@ -200,7 +208,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 for (int i = 0; i < 16; ++i) p[i] = c0 + i < kv_len ? ex2_fast(fmaf(__uint_as_float(v[i]), a.scale_log2, -mb)) : 0.f;
             }
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) { l0 += p[i]; l1 += p[i + 1]; w[i >> 1] = pack_bf16x2(p[i], p[i + 1]); }
+            for (int i = 0; i < 16; i += 2) { l0 += p[i]; l1 += p[i + 1]; w[i >> 1] = pack_bf16x2_alu(p[i], p[i + 1]); }
             tmem_st_32x8(t_row + p_col(c0), w);
         };
         if (live && c_lo < c_hi) {
@@ -304,8 +312,7 @@ int attn_tc_launch(const IttaiAttention* p, cudaStream_t st) {
 #ifdef ITTAI_ATTN_PROFILE
     a.clk = nullptr;
 #endif
-    attn_tc_kernel<<<dim3(p->n_heads, (p->max_q_len + 127) / 128, p->n_seqs), kTcThreads, kTcSmem, st>>>(tq, tk, tv, a);
-    const cudaError_t e = cudaGetLastError();
+    const cudaError_t e = launch_pdl(attn_tc_kernel, dim3(p->n_heads, (p->max_q_len + 127) / 128, p->n_seqs), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a);
     return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_tc_kernel");
 }
 

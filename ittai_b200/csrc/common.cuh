@@ -141,6 +141,19 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return d;
 }
 
+// The same roundings on the integer pipe, for code whose conversion pipe is the bottleneck (it shares a quarter-rate
+// unit with ex2 / tanh).  bf16r_bits: fp32 bits rounded to nearest-even bf16, still as fp32 bits (finite inputs).
+__device__ __forceinline__ uint32_t bf16r_bits(uint32_t u) { return (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u; }
+// Two non-negative finite floats -> packed bf16 pair, round half up (differs from nearest-even only on exact ties).
+__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+
+// Programmatic dependent launch (see launch.h): let the next kernel of the stream start launching / wait until every
+// kernel this one depends on has completed and its writes are visible.  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 struct Waiter {
     uint32_t* sync;     // sync[1] = abort flag
     uint32_t* status;

@@ -16,6 +16,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "tmap.h"
+#include "launch.h"
 
 namespace ittai {
 
@@ -127,11 +128,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
     }
+    pdl_trigger();
     if (warp == 1) tmem_alloc_pair(tmem_slot, kTmemCols2);
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();                                              // the peer's barriers exist before anything targets them
     tc_fence_after();
+    pdl_wait();                                                      // operands come from the kernels before this one
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -312,15 +315,6 @@ int gemm2_bf16_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Ge
     if (g.residual != nullptr) rc = make_tmap_bf16(&tm_res, g.residual, g.M, g.N, g.ld_res, 32, 32);
     else tm_res = tm_out;
     if (rc != ITTAI_OK) return rc;
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(kThreads2);
-    cfg.dynamicSmemBytes = kSmem2;
-    cfg.stream = st;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
     static thread_local int attr_dev = -1, max_pairs = 0;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -330,6 +324,14 @@ int gemm2_bf16_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Ge
         int n_sms = 0;
         e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.blockDim = dim3(kThreads2);
+        cfg.dynamicSmemBytes = kSmem2;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
         cfg.gridDim = dim3(n_sms & ~1);
         int n_clusters = 0;
         e = cudaOccupancyMaxActiveClusters(&n_clusters, gemm2_bf16_kernel, &cfg);
@@ -338,8 +340,7 @@ int gemm2_bf16_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const Ge
         attr_dev = dev;
     }
     const int tiles = ((g.M + PM - 1) / PM) * (g.N / PN);
-    cfg.gridDim = dim3(2 * (tiles < max_pairs ? tiles : max_pairs));
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, tm_a, tm_b, tm_out, tm_res, g);
+    const cudaError_t e = launch_pdl(gemm2_bf16_kernel, dim3(2 * (tiles < max_pairs ? tiles : max_pairs)), dim3(kThreads2), kSmem2, st, 2, tm_a, tm_b, tm_out, tm_res, g);
     if (e != cudaSuccess) return cuda_fail(e, "launch gemm2_bf16_kernel");
     return ITTAI_OK;
 }

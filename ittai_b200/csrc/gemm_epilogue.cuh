@@ -92,31 +92,47 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, const uint32_t
 // columns (shared or global memory) or is null.  The caller adds the residual afterwards, on the rounded values, as the
 // eager modules do.
 __device__ __forceinline__ void epilogue_pack(const GemmArgs& g, const uint32_t (&r)[32], const float* bias32, uint32_t (&o)[16]) {
-    float v[32];
+    // arithmetic on fp32 pairs: one packed instruction does two columns
+    float2 v[16];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 16; ++i) v[i] = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
     if (bias32 != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-            const float4 b4 = *reinterpret_cast<const float4*>(bias32 + i);
-            v[i] += b4.x; v[i + 1] += b4.y; v[i + 2] += b4.z; v[i + 3] += b4.w;
+        for (int i = 0; i < 16; i += 2) {
+            const float4 b4 = *reinterpret_cast<const float4*>(bias32 + 2 * i);
+            v[i] = __fadd2_rn(v[i], make_float2(b4.x, b4.y));
+            v[i + 1] = __fadd2_rn(v[i + 1], make_float2(b4.z, b4.w));
         }
     }
     if (g.epi == ITTAI_EPI_SWIGLU) {
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-            const float g0 = bf16r(v[2 * i]), u0 = bf16r(v[2 * i + 1]);
-            const float g1 = bf16r(v[2 * i + 2]), u1 = bf16r(v[2 * i + 3]);
+            const float g0 = bf16r(v[i].x), u0 = bf16r(v[i].y);
+            const float g1 = bf16r(v[i + 1].x), u1 = bf16r(v[i + 1].y);
             o[i / 2] = pack_bf16x2(bf16r(g0 / (1.0f + expf(-g0))) * u0, bf16r(g1 / (1.0f + expf(-g1))) * u1);
         }
         return;
     }
     if (g.epi == ITTAI_EPI_GELU) {
+        // 0.5 y (1 + tanh(0.79788456 (y + 0.044715 y^3))) on the Linear output rounded to bf16, written as
+        // hy + hy * tanh(y * (c0 + c1 y^2)) with hy = y / 2
+        const float2 c0 = make_float2(0.7978845608028654f, 0.7978845608028654f);
+        const float2 c1 = make_float2(0.7978845608028654f * 0.044715f, 0.7978845608028654f * 0.044715f);
+        const float2 half2 = make_float2(0.5f, 0.5f);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(bf16r(v[i]));
+        for (int i = 0; i < 16; ++i) {
+            // rounded on the integer pipe: the conversion unit is busy with tanh and the output packing
+            const float2 y = make_float2(__uint_as_float(bf16r_bits(__float_as_uint(v[i].x))), __uint_as_float(bf16r_bits(__float_as_uint(v[i].y))));
+            const float2 u = __fmul2_rn(y, __ffma2_rn(__fmul2_rn(y, y), c1, c0));
+            float2 th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th.x) : "f"(u.x));
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th.y) : "f"(u.y));
+            const float2 hy = __fmul2_rn(y, half2);
+            v[i] = __ffma2_rn(hy, th, hy);
+        }
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+    for (int i = 0; i < 16; ++i) o[i] = pack_bf16x2(v[i].x, v[i].y);
 }
 
 }  // namespace ittai

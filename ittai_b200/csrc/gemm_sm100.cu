@@ -16,6 +16,7 @@
 
 #include "gemm_epilogue.cuh"
 #include "tmap.h"
+#include "launch.h"
 
 namespace ittai {
 
@@ -53,10 +54,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
     }
+    pdl_trigger();
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();                                                      // operands come from the kernels before this one
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -212,8 +215,7 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
 #endif
     if (pair) return gemm2_bf16_launch(tm_a, tm_b, g, st);
     const int tiles = ((a->m + GM - 1) / GM) * (a->n / GN);
-    gemm_bf16_kernel<<<tiles < n_sms ? tiles : n_sms, kGemmThreads, kGemmSmem, st>>>(tm_a, tm_b, g);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(gemm_bf16_kernel, dim3(tiles < n_sms ? tiles : n_sms), dim3(kGemmThreads), kGemmSmem, st, 1, tm_a, tm_b, g);
     if (e != cudaSuccess) return cuda_fail(e, "launch gemm_bf16_kernel");
     return ITTAI_OK;
 }

@@ -6,6 +6,7 @@
 // src/ittai/qwen3/base.py:59-78, :84-109; src/ittai/siglip/kernel.py:266-364).  Here they are separate passes so that
 // every rounding point is the eager module's (norm output rounded to bf16 before the Linear reads it).
 #include "common.cuh"
+#include "launch.h"
 
 namespace ittai {
 
@@ -14,6 +15,8 @@ constexpr int kRowThreads = 256;     // 8 rows per CTA
 // y = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * gain), width 1024.
 __global__ void __launch_bounds__(kRowThreads) rmsnorm_rows_kernel(const bf16* __restrict__ x, int ld_x, const bf16* __restrict__ gain,
                                                                      bf16* __restrict__ y, int ld_y, int rows, float eps) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     uint4 v[4];
@@ -40,47 +43,70 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_rows_kernel(const bf16* _
 }
 
 // y = bf16((x - mean) * rsqrt(var + eps) * gain + beta); width a multiple of 8, at most NCH * 256; gain/beta fp32.
+// A warp walks rows with a grid stride, holding its slice of gain and beta in registers (re-reading them per row costs
+// four times the row's own bytes) and loading the next row while it reduces the current one.
 template <int NCH>
 __global__ void __launch_bounds__(kRowThreads) layernorm_rows_kernel(const bf16* __restrict__ x, int ld_x, const float* __restrict__ gain,
                                                                        const float* __restrict__ beta, bf16* __restrict__ y, int ld_y,
                                                                        int rows, int width, float eps) {
-    const int row = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int n_chunks = width / 8, stride = gridDim.x * (kRowThreads / 32);
+    int row = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5);
     if (row >= rows) return;
-    const int n_chunks = width / 8;
-    float v[NCH][8];
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-        const int ch = lane + 32 * i;
-        if (ch < n_chunks) {
-            const uint4 q = *reinterpret_cast<const uint4*>(x + (size_t)row * ld_x + ch * 8);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { v[i][2 * j] = bf_lo(w[j]); v[i][2 * j + 1] = bf_hi(w[j]); s += v[i][2 * j] + v[i][2 * j + 1]; }
-        }
-    }
-    const float mean = warp_sum(s) / (float)width;
-    float sq = 0.f;
-#pragma unroll
-    for (int i = 0; i < NCH; ++i)
-        if (lane + 32 * i < n_chunks) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; sq += d * d; }
-        }
-    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    float gg[NCH][8], bb[NCH][8];
+    uint4 cur[NCH], nxt[NCH];
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
         const int ch = lane + 32 * i;
         if (ch < n_chunks) {
             const float4 g0 = *reinterpret_cast<const float4*>(gain + ch * 8), g1 = *reinterpret_cast<const float4*>(gain + ch * 8 + 4);
             const float4 b0 = *reinterpret_cast<const float4*>(beta + ch * 8), b1 = *reinterpret_cast<const float4*>(beta + ch * 8 + 4);
-            const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                o[j] = pack_bf16x2((v[i][2 * j] - mean) * rstd * gg[2 * j] + bb[2 * j], (v[i][2 * j + 1] - mean) * rstd * gg[2 * j + 1] + bb[2 * j + 1]);
-            *reinterpret_cast<uint4*>(y + (size_t)row * ld_y + ch * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            gg[i][0] = g0.x; gg[i][1] = g0.y; gg[i][2] = g0.z; gg[i][3] = g0.w; gg[i][4] = g1.x; gg[i][5] = g1.y; gg[i][6] = g1.z; gg[i][7] = g1.w;
+            bb[i][0] = b0.x; bb[i][1] = b0.y; bb[i][2] = b0.z; bb[i][3] = b0.w; bb[i][4] = b1.x; bb[i][5] = b1.y; bb[i][6] = b1.z; bb[i][7] = b1.w;
+            cur[i] = *reinterpret_cast<const uint4*>(x + (size_t)row * ld_x + ch * 8);
         }
+    }
+    const float inv_w = 1.0f / (float)width;
+    for (; row < rows; row += stride) {
+        const int next = row + stride;
+        if (next < rows) {
+#pragma unroll
+            for (int i = 0; i < NCH; ++i)
+                if (lane + 32 * i < n_chunks) nxt[i] = *reinterpret_cast<const uint4*>(x + (size_t)next * ld_x + (lane + 32 * i) * 8);
+        }
+        float v[NCH][8];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i)
+            if (lane + 32 * i < n_chunks) {
+                const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { v[i][2 * j] = bf_lo(w[j]); v[i][2 * j + 1] = bf_hi(w[j]); s += v[i][2 * j] + v[i][2 * j + 1]; }
+            }
+        const float mean = warp_sum(s) * inv_w;
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i)
+            if (lane + 32 * i < n_chunks) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; sq += d * d; }
+            }
+        const float rstd = 1.0f / sqrtf(warp_sum(sq) * inv_w + eps);
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int ch = lane + 32 * i;
+            if (ch < n_chunks) {
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    o[j] = pack_bf16x2((v[i][2 * j] - mean) * rstd * gg[i][2 * j] + bb[i][2 * j], (v[i][2 * j + 1] - mean) * rstd * gg[i][2 * j + 1] + bb[i][2 * j + 1]);
+                *reinterpret_cast<uint4*>(y + (size_t)row * ld_y + ch * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) cur[i] = nxt[i];
     }
 }
 
@@ -94,6 +120,8 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
                                                                         const int* __restrict__ slot,
                                                                         bf16* __restrict__ kc, bf16* __restrict__ vc, int n_tokens,
                                                                         int kv_cap, float eps) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int HD = ITTAI_Q3_HD, NKV = ITTAI_Q3_NKV, DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV;
     const int gw = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int t = gw >> 5, head = gw & 31;
@@ -136,6 +164,8 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
 // order, the order a Conv2d weight flattens to (reference src/ittai/siglip/kernel.py:633-637).  One thread per
 // 4 consecutive pixels of a patch row.
 __global__ void im2col_kernel(const float* __restrict__ px, bf16* __restrict__ out, int B, int H, int W, int p) {
+    pdl_trigger();
+    pdl_wait();
     const int gw = W / p, gh = H / p, kp = 3 * p * p;
     const size_t total = (size_t)B * gh * gw * kp / 4;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -152,6 +182,8 @@ __global__ void im2col_kernel(const float* __restrict__ px, bf16* __restrict__ o
 // Embedding rows: out[t] = table[ids[t]], width 1024 (reference src/ittai/qwen3/base.py:147-162).
 __global__ void __launch_bounds__(kRowThreads) embed_rows_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
                                                                    bf16* __restrict__ out, int rows, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     int id = ids[row];
@@ -166,6 +198,8 @@ __global__ void __launch_bounds__(kRowThreads) embed_rows_kernel(const int* __re
 // (reference src/ittai/qwen3/base.py:131-145).  One warp per sequence; rows[s] is the last token's row.
 __global__ void __launch_bounds__(kRowThreads) final_pool_kernel(const bf16* __restrict__ h, const int* __restrict__ rows,
                                                                    const bf16* __restrict__ gain, float* __restrict__ out, int n_seq, float eps) {
+    pdl_trigger();
+    pdl_wait();
     const int s = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (s >= n_seq) return;
     const bf16* x = h + (size_t)rows[s] * 1024;
@@ -195,7 +229,7 @@ using namespace ittai;
 
 extern "C" int ittai_rmsnorm_rows(const void* x, int ld_x, const void* gain, void* y, int ld_y, int rows, float eps, void* stream) {
     if (!x || !gain || !y || rows < 1 || ld_x % 8 || ld_y % 8) { set_error("rmsnorm_rows: bad argument"); return ITTAI_E_ARG; }
-    rmsnorm_rows_kernel<<<row_grid(rows), kRowThreads, 0, (cudaStream_t)stream>>>((const bf16*)x, ld_x, (const bf16*)gain, (bf16*)y, ld_y, rows, eps);
+    launch_pdl(rmsnorm_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, (cudaStream_t)stream, 1, (const bf16*)x, ld_x, (const bf16*)gain, (bf16*)y, ld_y, rows, eps);
     return launched("rmsnorm_rows_kernel");
 }
 
@@ -205,11 +239,12 @@ extern "C" int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, c
         set_error("layernorm_rows: width must be a multiple of 8 up to 2048");
         return ITTAI_E_ARG;
     }
-    const int grid = row_grid(rows);
+    // a few rows per warp, so that the parameter registers are worth loading: four CTAs per SM
+    const int grid = row_grid(rows) < 148 * 4 ? row_grid(rows) : 148 * 4;
     cudaStream_t st = (cudaStream_t)stream;
-    if (width <= 768) layernorm_rows_kernel<3><<<grid, kRowThreads, 0, st>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
-    else if (width <= 1280) layernorm_rows_kernel<5><<<grid, kRowThreads, 0, st>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
-    else layernorm_rows_kernel<8><<<grid, kRowThreads, 0, st>>>((const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
+    if (width <= 768) launch_pdl(layernorm_rows_kernel<3>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
+    else if (width <= 1280) launch_pdl(layernorm_rows_kernel<5>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
+    else launch_pdl(layernorm_rows_kernel<8>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
     return launched("layernorm_rows_kernel");
 }
 
@@ -217,7 +252,7 @@ extern "C" int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void
                                            const int32_t* seq, const int32_t* slot, void* kcache_layer, void* vcache_layer,
                                            int n_tokens, int kv_cap, float eps, void* stream) {
     if (!qkv || !qn || !kn || !rope || !pos || !seq || !slot || !kcache_layer || !vcache_layer || n_tokens < 1) { set_error("qk_rope_scatter: bad argument"); return ITTAI_E_ARG; }
-    qk_rope_scatter_kernel<<<row_grid((long long)n_tokens * 32), kRowThreads, 0, (cudaStream_t)stream>>>(
+    launch_pdl(qk_rope_scatter_kernel, dim3(row_grid((long long)n_tokens * 32)), dim3(kRowThreads), 0, (cudaStream_t)stream, 1, 
         (bf16*)qkv, (const bf16*)qn, (const bf16*)kn, (const bf16*)rope, pos, seq, slot, (bf16*)kcache_layer, (bf16*)vcache_layer, n_tokens, kv_cap, eps);
     return launched("qk_rope_scatter_kernel");
 }
@@ -226,18 +261,18 @@ extern "C" int ittai_siglip_im2col(const float* pixels, void* patches, int batch
     if (!pixels || !patches || batch < 1 || patch % 4 || height % patch || width % patch) { set_error("im2col: bad argument"); return ITTAI_E_ARG; }
     const size_t total = (size_t)batch * height * width * 3 / 4;
     const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    im2col_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(pixels, (bf16*)patches, batch, height, width, patch);
+    launch_pdl(im2col_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, 1, pixels, (bf16*)patches, batch, height, width, patch);
     return launched("im2col_kernel");
 }
 
 extern "C" int ittai_embed_rows(const int32_t* ids, const void* table, void* out, int rows, int vocab, void* stream) {
     if (!ids || !table || !out || rows < 1 || vocab < 1) { set_error("embed_rows: bad argument"); return ITTAI_E_ARG; }
-    embed_rows_kernel<<<row_grid(rows), kRowThreads, 0, (cudaStream_t)stream>>>(ids, (const bf16*)table, (bf16*)out, rows, vocab);
+    launch_pdl(embed_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, (cudaStream_t)stream, 1, ids, (const bf16*)table, (bf16*)out, rows, vocab);
     return launched("embed_rows_kernel");
 }
 
 extern "C" int ittai_qwen3_final_pool(const void* h, const int32_t* rows, const void* gain, float* out, int n_seq, float eps, void* stream) {
     if (!h || !rows || !gain || !out || n_seq < 1) { set_error("final_pool: bad argument"); return ITTAI_E_ARG; }
-    final_pool_kernel<<<row_grid(n_seq), kRowThreads, 0, (cudaStream_t)stream>>>((const bf16*)h, rows, (const bf16*)gain, out, n_seq, eps);
+    launch_pdl(final_pool_kernel, dim3(row_grid(n_seq)), dim3(kRowThreads), 0, (cudaStream_t)stream, 1, (const bf16*)h, rows, (const bf16*)gain, out, n_seq, eps);
     return launched("final_pool_kernel");
 }
