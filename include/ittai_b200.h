@@ -209,10 +209,12 @@ typedef struct IttaiAttention {
     const int32_t* seqs;   /* [n_seqs][4] device: first q row, q rows, first k/v row, k/v rows */
     int32_t n_seqs, n_heads, group, head_dim, causal, max_q_len;
     int32_t max_kv_len;    /* largest kv_rows over the sequences, or 0 if unknown (enables the short-sequence kernel) */
-    /* The tensor-memory kernel (head_dim 64, dense, 65..256 queries and at most 224 keys per sequence, heads adjacent in
-     * a row: q_head = k_head = v_head = 64, k_seq = v_seq = 0) addresses q, k and v through TMA tensor maps and needs the
-     * row counts of the matrices they point into, plus status words for its bounded waits.  Leave the three at 0/NULL
-     * to stay on the register-tile kernels. */
+    /* The tensor-memory kernels address q, k and v through TMA tensor maps and need the row counts of the matrices they
+     * point into, plus status words for their bounded waits; leave the three at 0/NULL to stay on the register-tile
+     * kernels.  Covered: head_dim 64, dense, 65..256 queries and at most 224 keys per sequence, heads adjacent in a row
+     * (q_head = k_head = v_head = 64, k_seq = v_seq = 0); and head_dim 128 with a key loop, causal or dense, q_head = 128,
+     * keys and values as dense rows (k_row = v_row = 128, head and sequence strides multiples of 128, equal for k and v:
+     * the cache layout), more than 64 queries in some sequence. */
     int32_t q_rows_total;  /* rows of the matrix behind q (every sequence's q_row0 + q rows lies inside) */
     int32_t kv_rows_total; /* rows of the matrices behind k and v */
     int32_t reserved0;

@@ -331,6 +331,8 @@ void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 bool attn_tc_supported(const IttaiAttention* p);          // attention_sm100.cu
 int attn_tc_launch(const IttaiAttention* p, cudaStream_t st);
+bool attn_fa_supported(const IttaiAttention* p);          // attention_fa_sm100.cu
+int attn_fa_launch(const IttaiAttention* p, cudaStream_t st);
 
 }  // namespace ittai
 
@@ -343,6 +345,7 @@ extern "C" int ittai_attention_launch(const IttaiAttention* p, void* stream) {
     const long long strides[] = {p->q_row, p->q_head, p->k_row, p->k_head, p->k_seq, p->v_row, p->v_head, p->v_seq, p->o_row};
     for (long long s : strides) if (s % 8) { set_error("attention: strides must be multiples of 8 elements"); return ITTAI_E_ARG; }
     if (attn_tc_supported(p)) return attn_tc_launch(p, (cudaStream_t)stream);
+    if (attn_fa_supported(p)) return attn_fa_launch(p, (cudaStream_t)stream);
     AttnArgs a;
     a.q = (const bf16*)p->q; a.k = (const bf16*)p->k; a.v = (const bf16*)p->v; a.o = (bf16*)p->o;
     a.q_row = p->q_row; a.q_head = p->q_head; a.k_row = p->k_row; a.k_head = p->k_head; a.k_seq = p->k_seq;

@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_rows_kernel(const bf16*
 // Qwen3 prefill: per token and head, RMSNorm over the 128 head dims + half-split RoPE in bf16 steps (the arithmetic of
 // the decode phase), Q rotated in place in the qkv matrix, K and V written to cache row slot[t] of sequence seq[t]
 // (the rotary position pos[t] and the cache row differ when sequences are packed into one cache).
-// One warp per (token, head): heads 0..15 = q, 16..23 = k, 24..31 = v.
+// Eight lanes per (token, head), four heads per warp: heads 0..15 = q, 16..23 = k, 24..31 = v.  A lane owns elements
+// 8*sub .. 8*sub+7 and their rotation partners 64 + the same, as two 16-byte accesses.
 __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ qn,
                                                                         const bf16* __restrict__ kn, const bf16* __restrict__ rope,
                                                                         const int* __restrict__ pos, const int* __restrict__ seq,
@@ -122,42 +123,54 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
                                                                         int kv_cap, float eps) {
     pdl_trigger();
     pdl_wait();
-    constexpr int HD = ITTAI_Q3_HD, NKV = ITTAI_Q3_NKV, DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV;
+    constexpr int HD = ITTAI_Q3_HD, NKV = ITTAI_Q3_NKV, DQKV = ITTAI_Q3_DQKV;
     const int gw = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    const int t = gw >> 5, head = gw & 31;
+    const int t = gw >> 3, head = (gw & 7) * 4 + (lane >> 3), sub = lane & 7;
     if (t >= n_tokens) return;
     bf16* row = qkv + (size_t)t * DQKV + head * HD;
     const int p = pos[t], b = seq[t], sl = slot[t];   // rotary position, cache sequence, cache row
-    // elements 2*lane, 2*lane+1 and their rotation partners 64 + the same
-    const uint32_t ua = *reinterpret_cast<const uint32_t*>(row + 2 * lane), ub = *reinterpret_cast<const uint32_t*>(row + HD / 2 + 2 * lane);
-    if (head >= 24) {
-        const int g = head - 24;
-        bf16* dst = vc + (((size_t)b * NKV + g) * kv_cap + sl) * HD;
-        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = ua;
-        *reinterpret_cast<uint32_t*>(dst + HD / 2 + 2 * lane) = ub;
+    const uint4 ua = *reinterpret_cast<const uint4*>(row + 8 * sub), ub = *reinterpret_cast<const uint4*>(row + HD / 2 + 8 * sub);
+    if (head >= 24) {                                  // a warp's four heads are all q, all k or all v
+        bf16* dst = vc + (((size_t)b * NKV + (head - 24)) * kv_cap + sl) * HD;
+        *reinterpret_cast<uint4*>(dst + 8 * sub) = ua;
+        *reinterpret_cast<uint4*>(dst + HD / 2 + 8 * sub) = ub;
         return;
     }
     const bool is_k = head >= 16;
     const bf16* gain = is_k ? kn : qn;
-    float x[4] = {bf_lo(ua), bf_hi(ua), bf_lo(ub), bf_hi(ub)};
-    const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
-    const float rstd = 1.0f / sqrtf(ss * (1.0f / HD) + eps);
-    const uint32_t ga = *reinterpret_cast<const uint32_t*>(gain + 2 * lane), gb = *reinterpret_cast<const uint32_t*>(gain + HD / 2 + 2 * lane);
-    x[0] = bf16r(bf16r(x[0] * rstd) * bf_lo(ga)); x[1] = bf16r(bf16r(x[1] * rstd) * bf_hi(ga));
-    x[2] = bf16r(bf16r(x[2] * rstd) * bf_lo(gb)); x[3] = bf16r(bf16r(x[3] * rstd) * bf_hi(gb));
+    const uint4 ga = *reinterpret_cast<const uint4*>(gain + 8 * sub), gb = *reinterpret_cast<const uint4*>(gain + HD / 2 + 8 * sub);
     const bf16* rp = rope + (size_t)p * HD;
-    const uint32_t cw = *reinterpret_cast<const uint32_t*>(rp + 2 * lane), sw = *reinterpret_cast<const uint32_t*>(rp + HD / 2 + 2 * lane);
-    float lo[2], hi[2];
+    const uint4 cw = *reinterpret_cast<const uint4*>(rp + 8 * sub), sw = *reinterpret_cast<const uint4*>(rp + HD / 2 + 8 * sub);
+    const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+    const uint32_t wga[4] = {ga.x, ga.y, ga.z, ga.w}, wgb[4] = {gb.x, gb.y, gb.z, gb.w};
+    const uint32_t wc[4] = {cw.x, cw.y, cw.z, cw.w}, ws[4] = {sw.x, sw.y, sw.z, sw.w};
+    float xa[8], xb[8], ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float cs = j ? bf_hi(cw) : bf_lo(cw), sn = j ? bf_hi(sw) : bf_lo(sw);
-        lo[j] = bf16r(bf16r(x[j] * cs) + bf16r(-x[j + 2] * sn));
-        hi[j] = bf16r(bf16r(x[j + 2] * cs) + bf16r(x[j] * sn));
+    for (int j = 0; j < 4; ++j) {
+        xa[2 * j] = bf_lo(wa[j]); xa[2 * j + 1] = bf_hi(wa[j]); xb[2 * j] = bf_lo(wb[j]); xb[2 * j + 1] = bf_hi(wb[j]);
+        ss += xa[2 * j] * xa[2 * j] + xa[2 * j + 1] * xa[2 * j + 1] + xb[2 * j] * xb[2 * j] + xb[2 * j + 1] * xb[2 * j + 1];
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // the 8 lanes of this head
+    const float rstd = 1.0f / sqrtf(ss * (1.0f / HD) + eps);
+    uint32_t olo[4], ohi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float lo[2], hi[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float g0 = h ? bf_hi(wga[j]) : bf_lo(wga[j]), g1 = h ? bf_hi(wgb[j]) : bf_lo(wgb[j]);
+            const float cs = h ? bf_hi(wc[j]) : bf_lo(wc[j]), sn = h ? bf_hi(ws[j]) : bf_lo(ws[j]);
+            const float x0 = bf16r(bf16r(xa[2 * j + h] * rstd) * g0), x1 = bf16r(bf16r(xb[2 * j + h] * rstd) * g1);
+            lo[h] = bf16r(bf16r(x0 * cs) + bf16r(-x1 * sn));
+            hi[h] = bf16r(bf16r(x1 * cs) + bf16r(x0 * sn));
+        }
+        olo[j] = pack_bf16x2(lo[0], lo[1]);
+        ohi[j] = pack_bf16x2(hi[0], hi[1]);
     }
     bf16* dst = is_k ? kc + (((size_t)b * NKV + (head - 16)) * kv_cap + sl) * HD : row;
-    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16x2(lo[0], lo[1]);
-    *reinterpret_cast<uint32_t*>(dst + HD / 2 + 2 * lane) = pack_bf16x2(hi[0], hi[1]);
-    (void)DQ; (void)DKV;
+    *reinterpret_cast<uint4*>(dst + 8 * sub) = make_uint4(olo[0], olo[1], olo[2], olo[3]);
+    *reinterpret_cast<uint4*>(dst + HD / 2 + 8 * sub) = make_uint4(ohi[0], ohi[1], ohi[2], ohi[3]);
 }
 
 // SigLIP patch gather: fp32 pixels [B, 3, H, W] -> bf16 patches [B * (H/p) * (W/p), 3 * p * p] in (channel, row, col)
@@ -252,7 +265,7 @@ extern "C" int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void
                                            const int32_t* seq, const int32_t* slot, void* kcache_layer, void* vcache_layer,
                                            int n_tokens, int kv_cap, float eps, void* stream) {
     if (!qkv || !qn || !kn || !rope || !pos || !seq || !slot || !kcache_layer || !vcache_layer || n_tokens < 1) { set_error("qk_rope_scatter: bad argument"); return ITTAI_E_ARG; }
-    launch_pdl(qk_rope_scatter_kernel, dim3(row_grid((long long)n_tokens * 32)), dim3(kRowThreads), 0, (cudaStream_t)stream, 1, 
+    launch_pdl(qk_rope_scatter_kernel, dim3(row_grid((long long)n_tokens * 8)), dim3(kRowThreads), 0, (cudaStream_t)stream, 1, 
         (bf16*)qkv, (const bf16*)qn, (const bf16*)kn, (const bf16*)rope, pos, seq, slot, (bf16*)kcache_layer, (bf16*)vcache_layer, n_tokens, kv_cap, eps);
     return launched("qk_rope_scatter_kernel");
 }

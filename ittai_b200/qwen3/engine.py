@@ -70,7 +70,8 @@ class PrefillCore:
                                                    pos.data_ptr(), seq.data_ptr(), slot.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                                    T, kv_cap, EPS, s))
             ops.attention(qkv, kc, vc, attn, seqs, n_heads=NH, group=NH // NKV, head_dim=HD, causal=True, max_q_len=max_q_len,
-                          q_strides=(DQKV, HD), k_strides=k_strides, v_strides=k_strides, o_strides=(DQ, HD))
+                          q_strides=(DQKV, HD), k_strides=k_strides, v_strides=k_strides, o_strides=(DQ, HD),
+                          q_rows_total=T, kv_rows_total=kc.numel() // HD, status=st)
             ops.gemm(attn, w["wo"][l], st, residual=h, out=h)
             ops.rmsnorm_rows(h, w["ln2"][l], EPS, out=xn)
             ops.gemm(xn, w["wgu"][l], st, epi=_C.EPI_SWIGLU, out=act)

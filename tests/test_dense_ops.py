@@ -86,6 +86,33 @@ def test_attention_causal_gqa_cache_layout(q_len, prefix):
 
 
 @gpu
+@pytest.mark.parametrize("q_len,prefix,causal", [(300, 0, True), (130, 70, True), (512, 0, True), (128, 1000, True), (65, 3, True), (200, 56, False)])
+def test_attention_key_loop_tensor_memory_kernel(q_len, prefix, causal):
+    """The tcgen05 key-loop kernel (row totals + status words given) on the Qwen3 layout: q in a [T, 4096] qkv matrix, k/v in
+    a cache [B, 8, cap, 128] whose rows past each sequence hold NaN (unwritten cache must not leak into the result)."""
+    from ittai_b200 import ops
+    NH, NKV, hd, cap, B = 16, 8, 128, 1280, 2
+    kv_len = prefix + q_len
+    qkv = _rand(B * q_len, 4096, seed=6)
+    kc, vc = _rand(B, NKV, cap, hd, seed=7), _rand(B, NKV, cap, hd, seed=8)
+    kc[:, :, kv_len:] = float("nan")
+    vc[:, :, kv_len:] = float("nan")
+    out = torch.zeros(B * q_len, NH * hd, dtype=torch.bfloat16, device="cuda")
+    seqs = torch.tensor([[b * q_len, q_len, 0, kv_len] for b in range(B)], dtype=torch.int32, device="cuda")
+    st = ops.new_status(qkv.device)
+    ops.attention(qkv, kc, vc, out, seqs, n_heads=NH, group=2, head_dim=hd, causal=causal, max_q_len=q_len,
+                  q_strides=(4096, hd), k_strides=(hd, cap * hd, NKV * cap * hd), v_strides=(hd, cap * hd, NKV * cap * hd),
+                  o_strides=(NH * hd, hd), q_rows_total=B * q_len, kv_rows_total=B * NKV * cap, status=st)
+    ops.check_status(st)
+    q = qkv[:, :NH * hd].float().view(B, q_len, NH, hd).transpose(1, 2)
+    k = kc[:, :, :kv_len].float().repeat_interleave(2, 1)
+    v = vc[:, :, :kv_len].float().repeat_interleave(2, 1)
+    mask = torch.arange(kv_len, device="cuda")[None, :] <= torch.arange(q_len, device="cuda")[:, None] + prefix if causal else None
+    want = F.scaled_dot_product_attention(q, k, v, attn_mask=mask).transpose(1, 2).reshape(B * q_len, NH * hd)
+    _check(out, want, f"key-loop attention q={q_len} prefix={prefix} causal={causal}")
+
+
+@gpu
 def test_norm_rows():
     from ittai_b200 import ops
     x = _rand(777, 1024, scale=3.0, seed=5)
