@@ -240,11 +240,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tmem_ld_wait();
                 epilogue_pack(g, r, g.bias != nullptr ? sbias + 32 * ch : nullptr, o);
                 if (swiglu) {
-                    // 16 output columns per thread, stored straight from the row layout
-                    if (row0 + lane < g.M) {
-                        uint4* dst = reinterpret_cast<uint4*>(g.out + (size_t)(row0 + lane) * g.ld_out + (col0 + 32 * ch) / 2);
-                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    // 16 output columns per chunk: two consecutive chunks fill one 32-column staging tile, then one TMA store
+                    const uint32_t half = ch & 1;
+                    unsigned char* sto = so + ((cc >> 1) % 3u) * 2048;
+                    if (half == 0) {
+                        if (lane == 0) tma_store_wait_read<2>();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        *reinterpret_cast<uint4*>(sto + lane * 64 + (((2 * half + j) ^ swz) << 4)) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                    if (half == 1) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) { tma_store_2d(&tm_out, sto, (col0 + 32 * ((int)ch - 1)) / 2, row0); tma_store_commit(); }
                     }
                     continue;
                 }

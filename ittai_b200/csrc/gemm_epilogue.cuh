@@ -105,11 +105,22 @@ __device__ __forceinline__ void epilogue_pack(const GemmArgs& g, const uint32_t 
         }
     }
     if (g.epi == ITTAI_EPI_SWIGLU) {
+        // adjacent columns are (gate, up): act = bf16(bf16(silu(bf16 gate)) * bf16 up), silu(x) = x / (1 + 2^(-x log2 e)) with
+        // the hardware exponential and reciprocal (their error is far below the bf16 rounding of the result); the
+        // roundings of the Linear outputs run on the integer pipe
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-            const float g0 = bf16r(v[i].x), u0 = bf16r(v[i].y);
-            const float g1 = bf16r(v[i + 1].x), u1 = bf16r(v[i + 1].y);
-            o[i / 2] = pack_bf16x2(bf16r(g0 / (1.0f + expf(-g0))) * u0, bf16r(g1 / (1.0f + expf(-g1))) * u1);
+            float gt[2], up[2], sl[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                gt[h] = __uint_as_float(bf16r_bits(__float_as_uint(v[i + h].x)));
+                up[h] = __uint_as_float(bf16r_bits(__float_as_uint(v[i + h].y)));
+                float e, rc;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gt[h] * -1.4426950408889634f));
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + e));
+                sl[h] = __uint_as_float(bf16r_bits(__float_as_uint(gt[h] * rc)));
+            }
+            o[i / 2] = pack_bf16x2(sl[0] * up[0], sl[1] * up[1]);
         }
         return;
     }
