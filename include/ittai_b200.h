@@ -190,6 +190,20 @@ typedef struct IttaiGemm {
     const void* residual;  /* [M, ld_res] bf16 or NULL */
     void* out;
     uint32_t* status;      /* [ITTAI_STATUS_WORDS] device words */
+    /* LayerNorm folded into the GEMM (both NULL: off; M > 128 only).  With W' = gain (.) W along K, col_sums[n] = sum_k W'[n,k]
+     * and bias' = bias + W beta, LayerNorm(x) W^T + bias = rstd_r (x W'^T - mean_r col_sums) + bias': the kernel reads the
+     * un-normalised x as A and applies the row statistics in the epilogue, as the reference does
+     * (src/ittai/siglip/kernel.py:284-288, 523-525).  The caller passes W' as `w`, bias' as `bias`. */
+    const float* row_stats; /* stats_parts == 0: [M][2] fp32 mean, rstd of each row of A (ittai_row_stats);
+                               stats_parts > 0: [M][stats_parts][2] partial (sum, sum of squares) over slices of the K columns,
+                               as another GEMM's stats_out wrote them; mean and rstd are finished in the epilogue */
+    const float* col_sums;  /* [N] fp32 */
+    float* stats_out;       /* or NULL (M > 128, no SwiGLU): [M][N/128][2] fp32, (sum, sum of squares) of every 128-column
+                               slice of each OUTPUT row, of the bf16 values as stored: the statistics of a LayerNorm over
+                               this GEMM's output come for free with its epilogue (the reference finishes them in the last
+                               arriving tile, src/ittai/siglip/kernel.py:335-364); plain stores, no atomics */
+    int32_t stats_parts;
+    float stats_eps;        /* LayerNorm epsilon, used when stats_parts > 0 */
 } IttaiGemm;
 
 /* Replaces the tiled GEMM main loops + epilogues of the reference's megakernels
@@ -227,6 +241,9 @@ int ittai_attention_launch(const IttaiAttention* a, void* stream);
 /* y = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * gain) over rows of 1024 bf16 (Qwen3 RMSNorm; the reference folds the gain
  * into the next weight and applies the scale in the GEMM epilogue: src/ittai/qwen3/engine.py:106-111, base.py:84-85). */
 int ittai_rmsnorm_rows(const void* x, int ld_x, const void* gain, void* y, int ld_y, int rows, float eps, void* stream);
+/* stats[r] = (mean, 1/sqrt(var + eps)) of row r over `width` bf16 columns (a multiple of 8, at most 2048): the row
+ * statistics a GEMM with a folded LayerNorm applies in its epilogue (reference src/ittai/siglip/kernel.py:335-364). */
+int ittai_row_stats(const void* x, int ld_x, float* stats, int rows, int width, float eps, void* stream);
 /* y = bf16(LayerNorm(x) * gain + beta), gain/beta fp32, width a multiple of 8 up to 2048 (SigLIP; folded into the next
  * GEMM by the reference: src/ittai/siglip/kernel.py:284-288,523-525). */
 int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, const void* beta, void* y, int ld_y, int rows, int width,

@@ -22,7 +22,7 @@ EXPORTS = (
     "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
     "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
     "ittai_qwen3_decode_launch_static",
-    "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows",
+    "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows", "ittai_row_stats",
     "ittai_qwen3_qk_rope_scatter", "ittai_siglip_im2col", "ittai_embed_rows", "ittai_qwen3_final_pool",
 )
 EPI_NONE, EPI_GELU, EPI_SWIGLU = range(3)
@@ -53,7 +53,8 @@ class Gemm(C.Structure):
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("epi", C.c_int32),
         ("ld_a", C.c_int32), ("ld_w", C.c_int32), ("ld_out", C.c_int32), ("ld_res", C.c_int32),
         ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
-        ("out", C.c_void_p), ("status", C.c_void_p),
+        ("out", C.c_void_p), ("status", C.c_void_p), ("row_stats", C.c_void_p), ("col_sums", C.c_void_p),
+        ("stats_out", C.c_void_p), ("stats_parts", C.c_int32), ("stats_eps", C.c_float),
     ]
 
 
@@ -94,6 +95,7 @@ def lib() -> C.CDLL:
     vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
     L.ittai_rmsnorm_rows.argtypes = [vp, i32, vp, vp, i32, i32, f32, vp]
     L.ittai_layernorm_rows.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, f32, vp]
+    L.ittai_row_stats.argtypes = [vp, i32, vp, i32, i32, f32, vp]
     L.ittai_qwen3_qk_rope_scatter.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp]
     L.ittai_siglip_im2col.argtypes = [vp, vp, i32, i32, i32, i32, vp]
     L.ittai_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp]

@@ -33,7 +33,7 @@ constexpr int kEpiCols = PN / (kEpiWarps / 4);    // accumulator columns per epi
 constexpr int kThreads2 = 64 + 32 * kEpiWarps;
 constexpr uint32_t kHalfA = 128 * PK * 2, kHalfB = 128 * PK * 2;                // per CTA per stage
 constexpr uint32_t kStageOut = 3 * 2048;                                         // per epilogue warp: three tiles of 32 rows x 64 B
-constexpr uint32_t kSmem2 = kStages2 * (kHalfA + kHalfB) + kEpiWarps * kStageOut + 4096 /*bias slices*/ + 1024 /*alignment*/ + 512 /*barriers*/;
+constexpr uint32_t kSmem2 = kStages2 * (kHalfA + kHalfB) + kEpiWarps * kStageOut + 2 * 4096 /*bias and column-sum slices*/ + 1024 /*alignment*/ + 512 /*barriers*/;
 constexpr uint32_t kSpin2 = 1u << 24;
 #ifdef ITTAI_TILE_MFAST
 #define TILE_M(t) ((t) % tiles_m)
@@ -104,7 +104,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     unsigned char* sa = gsm;                                         // [stages][128 rows][128 B]
     unsigned char* sb = gsm + kStages2 * kHalfA;                     // [stages][128 rows][128 B]
     unsigned char* sout = sb + kStages2 * kHalfB;                    // [epilogue warps] staging tiles, then their bias slices
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sout + kEpiWarps * kStageOut + 4096);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sout + kEpiWarps * kStageOut + 2 * 4096);
     unsigned long long* full = bars;                                 // [stages]  both producers -> leader's MMA
     unsigned long long* empty = bars + kStages2;                     // [stages]  MMA -> this CTA's producer
     unsigned long long* acc_full = bars + 2 * kStages2;              // [2]       MMA -> this CTA's epilogue
@@ -194,6 +194,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int ew = warp - 2, q = warp & 3, cq = ew >> 2;         // TMEM lane quarter, column slice (kEpiCols columns)
         unsigned char* so = sout + ew * kStageOut;                   // three [32 rows][64 B] tiles, 64-byte swizzle
         float* sbias = reinterpret_cast<float*>(sout + kEpiWarps * kStageOut) + ew * kEpiCols;   // this warp's bias values
+        float* scsum = sbias + kEpiWarps * kEpiCols;                 // and, with a folded LayerNorm, its column sums
+        const bool fold = g.row_stats != nullptr;
         unsigned long long* res_bar = res_bars + 2 * ew;
         const bool swiglu = g.epi == ITTAI_EPI_SWIGLU, has_res = g.residual != nullptr;
         const int swz = (lane >> 1) & 3;                             // 64-byte swizzle of this thread's staging row
@@ -220,6 +222,25 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const int col0 = tile_n * PN + kEpiCols * cq;             // first accumulator column of this warp
             // the bias slice does not depend on the accumulator: fetched before waiting for it
             if (g.bias != nullptr && lane < kEpiCols / 4) *reinterpret_cast<float4*>(sbias + 4 * lane) = *reinterpret_cast<const float4*>(g.bias + col0 + 4 * lane);
+            float mean = 0.f, rstd = 1.f;
+            if (fold) {
+                if (lane < kEpiCols / 4) *reinterpret_cast<float4*>(scsum + 4 * lane) = *reinterpret_cast<const float4*>(g.col_sums + col0 + 4 * lane);
+                if (row0 + lane < g.M) {
+                    if (g.stats_parts == 0) {
+                        const float2 ms = *reinterpret_cast<const float2*>(g.row_stats + 2 * (size_t)(row0 + lane));
+                        mean = ms.x; rstd = ms.y;
+                    } else {
+                        // partial (sum, sum of squares) of the K columns in slices, added in slice order
+                        const float2* ps = reinterpret_cast<const float2*>(g.row_stats) + (size_t)(row0 + lane) * g.stats_parts;
+                        float s1 = 0.f, s2 = 0.f;
+                        for (int i = 0; i < g.stats_parts; ++i) { const float2 t = ps[i]; s1 += t.x; s2 += t.y; }
+                        const float inv_k = 1.0f / (float)g.K;
+                        mean = s1 * inv_k;
+                        rstd = rsqrtf(fmaxf(s2 * inv_k - mean * mean, 0.f) + g.stats_eps);
+                    }
+                }
+            }
+            float st1 = 0.f, st2 = 0.f;                               // statistics of this row's output slice
             __syncwarp();
             bool ok = true;
             GEMM_PROF(long long t0 = clock64();)
@@ -238,7 +259,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 uint32_t r[32], o[16];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + kEpiCols * cq + 32 * ch), r);
                 tmem_ld_wait();
-                epilogue_pack(g, r, g.bias != nullptr ? sbias + 32 * ch : nullptr, o);
+                epilogue_pack(g, r, g.bias != nullptr ? sbias + 32 * ch : nullptr, o, fold ? scsum + 32 * ch : nullptr, mean, rstd);
                 if (swiglu) {
                     // 16 output columns per chunk: two consecutive chunks fill one 32-column staging tile, then one TMA store
                     const uint32_t half = ch & 1;
@@ -277,6 +298,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     __syncwarp();                                     // every lane has consumed the buffer: refill it
                     if (lane == 0) prefetch_res(cc + 2);
                 }
+                if (g.stats_out != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float lo = bf_lo(o[i]), hi = bf_hi(o[i]);
+                        st1 += lo + hi;
+                        st2 = fmaf(lo, lo, fmaf(hi, hi, st2));
+                    }
+                }
                 // the store that last used this staging tile must have finished reading it
                 unsigned char* sto = has_res ? so : so + (cc % 3u) * 2048;
                 if (lane == 0) { if (has_res) tma_store_wait_read<0>(); else tma_store_wait_read<2>(); }
@@ -289,6 +318,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 if (lane == 0) { tma_store_2d(&tm_out, sto, col0 + 32 * (int)ch, row0); tma_store_commit(); }
             }
             if (!ok) break;
+            if (g.stats_out != nullptr && row0 + lane < g.M)
+                *reinterpret_cast<float2*>(g.stats_out + 2 * ((size_t)(row0 + lane) * (g.N / 128) + col0 / 128)) = make_float2(st1, st2);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[buf], 0));

@@ -15,6 +15,11 @@ struct GemmArgs {
     bf16* out;               // [M, ld_out]  (SwiGLU: N/2 columns)
     int ld_out;
     uint32_t* status;        // device status words
+    const float* row_stats;  // [M][2] (mean, rstd) of the rows of A, or nullptr: LayerNorm folded into the GEMM
+    const float* col_sums;   // [N] column sums of the folded weight
+    float* stats_out;        // [M][N/128][2] (sum, sum of squares) per 128-column slice of the output rows, or nullptr
+    int stats_parts;         // > 0: row_stats holds [M][parts][2] partial sums over K instead of (mean, rstd)
+    float stats_eps;
 #ifdef ITTAI_GEMM_PROFILE
     long long* clk;          // [CTAs][8]: total, MMA waiting for loads, MMA waiting for a free accumulator, epilogue busy, epilogue waiting
 #endif
@@ -91,11 +96,22 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& g, const uint32_t
 // module output (16 words; SwiGLU: 8 words for 16 output columns).  `bias32` points at the 32 bias values of these
 // columns (shared or global memory) or is null.  The caller adds the residual afterwards, on the rounded values, as the
 // eager modules do.
-__device__ __forceinline__ void epilogue_pack(const GemmArgs& g, const uint32_t (&r)[32], const float* bias32, uint32_t (&o)[16]) {
+__device__ __forceinline__ void epilogue_pack(const GemmArgs& g, const uint32_t (&r)[32], const float* bias32, uint32_t (&o)[16],
+                                              const float* csum32 = nullptr, float mean = 0.f, float rstd = 1.f) {
     // arithmetic on fp32 pairs: one packed instruction does two columns
     float2 v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    if (csum32 != nullptr) {
+        // folded LayerNorm: rstd * (acc - mean * column sum)
+        const float2 nm = make_float2(-mean, -mean), rs = make_float2(rstd, rstd);
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            const float4 c4 = *reinterpret_cast<const float4*>(csum32 + 2 * i);
+            v[i] = __fmul2_rn(rs, __ffma2_rn(nm, make_float2(c4.x, c4.y), v[i]));
+            v[i + 1] = __fmul2_rn(rs, __ffma2_rn(nm, make_float2(c4.z, c4.w), v[i + 1]));
+        }
+    }
     if (bias32 != nullptr) {
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {

@@ -176,6 +176,12 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     }
     if (a->epi < ITTAI_EPI_NONE || a->epi > ITTAI_EPI_SWIGLU) { set_error("unknown epilogue %d", a->epi); return ITTAI_E_ARG; }
     if (a->epi == ITTAI_EPI_SWIGLU && a->residual) { set_error("SwiGLU epilogue takes no residual"); return ITTAI_E_ARG; }
+    if ((a->row_stats == nullptr) != (a->col_sums == nullptr) || (a->row_stats != nullptr && a->m <= GM)) {
+        set_error("a folded LayerNorm needs both row_stats and col_sums, and M > %d", GM);
+        return ITTAI_E_ARG;
+    }
+    if (a->stats_out != nullptr && (a->m <= GM || a->epi == ITTAI_EPI_SWIGLU)) { set_error("stats_out needs M > %d and no SwiGLU", GM); return ITTAI_E_ARG; }
+    if (a->stats_parts < 0 || a->stats_parts > 64) { set_error("stats_parts %d out of range", a->stats_parts); return ITTAI_E_ARG; }
     const int ld_a = a->ld_a ? a->ld_a : a->k, ld_w = a->ld_w ? a->ld_w : a->k;
     const int n_out = a->epi == ITTAI_EPI_SWIGLU ? a->n / 2 : a->n;
     const int ld_out = a->ld_out ? a->ld_out : n_out, ld_res = a->ld_res ? a->ld_res : a->n;
@@ -209,6 +215,11 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.out = reinterpret_cast<bf16*>(a->out);
     g.ld_out = ld_out;
     g.status = a->status;
+    g.row_stats = a->row_stats;
+    g.col_sums = a->col_sums;
+    g.stats_out = a->stats_out;
+    g.stats_parts = a->stats_parts;
+    g.stats_eps = a->stats_eps;
 #ifdef ITTAI_GEMM_PROFILE
     extern long long* g_gemm_clk;
     g.clk = g_gemm_clk;

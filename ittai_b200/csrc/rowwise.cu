@@ -110,6 +110,40 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_rows_kernel(const bf16*
     }
 }
 
+// stats[row] = (mean, rstd) over `width` columns: what a GEMM with a folded LayerNorm applies in its epilogue (the
+// reference's row statistics, src/ittai/siglip/kernel.py:335-364).  Two passes over registers, like the LayerNorm above.
+template <int NCH>
+__global__ void __launch_bounds__(kRowThreads) row_stats_kernel(const bf16* __restrict__ x, int ld_x, float* __restrict__ stats,
+                                                                  int rows, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int n_chunks = width / 8;
+    float v[NCH][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        const int ch = lane + 32 * i;
+        if (ch < n_chunks) {
+            const uint4 q = *reinterpret_cast<const uint4*>(x + (size_t)row * ld_x + ch * 8);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { v[i][2 * j] = bf_lo(w[j]); v[i][2 * j + 1] = bf_hi(w[j]); s += v[i][2 * j] + v[i][2 * j + 1]; }
+        }
+    }
+    const float mean = warp_sum(s) / (float)width;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+        if (lane + 32 * i < n_chunks) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; sq += d * d; }
+        }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    if (lane == 0) *reinterpret_cast<float2*>(stats + 2 * (size_t)row) = make_float2(mean, rstd);
+}
+
 // Qwen3 prefill: per token and head, RMSNorm over the 128 head dims + half-split RoPE in bf16 steps (the arithmetic of
 // the decode phase), Q rotated in place in the qkv matrix, K and V written to cache row slot[t] of sequence seq[t]
 // (the rotary position pos[t] and the cache row differ when sequences are packed into one cache).
@@ -259,6 +293,16 @@ extern "C" int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, c
     else if (width <= 1280) launch_pdl(layernorm_rows_kernel<5>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
     else launch_pdl(layernorm_rows_kernel<8>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, (const float*)gain, (const float*)beta, (bf16*)y, ld_y, rows, width, eps);
     return launched("layernorm_rows_kernel");
+}
+
+extern "C" int ittai_row_stats(const void* x, int ld_x, float* stats, int rows, int width, float eps, void* stream) {
+    if (!x || !stats || rows < 1 || width < 8 || width % 8 || width > 2048 || ld_x % 8) { set_error("row_stats: bad argument"); return ITTAI_E_ARG; }
+    const int grid = row_grid(rows);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (width <= 768) launch_pdl(row_stats_kernel<3>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, stats, rows, width, eps);
+    else if (width <= 1280) launch_pdl(row_stats_kernel<5>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, stats, rows, width, eps);
+    else launch_pdl(row_stats_kernel<8>, dim3(grid), dim3(kRowThreads), 0, st, 1, (const bf16*)x, ld_x, stats, rows, width, eps);
+    return launched("row_stats_kernel");
 }
 
 extern "C" int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void* kn, const void* rope, const int32_t* pos,

@@ -22,9 +22,15 @@ def _stream(t: torch.Tensor):
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Tensor | None = None,
-         residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None) -> torch.Tensor:
+         residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None,
+         row_stats: torch.Tensor | None = None, col_sums: torch.Tensor | None = None, stats_out: torch.Tensor | None = None,
+         stats_eps: float = 0.0) -> torch.Tensor:
     """``out = epilogue(a @ w.T)`` on the tcgen05 GEMM: a [M, K] and w [N, K] bf16 (last dim contiguous), bias fp32 [N],
-    residual bf16 [M, N].  SwiGLU takes interleaved (gate, up) weight rows and returns [M, N/2]."""
+    residual bf16 [M, N].  SwiGLU takes interleaved (gate, up) weight rows and returns [M, N/2].  ``row_stats`` (fp32
+    [M, 2] from ``row_stats``) with ``col_sums`` (fp32 [N]) folds a LayerNorm over ``a`` into the GEMM: ``w`` is then the
+    weight scaled by the LayerNorm gain along K and ``bias`` includes ``W @ beta`` (see ``fold_layernorm``).  ``stats_out``
+    (fp32 [M, N/128, 2]) receives the (sum, sum of squares) of every 128-column slice of the output rows; passed as the
+    ``row_stats`` of the next GEMM (3-D, with ``stats_eps``) it replaces the separate statistics pass."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
     m, k = a.shape
     n = w.shape[0]
@@ -42,8 +48,37 @@ def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Ten
     if residual is not None:
         assert residual.dtype == torch.bfloat16 and residual.shape == (m, n) and residual.stride(1) == 1
         g.residual, g.ld_res = residual.data_ptr(), residual.stride(0)
+    if row_stats is not None:
+        assert row_stats.dtype == torch.float32 and row_stats.is_contiguous() and row_stats.shape[0] == m and row_stats.shape[-1] == 2
+        assert col_sums is not None and col_sums.dtype == torch.float32 and col_sums.numel() == n
+        g.row_stats, g.col_sums = row_stats.data_ptr(), col_sums.data_ptr()
+        if row_stats.dim() == 3:
+            assert row_stats.shape[1] * 128 == k and stats_eps > 0
+            g.stats_parts, g.stats_eps = row_stats.shape[1], stats_eps
+    if stats_out is not None:
+        assert stats_out.dtype == torch.float32 and stats_out.is_contiguous() and tuple(stats_out.shape) == (m, n // 128, 2)
+        g.stats_out = stats_out.data_ptr()
     _C.check(_C.lib().ittai_gemm_bf16_launch(C.byref(g), _stream(a)))
     return out
+
+
+def row_stats(x: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 ``[rows, 2]``: mean and ``1/sqrt(var + eps)`` of every row of bf16 ``x``."""
+    out = torch.empty(x.shape[0], 2, dtype=torch.float32, device=x.device) if out is None else out
+    _C.check(_C.lib().ittai_row_stats(x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], x.shape[1], eps, _stream(x)))
+    return out
+
+
+def fold_layernorm(w: torch.Tensor, bias: torch.Tensor | None, gain: torch.Tensor, beta: torch.Tensor):
+    """Weights of ``Linear(LayerNorm(x))`` for the folded GEMM: returns (w' bf16 = gain (.) w along K, bias' fp32 = bias + w beta,
+    column sums fp32 of the ROUNDED w', so that the epilogue's ``acc - mean * col_sum`` cancels exactly what the tensor
+    cores accumulated).  Reference: the fold of ``src/ittai/siglip/kernel.py:523-525``."""
+    wf = w.float()
+    wp = (wf * gain.float()[None, :]).to(torch.bfloat16).contiguous()
+    b = wf @ beta.float()
+    if bias is not None:
+        b = b + bias.float()
+    return wp, b.contiguous(), wp.float().sum(dim=1).contiguous()
 
 
 def attention(q, k, v, o, seqs: torch.Tensor, *, n_heads: int, group: int, head_dim: int, causal: bool, max_q_len: int,

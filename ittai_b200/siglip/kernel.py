@@ -24,7 +24,7 @@ class Engine:
     (``tile_n, stages, warps, fold_k, group_m, kv_block``) are accepted and ignored: there is one sm_100a kernel."""
 
     @torch.no_grad()
-    def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True):
+    def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True, fold_ln=True):
         vm = _vision_model(vm)
         cfg, emb = vm.config, vm.embeddings
         if not isinstance(emb.patch_embedding, torch.nn.Conv2d):
@@ -55,12 +55,24 @@ class Engine:
                 wo=bf(a.out_proj.weight), bo=f32(a.out_proj.bias), w1=bf(m.fc1.weight), b1=f32(m.fc1.bias),
                 w2=bf(m.fc2.weight), b2=f32(m.fc2.bias)))
         self.post = (f32(vm.post_layernorm.weight), f32(vm.post_layernorm.bias))
+        # LayerNorm folded into the GEMMs around it, as the reference does (``:284-288, 335-364, 523-525``): the GEMM that
+        # writes the residual stream also writes its row statistics, the GEMM that consumes it reads the stream itself and
+        # applies mean / rstd in its epilogue, so there is no LayerNorm pass and the normalised activations are never
+        # written.  ``fold_ln=False`` keeps the separate LayerNorm kernel, whose rounding points are exactly the eager
+        # module's (the folded path rounds the gain-scaled weights instead of the normalised activations).
+        self.fold_ln = fold_ln and B * emb.num_patches > 128
+        if self.fold_ln:
+            for w in self.layers:
+                w["qkv_f"] = ops.fold_layernorm(w["wqkv"], w["bqkv"], *w["ln1"])
+                w["fc1_f"] = ops.fold_layernorm(w["w1"], w["b1"], *w["ln2"])
         h = vm.head
         inw, inb = h.attention.in_proj_weight, h.attention.in_proj_bias
         # the probe is a parameter, so its query projection does not depend on the image: computed once, as the eager
         # module would (bf16 Linear)
         self.probe_q = bf(torch.nn.functional.linear(h.probe[0].to(torch.bfloat16), inw[:D].to(torch.bfloat16), inb[:D].to(torch.bfloat16)))
         self.wkv, self.bkv = bf(inw[D:]), f32(inb[D:])
+        if self.fold_ln:
+            self.kv_f = ops.fold_layernorm(self.wkv, self.bkv, *self.post)
         self.who, self.bho = bf(h.attention.out_proj.weight), f32(h.attention.out_proj.bias)
         self.hln = (f32(h.layernorm.weight), f32(h.layernorm.bias))
         self.hw1, self.hb1, self.hw2, self.hb2 = bf(h.mlp.fc1.weight), f32(h.mlp.fc1.bias), bf(h.mlp.fc2.weight), f32(h.mlp.fc2.bias)
@@ -72,6 +84,10 @@ class Engine:
         self.embeds = z(B, D)
         self.seqs = torch.tensor([[b * S, S, b * S, S] for b in range(B)], dtype=torch.int32, device=dev)
         self.pool_seqs = torch.tensor([[b, 1, b * S, S] for b in range(B)], dtype=torch.int32, device=dev)
+        # per-row (sum, sum of squares) of the residual stream in 128-column slices, written by the epilogue of the GEMM that
+        # produces it: one buffer for the stream after attention, one for the stream after the MLP
+        self.stats_a = torch.zeros(M, D // 128, 2, dtype=torch.float32, device=dev)
+        self.stats_m = torch.zeros(M, D // 128, 2, dtype=torch.float32, device=dev)
         self.status = ops.new_status(dev)
         self.graph = None if graph else False
 
@@ -80,20 +96,31 @@ class Engine:
         L, st = _C.lib(), self.status
         _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p,
                                        ops._stream(self.pixels)))
-        ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x)
+        fold = self.fold_ln
+        ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m if fold else None)
         for w in self.layers:
-            ops.layernorm_rows(self.x, *w["ln1"], eps, out=self.y)
-            ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
+            if fold:
+                ops.gemm(self.x, w["qkv_f"][0], st, bias=w["qkv_f"][1], out=self.qkv, row_stats=self.stats_m, col_sums=w["qkv_f"][2], stats_eps=eps)
+            else:
+                ops.layernorm_rows(self.x, *w["ln1"], eps, out=self.y)
+                ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
             ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
                           causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
                           o_strides=(D, hd), max_kv_len=S, q_rows_total=self.M, kv_rows_total=self.M, status=st)
-            ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x)
-            ops.layernorm_rows(self.x, *w["ln2"], eps, out=self.y)
-            ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)
-            ops.gemm(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x)
+            ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x, stats_out=self.stats_a if fold else None)
+            if fold:
+                ops.gemm(self.x, w["fc1_f"][0], st, bias=w["fc1_f"][1], epi=_C.EPI_GELU, out=self.h, row_stats=self.stats_a, col_sums=w["fc1_f"][2],
+                         stats_eps=eps)
+            else:
+                ops.layernorm_rows(self.x, *w["ln2"], eps, out=self.y)
+                ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)
+            ops.gemm(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x, stats_out=self.stats_m if fold else None)
         # post-LayerNorm + MAP head: probe attends over the tokens, then LayerNorm + MLP with a residual
-        ops.layernorm_rows(self.x, *self.post, eps, out=self.y)
-        ops.gemm(self.y, self.wkv, st, bias=self.bkv, out=self.kv)
+        if fold:
+            ops.gemm(self.x, self.kv_f[0], st, bias=self.kv_f[1], out=self.kv, row_stats=self.stats_m, col_sums=self.kv_f[2], stats_eps=eps)
+        else:
+            ops.layernorm_rows(self.x, *self.post, eps, out=self.y)
+            ops.gemm(self.y, self.wkv, st, bias=self.bkv, out=self.kv)
         ops.attention(self.probe_q, self.kv, self.kv[:, D:], self.pool_a, self.pool_seqs, n_heads=H, group=1, head_dim=hd,
                       causal=False, max_q_len=1, q_strides=(0, hd), k_strides=(2 * D, hd, 0), v_strides=(2 * D, hd, 0),
                       o_strides=(D, hd))

@@ -9,9 +9,13 @@ import torch
 gpu = pytest.mark.gpu
 
 
-def _check(got, want, what):
+def _check(got, want, what, mid=None):
+    """``mid``: an intermediate the epilogue rounds to bf16 before adding something to it (the module output ahead of a
+    residual add); one ulp of it is allowed on top, since it does not shrink when the sum cancels."""
     got, want = got.float(), want.float()
     tol = 2.0 ** -6 * want.abs() + 2.0 ** -7 * want.pow(2).mean().sqrt()
+    if mid is not None:
+        tol = tol + 2.0 ** -7 * mid.float().abs()
     bad = (got - want).abs() > tol
     assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} outside tolerance, max err {(got - want).abs().max():.4g}"
 
@@ -50,7 +54,7 @@ def test_gemm_bias_gelu_residual_swiglu():
     from ittai_b200 import _C, ops
     m, n, k = 392, 3072, 768
     a, w = _rand(m, k, seed=4), _rand(n, k, scale=0.05, seed=5)
-    bias = torch.randn(n, device="cuda") * 0.1
+    bias = _rand(n, seed=7).float() * 0.1
     res = _rand(m, n, seed=6)
     st = ops.new_status("cuda")
     acc = a.float() @ w.float().t()
@@ -58,11 +62,57 @@ def test_gemm_bias_gelu_residual_swiglu():
     _check(ops.gemm(a, w, st, bias=bias), acc + bias, "bias")
     _check(ops.gemm(a, w, st, bias=bias, epi=_C.EPI_GELU),
            torch.nn.functional.gelu(rb(acc + bias), approximate="tanh"), "bias + gelu")
-    _check(ops.gemm(a, w, st, bias=bias, residual=res), res.float() + rb(acc + bias), "bias + residual")
-    _check(ops.gemm(a, w, st, residual=res), res.float() + rb(acc), "residual")
+    _check(ops.gemm(a, w, st, bias=bias, residual=res), res.float() + rb(acc + bias), "bias + residual", mid=acc + bias)
+    _check(ops.gemm(a, w, st, residual=res), res.float() + rb(acc), "residual", mid=acc)
     g, u = rb(acc[:, 0::2]), rb(acc[:, 1::2])
     _check(ops.gemm(a, w, st, epi=_C.EPI_SWIGLU), rb(torch.nn.functional.silu(g)) * u, "swiglu")
     ops.check_status(st)
+
+
+@gpu
+@pytest.mark.parametrize("m,n,k,epi", [(1000, 2304, 768, 0), (12544, 3072, 768, 1), (196, 1536, 768, 0)])
+def test_gemm_folded_layernorm(m, n, k, epi):
+    """Linear(LayerNorm(x)) with the LayerNorm folded into the GEMM (row statistics in the epilogue) against the unfused
+    fp32 computation; rows carry a large common offset so that a wrong mean term would show."""
+    import torch.nn.functional as F
+    from ittai_b200 import _C, ops
+    x = (_rand(m, k, seed=11).float() * 1.5 + 3.0).to(torch.bfloat16)
+    w, bias = _rand(n, k, scale=0.05, seed=12), torch.randn(n, device="cuda")
+    gain, beta = torch.rand(k, device="cuda") + 0.5, torch.randn(k, device="cuda") * 0.1
+    st = ops.new_status("cuda")
+    stats = ops.row_stats(x, 1e-6)
+    xf = x.float()
+    assert torch.allclose(stats[:, 0], xf.mean(-1), atol=1e-5, rtol=1e-5)
+    assert torch.allclose(stats[:, 1], torch.rsqrt(xf.var(-1, unbiased=False) + 1e-6), rtol=1e-4)
+    wp, bp, cs = ops.fold_layernorm(w, bias, gain, beta)
+    out = ops.gemm(x, wp, st, bias=bp, epi=_C.EPI_GELU if epi else _C.EPI_NONE, row_stats=stats, col_sums=cs)
+    ops.check_status(st)
+    want = F.linear(F.layer_norm(xf, (k,), gain, beta, 1e-6), w.float(), bias)
+    if epi:
+        want = F.gelu(want.to(torch.bfloat16).float(), approximate="tanh")
+    _check(out, want, f"folded LayerNorm gemm {m}x{n}x{k} epi={epi}")
+
+
+@gpu
+def test_gemm_statistics_from_the_producing_epilogue():
+    """A GEMM writes (sum, sum of squares) of its output rows per 128-column slice; the next GEMM finishes mean / rstd
+    from them and applies the folded LayerNorm: the pair must match LayerNorm + Linear on the stored bf16 rows."""
+    import torch.nn.functional as F
+    from ittai_b200 import ops
+    m, d, n = 1000, 768, 2304
+    a0, w0, r0 = _rand(m, d, seed=21), _rand(d, d, scale=0.05, seed=22), (_rand(m, d, seed=23).float() * 2 + 1).to(torch.bfloat16)
+    st = ops.new_status("cuda")
+    parts = torch.full((m, d // 128, 2), float("nan"), device="cuda")
+    x = ops.gemm(a0, w0, st, residual=r0, stats_out=parts)
+    xf = x.float().view(m, d // 128, 128)
+    assert torch.allclose(parts[..., 0], xf.sum(-1), rtol=1e-5, atol=1e-3)
+    assert torch.allclose(parts[..., 1], xf.pow(2).sum(-1), rtol=1e-5, atol=1e-3)
+    w, bias = _rand(n, d, scale=0.05, seed=24), torch.randn(n, device="cuda")
+    gain, beta = torch.rand(d, device="cuda") + 0.5, torch.randn(d, device="cuda") * 0.1
+    wp, bp, cs = ops.fold_layernorm(w, bias, gain, beta)
+    out = ops.gemm(x, wp, st, bias=bp, row_stats=parts, col_sums=cs, stats_eps=1e-6)
+    ops.check_status(st)
+    _check(out, F.linear(F.layer_norm(x.float(), (d,), gain, beta, 1e-6), w.float(), bias), "folded LayerNorm from epilogue statistics")
 
 
 @gpu
