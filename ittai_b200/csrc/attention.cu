@@ -296,6 +296,72 @@ __global__ void __launch_bounds__(512) attn_short_kernel(const AttnArgs a, int w
     }
 }
 
+// One query per sequence (the SigLIP MAP head: a learned probe attends over the tokens), head_dim 64: a CTA of 4 warps
+// per (sequence, head); 8 lanes share a key (8 dims each, one 16-byte load), so a warp scores 4 keys per step; each
+// 8-lane group keeps a private online softmax over its keys and the 16 groups are merged once through shared memory.
+__global__ void __launch_bounds__(128) attn_q1_kernel(const AttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int head = blockIdx.x, kvh = head / a.group;
+    const int4 sinfo = a.seqs[blockIdx.y];
+    const int kv_len = sinfo.w;
+    const int grp = threadIdx.x >> 3, sub = threadIdx.x & 7;          // 16 groups of 8 lanes
+    __shared__ float s_m[16], s_l[16], s_o[16][64];
+    const bf16* qp = a.q + (long long)sinfo.x * a.q_row + (long long)head * a.q_head + 8 * sub;
+    const uint4 qw = *reinterpret_cast<const uint4*>(qp);
+    const uint32_t qq[4] = {qw.x, qw.y, qw.z, qw.w};
+    float q[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { q[2 * j] = bf_lo(qq[j]) * a.scale_log2; q[2 * j + 1] = bf_hi(qq[j]) * a.scale_log2; }
+    const bf16* kb = a.k + (long long)blockIdx.y * a.k_seq + (long long)kvh * a.k_head + (long long)sinfo.z * a.k_row + 8 * sub;
+    const bf16* vb = a.v + (long long)blockIdx.y * a.v_seq + (long long)kvh * a.v_head + (long long)sinfo.z * a.v_row + 8 * sub;
+    float m = -INFINITY, l = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j0 = 0; j0 < kv_len; j0 += 16) {
+        const int j = j0 + grp;
+        const bool valid = j < kv_len;
+        uint4 kw = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
+        if (valid) {
+            kw = *reinterpret_cast<const uint4*>(kb + (long long)j * a.k_row);
+            vw = *reinterpret_cast<const uint4*>(vb + (long long)j * a.v_row);
+        }
+        const uint32_t kk[4] = {kw.x, kw.y, kw.z, kw.w}, vv[4] = {vw.x, vw.y, vw.z, vw.w};
+        float sc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc += q[2 * e] * bf_lo(kk[e]) + q[2 * e + 1] * bf_hi(kk[e]);
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+        if (valid) {
+            const float mn = fmaxf(m, sc), c = exp2f(m - mn), pr = exp2f(sc - mn);
+            l = l * c + pr;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                acc[2 * e] = acc[2 * e] * c + pr * bf_lo(vv[e]);
+                acc[2 * e + 1] = acc[2 * e + 1] * c + pr * bf_hi(vv[e]);
+            }
+            m = mn;
+        }
+    }
+    if (sub == 0) { s_m[grp] = m; s_l[grp] = l; }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_o[grp][8 * sub + e] = acc[e];
+    __syncthreads();
+    if (threadIdx.x < 64) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < 16; ++g) M = fmaxf(M, s_m[g]);
+        float o = 0.f, L = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+                const float w = exp2f(s_m[g] - M);        // a group without keys has m = -inf: weight 0
+                o = fmaf(s_o[g][threadIdx.x], w, o);
+                L = fmaf(s_l[g], w, L);
+            }
+        }
+        a.o[(long long)sinfo.x * a.o_row + (long long)head * a.o_head + threadIdx.x] = __float2bfloat16_rn(L > 0.f ? o / L : 0.f);
+    }
+}
+
 static int attn_short_launch(const AttnArgs& a, int max_q_len, int n_heads, int n_seqs, cudaStream_t st) {
     const int warps = (max_q_len + 15) / 16;
     const size_t smem = (size_t)(warps * 16 + 2 * kShortKeys) * 64 * 2;
@@ -355,6 +421,10 @@ extern "C" int ittai_attention_launch(const IttaiAttention* p, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     const int ql = p->max_q_len, nh = p->n_heads, ns = p->n_seqs;
     int rc;
+    if (p->head_dim == 64 && !p->causal && ql == 1) {
+        const cudaError_t e1 = launch_pdl(attn_q1_kernel, dim3(nh, ns), dim3(128), 0, st, 1, a);
+        return e1 == cudaSuccess ? ITTAI_OK : cuda_fail(e1, "launch attn_q1_kernel");
+    }
     if (p->head_dim == 128) rc = p->causal ? attn_launch<128, true, 4>(a, ql, nh, ns, st) : attn_launch<128, false, 4>(a, ql, nh, ns, st);
     else if (!p->causal && ql > 64 && ql <= 256 && p->max_kv_len > 0 && p->max_kv_len <= kShortKeys) rc = attn_short_launch(a, ql, nh, ns, st);
     else if (ql <= 64) rc = p->causal ? attn_launch<64, true, 4>(a, ql, nh, ns, st) : attn_launch<64, false, 4>(a, ql, nh, ns, st);

@@ -4,14 +4,15 @@
 // GEMM epilogues fuse (src/ittai/qwen3/base.py:110-129, src/ittai/siglip/kernel.py:266-333): bias, residual add,
 // GELU-tanh, SwiGLU on interleaved gate/up columns.
 //
-// Persistent kernel, one CTA per SM, looping over 128 x 256 output tiles (tile t = blockIdx.x + i * gridDim.x, N
-// fastest so that the CTAs of a wave share A tiles through L2, the reference's "N-tile outer, M-block inner" grouping:
-// src/ittai/qwen3/engine.py:53-63).  Warp 0 (one lane) streams 128 x 64 A tiles and 256 x 64 W tiles through a ring of
-// shared-memory stages with TMA (128-byte swizzle); warp 1 owns all 512 TMEM columns as two 256-column accumulators
-// and (one lane) issues four tcgen05.mma (M128 N256 K16) per stage, releasing the stage with tcgen05.commit; warps 2-5
-// read a finished accumulator with tcgen05.ld (each warp its own 32 TMEM lanes = 32 output rows) and run the epilogue
-// while the MMA warp already fills the other accumulator.  Every wait is bounded; a wait that runs out raises the
-// abort flag, all roles fall through to the common exit and TMEM is freed.
+// This file: argument checking and dispatch (M > 128 goes to the two-SM kernel of gemm2_sm100.cu), and the one-SM
+// kernel for M <= 128.  Persistent, one CTA per SM, looping over 128 x TN output tiles (tile t = blockIdx.x +
+// i * gridDim.x, N fastest, the reference's "N-tile outer, M-block inner" grouping: src/ittai/qwen3/engine.py:53-63).
+// Warp 0 (one lane) streams 128 x 64 A tiles and TN x 64 W tiles through a ring of shared-memory stages with TMA
+// (128-byte swizzle); warp 1 owns the TMEM columns as two TN-column accumulators and (one lane) issues four
+// tcgen05.mma (M128 N=TN K16) per stage, releasing the stage with tcgen05.commit; warps 2-9 read a finished
+// accumulator with tcgen05.ld (each warp its own 32 TMEM lanes = 32 output rows, two warps per lane quarter splitting
+// the columns) and run the epilogue while the MMA warp already fills the other accumulator.  Every wait is bounded; a
+// wait that runs out raises the abort flag, all roles fall through to the common exit and TMEM is freed.
 #include <cuda.h>
 
 #include "gemm_epilogue.cuh"
@@ -20,34 +21,41 @@
 
 namespace ittai {
 
-constexpr int GM = 128, GN = 256, GK = 64;
-constexpr int kGemmStages = 4;
+constexpr int GM = 128, GN = 256, GK = 64;     // GN: tile width of the wide kernel and the granularity N must have
 constexpr int kGemmThreads = 320;        // TMA warp, MMA warp, 8 epilogue warps
-constexpr uint32_t kStageBytesA = GM * GK * 2, kStageBytesB = GN * GK * 2;
-constexpr uint32_t kGemmSmem = kGemmStages * (kStageBytesA + kStageBytesB) + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr uint32_t kStageBytesA = GM * GK * 2;
+// Instantiated with tiles 128 x 64 and 8 stages: this kernel serves M <= 128 (larger problems go to the two-SM kernel),
+// where a GEMM has one row tile and only the number of column tiles puts CTAs to work (the MAP head: N = 768 would be 3
+// tiles of 256 columns but is 12 of 64).
+template <int TN, int STAGES>
+struct GemmCfg {
+    static constexpr uint32_t kStageBytesB = TN * GK * 2;
+    static constexpr uint32_t kSmem = STAGES * (kStageBytesA + kStageBytesB) + 1024 /*alignment*/ + 256 /*barriers*/;
+};
 constexpr uint32_t kGemmSpin = 1u << 24;
 constexpr uint32_t kTmemCols = 512;
 
+template <int TN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmArgs g) {
     extern __shared__ __align__(1024) unsigned char gsm_raw[];
     unsigned char* gsm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gsm_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sa = gsm;                                         // [stages][128 rows][128 B]
-    unsigned char* sb = gsm + kGemmStages * kStageBytesA;            // [stages][256 rows][128 B]
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sb + kGemmStages * kStageBytesB);
+    unsigned char* sb = gsm + STAGES * kStageBytesA;            // [stages][256 rows][128 B]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sb + STAGES * GemmCfg<TN, STAGES>::kStageBytesB);
     unsigned long long* full = bars;                                 // [stages]  TMA -> MMA
-    unsigned long long* empty = bars + kGemmStages;                  // [stages]  MMA -> TMA
-    unsigned long long* acc_full = bars + 2 * kGemmStages;           // [2]       MMA -> epilogue
-    unsigned long long* acc_empty = bars + 2 * kGemmStages + 2;      // [2]       epilogue -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kGemmStages + 4);
+    unsigned long long* empty = bars + STAGES;                  // [stages]  MMA -> TMA
+    unsigned long long* acc_full = bars + 2 * STAGES;           // [2]       MMA -> epilogue
+    unsigned long long* acc_empty = bars + 2 * STAGES + 2;      // [2]       epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = g.N / GN, tiles_m = (g.M + GM - 1) / GM, n_tiles = tiles_m * tiles_n;
+    const int tiles_n = g.N / TN, tiles_m = (g.M + GM - 1) / GM, n_tiles = tiles_m * tiles_n;
     const int n_kb = g.K / GK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         *abort_flag = 0;
         fence_mbar_init();
@@ -69,19 +77,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
                 const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                    const int s = it % kGemmStages, use = it / kGemmStages;
+                    const int s = it % STAGES, use = it / STAGES;
                     if (use > 0 && !mbar_wait_bounded(&empty[s], (use - 1) & 1, kGemmSpin)) { *abort_flag = 1; break; }
                     if (*abort_flag) break;
-                    mbar_expect_tx(&full[s], kStageBytesA + kStageBytesB);
+                    mbar_expect_tx(&full[s], kStageBytesA + GemmCfg<TN, STAGES>::kStageBytesB);
                     tma_load_2d(sa + s * kStageBytesA, &tm_a, kb * GK, tile_m * GM, &full[s]);
-                    tma_load_2d(sb + s * kStageBytesB, &tm_b, kb * GK, tile_n * GN, &full[s]);
+                    tma_load_2d(sb + s * GemmCfg<TN, STAGES>::kStageBytesB, &tm_b, kb * GK, tile_n * TN, &full[s]);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer
-            constexpr uint32_t idesc = umma_idesc_bf16(GM, GN);
+            constexpr uint32_t idesc = umma_idesc_bf16(GM, TN);
             int it = 0, local = 0;
             bool ok = true;
             GEMM_PROF(long long t_start = clock64(); long long w_full = 0; long long w_acc = 0;)
@@ -93,15 +101,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 GEMM_PROF(w_acc += clock64() - t0;)
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * GN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * TN);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                    const int s = it % kGemmStages, use = it / kGemmStages;
+                    const int s = it % STAGES, use = it / STAGES;
                     GEMM_PROF(long long t1 = clock64();)
                     ok = mbar_wait_bounded(&full[s], use & 1, kGemmSpin) && !*abort_flag;
                     GEMM_PROF(w_full += clock64() - t1;)
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * kStageBytesB);
+                    const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * GemmCfg<TN, STAGES>::kStageBytesB);
 #pragma unroll
                     for (int k = 0; k < GK / 16; ++k)      // 16 bf16 = 32 bytes = 2 descriptor address units per step
                         umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
@@ -135,11 +143,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after();
             const int row = tile_m * GM + q * 32 + lane;
 #pragma unroll 1
-            for (int c0 = col_half * (GN / 2); c0 < (col_half + 1) * (GN / 2); c0 += 32) {
+            for (int c0 = col_half * (TN / 2); c0 < (col_half + 1) * (TN / 2); c0 += 32) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + c0), r);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * TN + c0), r);
                 tmem_ld_wait();
-                if (row < g.M) epilogue_chunk(g, r, row, tile_n * GN + c0);
+                if (row < g.M) epilogue_chunk(g, r, row, tile_n * TN + c0);
             }
             tc_fence_before();
             __syncwarp();
@@ -195,13 +203,13 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     CUtensorMap tm_a, tm_b;
     int rc = make_tmap_bf16(&tm_a, a->a, a->m, a->k, ld_a, GM);
     if (rc != ITTAI_OK) return rc;
-    rc = make_tmap_bf16(&tm_b, a->w, a->n, a->k, ld_w, pair ? GN / 2 : GN);
+    rc = make_tmap_bf16(&tm_b, a->w, a->n, a->k, ld_w, pair ? GN / 2 : 64);
     if (rc != ITTAI_OK) return rc;
     static thread_local int attr_dev = -1, n_sms = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<64, 8>::kSmem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
         e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
@@ -225,8 +233,8 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.clk = g_gemm_clk;
 #endif
     if (pair) return gemm2_bf16_launch(tm_a, tm_b, g, st);
-    const int tiles = ((a->m + GM - 1) / GM) * (a->n / GN);
-    cudaError_t e = launch_pdl(gemm_bf16_kernel, dim3(tiles < n_sms ? tiles : n_sms), dim3(kGemmThreads), kGemmSmem, st, 1, tm_a, tm_b, g);
+    const int tiles = ((a->m + GM - 1) / GM) * (a->n / 64);
+    cudaError_t e = launch_pdl(gemm_bf16_kernel<64, 8>, dim3(tiles < n_sms ? tiles : n_sms), dim3(kGemmThreads), GemmCfg<64, 8>::kSmem, st, 1, tm_a, tm_b, g);
     if (e != cudaSuccess) return cuda_fail(e, "launch gemm_bf16_kernel");
     return ITTAI_OK;
 }

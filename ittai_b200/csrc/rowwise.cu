@@ -210,19 +210,19 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
 // SigLIP patch gather: fp32 pixels [B, 3, H, W] -> bf16 patches [B * (H/p) * (W/p), 3 * p * p] in (channel, row, col)
 // order, the order a Conv2d weight flattens to (reference src/ittai/siglip/kernel.py:633-637).  One thread per
 // 4 consecutive pixels of a patch row.
-__global__ void im2col_kernel(const float* __restrict__ px, bf16* __restrict__ out, int B, int H, int W, int p) {
+__global__ void __launch_bounds__(256) im2col_kernel(const float* __restrict__ px, bf16* __restrict__ out, int B, int H, int W, int p) {
     pdl_trigger();
     pdl_wait();
-    const int gw = W / p, gh = H / p, kp = 3 * p * p;
-    const size_t total = (size_t)B * gh * gw * kp / 4;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t e = i * 4;
-        const int col = (int)(e % kp);
-        const size_t patch = e / kp;
-        const int c = col / (p * p), py = (col / p) % p, pxx = col % p;
-        const int b = (int)(patch / (gh * gw)), pr = (int)(patch % (gh * gw)) / gw, pc = (int)(patch % gw);
-        const float4 v = *reinterpret_cast<const float4*>(px + (((size_t)b * 3 + c) * H + pr * p + py) * W + pc * p + pxx);
-        *reinterpret_cast<uint2*>(out + e) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    // 32-bit index arithmetic (the host checks that the element count fits); a thread's position inside a patch row
+    // group is fixed across its grid-stride steps when the stride is a multiple of the patch size in 4-pixel units
+    const unsigned gw = W / p, gh = H / p, pp = p * p, kp4 = 3 * pp / 4, p4 = p / 4;
+    const unsigned total = (unsigned)B * gh * gw * kp4;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned patch = i / kp4, col4 = i - patch * kp4;          // element = 4 consecutive pixels of a patch row
+        const unsigned c = col4 / (pp / 4), rem = col4 - c * (pp / 4), py = rem / p4, px4 = rem - py * p4;
+        const unsigned b = patch / (gh * gw), pi = patch - b * (gh * gw), pr = pi / gw, pc = pi - pr * gw;
+        const float4 v = __ldg(reinterpret_cast<const float4*>(px + (((size_t)b * 3 + c) * H + pr * p + py) * W + pc * p + px4 * 4));
+        *reinterpret_cast<uint2*>(out + (size_t)i * 4) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
     }
 }
 
@@ -316,6 +316,7 @@ extern "C" int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void
 
 extern "C" int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, void* stream) {
     if (!pixels || !patches || batch < 1 || patch % 4 || height % patch || width % patch) { set_error("im2col: bad argument"); return ITTAI_E_ARG; }
+    if ((unsigned long long)batch * height * width * 3 / 4 >= (1ull << 31)) { set_error("im2col: more than 2^33 pixels values in one call"); return ITTAI_E_ARG; }
     const size_t total = (size_t)batch * height * width * 3 / 4;
     const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     launch_pdl(im2col_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, 1, pixels, (bf16*)patches, batch, height, width, patch);
