@@ -72,16 +72,14 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // ---- dot products of 8 bf16 weights (one 16-byte chunk) with 8 fp32 activations ---------------------
+// Packed fp32 FMAs (two multiply-adds per instruction): even and odd elements accumulate separately and meet at the end.
 __device__ __forceinline__ float dot8(const uint4& w, const float* x, float acc) {
-    acc = fmaf(bf_lo(w.x), x[0], acc);
-    acc = fmaf(bf_hi(w.x), x[1], acc);
-    acc = fmaf(bf_lo(w.y), x[2], acc);
-    acc = fmaf(bf_hi(w.y), x[3], acc);
-    acc = fmaf(bf_lo(w.z), x[4], acc);
-    acc = fmaf(bf_hi(w.z), x[5], acc);
-    acc = fmaf(bf_lo(w.w), x[6], acc);
-    acc = fmaf(bf_hi(w.w), x[7], acc);
-    return acc;
+    float2 a = make_float2(acc, 0.f);
+    a = __ffma2_rn(make_float2(bf_lo(w.x), bf_hi(w.x)), make_float2(x[0], x[1]), a);
+    a = __ffma2_rn(make_float2(bf_lo(w.y), bf_hi(w.y)), make_float2(x[2], x[3]), a);
+    a = __ffma2_rn(make_float2(bf_lo(w.z), bf_hi(w.z)), make_float2(x[4], x[5]), a);
+    a = __ffma2_rn(make_float2(bf_lo(w.w), bf_hi(w.w)), make_float2(x[6], x[7]), a);
+    return a.x + a.y;
 }
 
 // ---- reductions ----------------------------------------------------------------------------------

@@ -57,7 +57,8 @@ struct Cta {
     const IttaiQwen3Decode& p;
     Q3Workspace ws;
     SmemHdr* hdr;
-    float* xs;          // [NB][FF] activations of the current GEMV
+    uint32_t* xs;       // [NB][FF/2] activations of the current GEMV as packed bf16 pairs (they are bf16 values: half the
+                        // shared-memory traffic of fp32 and conflict-free 128-bit reads)
     SmemAttn* at;       // aliases xs
     int cta, ncta, tid, lane, warp;
     Waiter w;
@@ -194,8 +195,11 @@ __device__ __forceinline__ const bf16* stream_acquire(Cta& c, uint32_t n, bool& 
 // load issued after the wait would put a full memory round trip on the critical path of every layer.  `ok` is this
 // thread's verdict on the waits that produced `u`; the first barrier both publishes the per-warp sums of squares and
 // collects the verdicts.  Returns false (uniformly) when any thread's wait failed.
+// With `ring_entry` non-null the wait for this phase's weights in the ring is folded in: its verdict rides on the barrier
+// that publishes xs, instead of costing a barrier of its own.
 template <int NB>
-__device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[NB], uint32_t gw, bool ok) {
+__device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[NB], uint32_t gw, bool ok,
+                                                   const bf16** ring_entry = nullptr) {
     static_assert(kThreads * 2 == D, "one bf16 pair per thread");
     static_assert(NB * kWarps <= 32 * 4, "per-warp partial sums must fit the scratch");
 #pragma unroll
@@ -212,8 +216,12 @@ __device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[N
 #pragma unroll
         for (int i = 0; i < kWarps; ++i) tot += c.hdr->red[b * kWarps + i];
         const float rstd = 1.0f / sqrtf(tot * (1.0f / D) + c.p.eps);
-        c.xs[b * FF + 2 * c.tid] = bf16r(bf16r(bf_lo(u[b]) * rstd) * bf_lo(gw));
-        c.xs[b * FF + 2 * c.tid + 1] = bf16r(bf16r(bf_hi(u[b]) * rstd) * bf_hi(gw));
+        c.xs[b * (FF / 2) + c.tid] = pack_bf16x2(bf16r(bf_lo(u[b]) * rstd) * bf_lo(gw), bf16r(bf_hi(u[b]) * rstd) * bf_hi(gw));
+    }
+    if (ring_entry != nullptr) {
+        const unsigned char* ptr = stream_wait(c.st, c.st.consumed, c.w);
+        *ring_entry = reinterpret_cast<const bf16*>(ptr);
+        return !cta_or(ptr == nullptr);
     }
     cta_sync();
     return true;
@@ -221,7 +229,7 @@ __device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[N
 
 // Waits for NB rows of K bf16 values in flagged-word format and spreads them into xs as fp32.
 template <int NB, int K>
-__device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, uint32_t tag, int what) {
+__device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, uint32_t tag, int what, const bf16** ring_entry = nullptr) {
     bool ok = true;
 #pragma unroll
     for (int b = 0; b < NB; ++b)
@@ -230,9 +238,13 @@ __device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, u
             const int wd = c.tid + i * kThreads;
             uint32_t u = 0;
             ok = ok && wait_word(c.w, src + (size_t)b * (K / 2) + wd, tag, u, what);
-            c.xs[b * FF + 2 * wd] = bf_lo(u);
-            c.xs[b * FF + 2 * wd + 1] = bf_hi(u);
+            c.xs[b * (FF / 2) + wd] = u;
         }
+    if (ring_entry != nullptr) {
+        const unsigned char* ptr = stream_wait(c.st, c.st.consumed, c.w);
+        *ring_entry = reinterpret_cast<const bf16*>(ptr);
+        ok = ok && ptr != nullptr;
+    }
     return all_ok(ok);
 }
 
@@ -246,13 +258,12 @@ __device__ __forceinline__ uint4 load_w(const bf16* p) {
     else return *reinterpret_cast<const uint4*>(p);
 }
 
-__device__ __forceinline__ void load_xreg(const float* xs, int lane, float (&xr)[32]) {
+__device__ __forceinline__ void load_xreg(const uint32_t* xs, int lane, float (&xr)[32]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float4 a = *reinterpret_cast<const float4*>(xs + (lane + 32 * i) * 8);
-        const float4 b = *reinterpret_cast<const float4*>(xs + (lane + 32 * i) * 8 + 4);
-        xr[i * 8 + 0] = a.x; xr[i * 8 + 1] = a.y; xr[i * 8 + 2] = a.z; xr[i * 8 + 3] = a.w;
-        xr[i * 8 + 4] = b.x; xr[i * 8 + 5] = b.y; xr[i * 8 + 6] = b.z; xr[i * 8 + 7] = b.w;
+        const uint4 q = *reinterpret_cast<const uint4*>(xs + (lane + 32 * i) * 4);
+        xr[i * 8 + 0] = bf_lo(q.x); xr[i * 8 + 1] = bf_hi(q.x); xr[i * 8 + 2] = bf_lo(q.y); xr[i * 8 + 3] = bf_hi(q.y);
+        xr[i * 8 + 4] = bf_lo(q.z); xr[i * 8 + 5] = bf_hi(q.z); xr[i * 8 + 6] = bf_lo(q.w); xr[i * 8 + 7] = bf_hi(q.w);
     }
 }
 
@@ -273,9 +284,9 @@ __device__ __forceinline__ void dot_subrows_xreg(const bf16* const (&wp)[R], con
     }
 }
 
-// xseg points at the 1024-float segment this sub-row multiplies, for batch row 0; batch rows are FF floats apart.
+// xseg points at the 1024-value segment (512 words) this sub-row multiplies, for batch row 0; batch rows are FF/2 words apart.
 template <bool GLOBAL, int NB, int R>
-__device__ __forceinline__ void dot_subrows_smem(const bf16* const (&wp)[R], const float* const (&xseg)[R], int lane,
+__device__ __forceinline__ void dot_subrows_smem(const bf16* const (&wp)[R], const uint32_t* const (&xseg)[R], int lane,
                                                  float (&acc)[R][NB]) {
     uint4 w[R][4];
 #pragma unroll
@@ -289,10 +300,8 @@ __device__ __forceinline__ void dot_subrows_smem(const bf16* const (&wp)[R], con
             float a = 0.f;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float* x = xseg[r] + b * FF + (lane + 32 * i) * 8;
-                float xv[8];
-                *reinterpret_cast<float4*>(xv) = *reinterpret_cast<const float4*>(x);
-                *reinterpret_cast<float4*>(xv + 4) = *reinterpret_cast<const float4*>(x + 4);
+                const uint4 q = *reinterpret_cast<const uint4*>(xseg[r] + b * (FF / 2) + (lane + 32 * i) * 4);
+                const float xv[8] = {bf_lo(q.x), bf_hi(q.x), bf_lo(q.y), bf_hi(q.y), bf_lo(q.z), bf_hi(q.z), bf_lo(q.w), bf_hi(q.w)};
                 a = dot8(w[r][i], xv, a);
             }
             acc[r][b] = warp_sum(a);
@@ -309,7 +318,7 @@ __device__ __forceinline__ void dot_rows_k1024(Cta& c, const bf16* const (&wp)[R
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r][0] = a[r];
     } else {
-        const float* xseg[R];
+        const uint32_t* xseg[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) xseg[r] = c.xs;
         dot_subrows_smem<GLOBAL, NB, R>(wp, xseg, c.lane, acc);
@@ -329,15 +338,13 @@ __device__ bool phase_qkv(Cta& c, int l) {
         if (l == 0) u[b] = ldcg32(reinterpret_cast<const bf16*>(p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * c.tid);
         else ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_QKV);
     }
-    if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
-    float xr[32];
-    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     int p0, p1;
     split_range(DQKV / 2, c.ncta, c.cta, p0, p1);
+    const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok, p1 > p0 ? &W : nullptr)) return false;
     if (p1 == p0) return true;
-    bool okw;
-    const bf16* W = stream_acquire(c, c.st.consumed, okw);     // this CTA's rows [2*p0, 2*p1), contiguous
-    if (!okw) return false;
+    float xr[32];
+    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     for (int pr = p0 + c.warp; pr < p1; pr += kWarps) {
         const bf16* wp[2] = {W + (size_t)(2 * (pr - p0)) * D, W + (size_t)(2 * (pr - p0) + 1) * D};
         float acc[2][NB];
@@ -502,10 +509,15 @@ __device__ bool phase_attn(Cta& c, int l) {
                 uint4 vr = make_uint4(0, 0, 0, 0);
                 if (tl < ring_rows) vr = *reinterpret_cast<const uint4*>(vt + (size_t)tl * HD + sub * 8);
                 else if (has_new && j * kTile + tl == it.n_old) vr = *reinterpret_cast<const uint4*>(at->vnew + sub * 8);
-                const float ve[8] = {bf_lo(vr.x), bf_hi(vr.x), bf_lo(vr.y), bf_hi(vr.y),
-                                     bf_lo(vr.z), bf_hi(vr.z), bf_lo(vr.w), bf_hi(vr.w)};
+                const uint32_t vw[4] = {vr.x, vr.y, vr.z, vr.w};
+                const float2 pp0 = make_float2(p0, p0), pp1 = make_float2(p1, p1);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) { acc0[e] = fmaf(p0, ve[e], acc0[e]); acc1[e] = fmaf(p1, ve[e], acc1[e]); }
+                for (int e = 0; e < 4; ++e) {       // packed fp32 FMAs: two dims per instruction
+                    const float2 ve = make_float2(bf_lo(vw[e]), bf_hi(vw[e]));
+                    const float2 r0 = __ffma2_rn(pp0, ve, make_float2(acc0[2 * e], acc0[2 * e + 1]));
+                    const float2 r1 = __ffma2_rn(pp1, ve, make_float2(acc1[2 * e], acc1[2 * e + 1]));
+                    acc0[2 * e] = r0.x; acc0[2 * e + 1] = r0.y; acc1[2 * e] = r1.x; acc1[2 * e + 1] = r1.y;
+                }
             }
             m0 = mt0; m1 = mt1;
             if (from_ring) stream_release(c.st, 2);
@@ -625,12 +637,10 @@ __device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uin
         else
             ok = wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw_early, 32 + what);
     }
-    if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what)) return false;
+    const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
+    if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what, p1 > p0 ? &W : nullptr)) return false;
     c.t_ready = clock64();
     if (p1 == p0) return all_ok(ok);
-    bool okw;
-    const bf16* W = stream_acquire(c, c.st.consumed, okw);     // this CTA's rows [2*p0, 2*p1), contiguous
-    if (!okw) return false;
     const int n_sub = 2 * (p1 - p0) * S;
     float* sub = c.hdr->sub;
     for (int base = 0; base < n_sub; base += kSlots) {
@@ -639,7 +649,7 @@ __device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uin
             const int gsr = base + sr;
             const int seg = gsr % S;
             const bf16* wp[1] = {W + (size_t)gsr * 1024};
-            const float* xseg[1] = {c.xs + seg * 1024};
+            const uint32_t* xseg[1] = {c.xs + seg * 512};
             float acc[1][NB];
             dot_subrows_smem<false, NB, 1>(wp, xseg, c.lane, acc);
             if (c.lane == 0) {
@@ -686,15 +696,13 @@ __device__ bool phase_gu(Cta& c, int l) {
     bool ok = true;
 #pragma unroll
     for (int b = 0; b < NB; ++b) ok = ok && wait_word(c.w, c.ws.hmid + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_GU);
-    if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
-    float xr[32];
-    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     int u0, u1;
     split_range(FF / 2, c.ncta, c.cta, u0, u1);      // unit = two activations = four weight rows = one flagged word
+    const bf16* W = nullptr;
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok, u1 > u0 ? &W : nullptr)) return false;
     if (u1 == u0) return true;
-    bool okw;
-    const bf16* W = stream_acquire(c, c.st.consumed, okw);
-    if (!okw) return false;
+    float xr[32];
+    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     for (int un = u0 + c.warp; un < u1; un += kWarps) {
         const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
         float a0[NB], a1[NB];
@@ -873,7 +881,7 @@ __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
 // global pointers of a struct returned by value from a helper that also receives the shared-memory base, so there is
 // deliberately no make_cta() function.
 #define ITTAI_MAKE_CTA(p, wsp, smem, nb, ring_bytes)                                                              \
-    Cta c{p, wsp, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<float*>(smem + kHdrBytes),                   \
+    Cta c{p, wsp, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<uint32_t*>(smem + kHdrBytes),                   \
           reinterpret_cast<SmemAttn*>(smem + kHdrBytes), (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x,       \
           (int)(threadIdx.x & 31), (int)(threadIdx.x >> 5),                                                       \
           Waiter{wsp.sync, p.status, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit},                     \
