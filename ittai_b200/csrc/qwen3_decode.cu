@@ -48,7 +48,7 @@ struct SmemAttn {
 };
 constexpr size_t kHdrBytes = (sizeof(SmemHdr) + 255) / 256 * 256;
 __host__ __device__ constexpr size_t q3_fixed_smem_bytes(int nb) {
-    size_t xs = (size_t)nb * FF * sizeof(float);
+    size_t xs = (size_t)nb * (FF / 2) * sizeof(uint32_t);      // activations as packed bf16 pairs
     size_t at = sizeof(SmemAttn);
     return kHdrBytes + ((xs > at ? xs : at) + 255) / 256 * 256;
 }
@@ -358,6 +358,14 @@ __device__ bool phase_qkv(Cta& c, int l) {
     return true;
 }
 
+// 2^x on the special-function unit without exp2f's range fix-ups (2^-inf = 0; arguments here are differences of
+// finite log2-domain scores or -inf).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ---- phase: QK-RMSNorm + RoPE + KV append + split-K GQA attention + merge -----------------------------
 // Work item = (sequence b, kv head g, split s) = CTA index.  Scores live in the log2 domain with the softmax scale
 // folded into q, as the reference does (src/ittai/qwen3/config.py:6-7).  Old cache rows arrive through the ring in tiles
@@ -459,15 +467,20 @@ __device__ bool phase_attn(Cta& c, int l) {
         // positions of this split: n_old rows from the ring, then (has_new) the current token's row
         const int n_pos = it.n_old + (has_new ? 1 : 0);
         const int n_ring_tiles = (it.n_old + kTile - 1) / kTile;
+        int rel = 0;                 // ring tiles already handed back
+        bool okr = true;
+        // two tiles (K and V of each: 128 KB) are held before they go back, when the ring has room for that and more
+        const int hold = c.st.ring_bytes >= 5u * kTile * HD * 2 ? 2 : 1;
         for (int j = 0; j * kTile < n_pos; ++j) {
             const int ring_rows = it.n_old - j * kTile < 0 ? 0 : (it.n_old - j * kTile < kTile ? it.n_old - j * kTile : kTile);
             const bool from_ring = j < n_ring_tiles;
             const bf16* kt = nullptr;
             const bf16* vt = nullptr;
             if (from_ring) {
-                const unsigned char* pk = stream_wait(c.st, c.st.consumed, c.w);
-                const unsigned char* pv = stream_wait(c.st, c.st.consumed + 1, c.w);
-                if (!all_ok(pk != nullptr && pv != nullptr)) return false;
+                const unsigned char* pk = stream_wait(c.st, c.st.consumed + 2 * (j - rel), c.w);
+                const unsigned char* pv = stream_wait(c.st, c.st.consumed + 2 * (j - rel) + 1, c.w);
+                // warp-uniform exit (the shuffles below need every lane); the CTA's verdict is collected at the next barrier
+                if (__any_sync(0xffffffffu, pk == nullptr || pv == nullptr)) { okr = false; break; }
                 kt = reinterpret_cast<const bf16*>(pk);
                 vt = reinterpret_cast<const bf16*>(pv);
             }
@@ -497,13 +510,13 @@ __device__ bool phase_attn(Cta& c, int l) {
 #pragma unroll
             for (int r = 0; r < kTile / 32; ++r) { mt0 = fmaxf(mt0, s0[r]); mt1 = fmaxf(mt1, s1[r]); }
             const float ms0 = mt0 == -INFINITY ? 0.f : mt0, ms1 = mt1 == -INFINITY ? 0.f : mt1;   // no (-inf) - (-inf)
-            const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
+            const float c0 = ex2_approx(m0 - ms0), c1 = ex2_approx(m1 - ms1);
             l0 *= c0; l1 *= c1;
 #pragma unroll
             for (int e = 0; e < 8; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
 #pragma unroll
             for (int r = 0; r < kTile / 32; ++r) {
-                const float p0 = exp2f(s0[r] - ms0), p1 = exp2f(s1[r] - ms1);
+                const float p0 = ex2_approx(s0[r] - ms0), p1 = ex2_approx(s1[r] - ms1);
                 l0 += p0; l1 += p1;
                 const int tl = r * 32 + c.warp * 2 + half;
                 uint4 vr = make_uint4(0, 0, 0, 0);
@@ -520,15 +533,18 @@ __device__ bool phase_attn(Cta& c, int l) {
                 }
             }
             m0 = mt0; m1 = mt1;
-            if (from_ring) stream_release(c.st, 2);
+            // the half-warps never synchronise inside a tile; ring entries go back two tiles at a time (one CTA barrier
+            // per 128 KB instead of two per tile), which is everything at batch 1
+            if (from_ring && j - rel == hold - 1) { stream_release(c.st, 2 * hold); rel += hold; }
         }
+        if (n_ring_tiles > rel) stream_release(c.st, 2 * (n_ring_tiles - rel));
         // -- merge the two halves of each warp, then the 16 warps, and publish (m, l, o) of this split
         {
             const float pm0 = __shfl_xor_sync(0xffffffffu, m0, 16), pm1 = __shfl_xor_sync(0xffffffffu, m1, 16);
             const float pl0 = __shfl_xor_sync(0xffffffffu, l0, 16), pl1 = __shfl_xor_sync(0xffffffffu, l1, 16);
             const float M0 = fmaxf(m0, pm0), M1 = fmaxf(m1, pm1);
             const float S0 = M0 == -INFINITY ? 0.f : M0, S1 = M1 == -INFINITY ? 0.f : M1;
-            const float w0 = exp2f(m0 - S0), w1 = exp2f(m1 - S1), v0 = exp2f(pm0 - S0), v1 = exp2f(pm1 - S1);
+            const float w0 = ex2_approx(m0 - S0), w1 = ex2_approx(m1 - S1), v0 = ex2_approx(pm0 - S0), v1 = ex2_approx(pm1 - S1);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float o0 = __shfl_xor_sync(0xffffffffu, acc0[e], 16), o1 = __shfl_xor_sync(0xffffffffu, acc1[e], 16);
@@ -544,7 +560,7 @@ __device__ bool phase_attn(Cta& c, int l) {
                 }
             }
         }
-        cta_sync();
+        if (cta_or(!okr)) return false;
         uint64_t* part = c.ws.part + (size_t)c.cta * Q3_PART_WORDS;
         if (c.tid < 2 * HD) {
             const int h = c.tid / HD, d = c.tid % HD;
@@ -555,7 +571,7 @@ __device__ bool phase_attn(Cta& c, int l) {
             float o = 0.f, ls = 0.f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
-                const float sc = exp2f(at->wm[w][h] - Ms);
+                const float sc = ex2_approx(at->wm[w][h] - Ms);
                 o = fmaf(at->ored[w][h][d], sc, o);
                 ls = fmaf(at->wl[w][h], sc, ls);
             }
@@ -605,7 +621,7 @@ __device__ bool phase_attn(Cta& c, int l) {
                 }
             }
             const float M = warp_max(m);
-            const float wk = exp2f(m - (M == -INFINITY ? 0.f : M));
+            const float wk = ex2_approx(m - (M == -INFINITY ? 0.f : M));
             const float Ls = warp_sum(l * wk), O0 = warp_sum(o0 * wk), O1 = warp_sum(o1 * wk);
             if (c.lane == 0)
                 st_flagged(c.ws.attn + (size_t)b * (DQ / 2) + ((2 * g + h) * HD + d0 + dd) / 2, pack_bf16x2(O0 / Ls, O1 / Ls), tag);
