@@ -21,32 +21,19 @@
 namespace ittai {
 
 constexpr int PM = 256, PN = 256, PK = 64;   // pair tile
-#ifndef ITTAI_GEMM2_STAGES
-#define ITTAI_GEMM2_STAGES 5
-#endif
-constexpr int kStages2 = ITTAI_GEMM2_STAGES;
-#ifndef ITTAI_EPI_WARPS
-#define ITTAI_EPI_WARPS 8
-#endif
-constexpr int kEpiWarps = ITTAI_EPI_WARPS;         // 8 or 16: 2 or 4 warps per TMEM lane quarter
+constexpr int kStages2 = 5;                       // 4, 5 and 6 stages measured the same: the main loop is supply-bound
+constexpr int kEpiWarps = 8;                      // 2 warps per TMEM lane quarter (16 warps were slower: the epilogue is
+                                                  // bound by the conversion pipe and shared memory, not by latency)
 constexpr int kEpiCols = PN / (kEpiWarps / 4);    // accumulator columns per epilogue warp
 constexpr int kThreads2 = 64 + 32 * kEpiWarps;
+static_assert(kEpiCols == 128, "stats_out slots and the bias / column-sum slices assume 128 columns per epilogue warp");
 constexpr uint32_t kHalfA = 128 * PK * 2, kHalfB = 128 * PK * 2;                // per CTA per stage
 constexpr uint32_t kStageOut = 3 * 2048;                                         // per epilogue warp: three tiles of 32 rows x 64 B
 constexpr uint32_t kSmem2 = kStages2 * (kHalfA + kHalfB) + kEpiWarps * kStageOut + 2 * 4096 /*bias and column-sum slices*/ + 1024 /*alignment*/ + 512 /*barriers*/;
 constexpr uint32_t kSpin2 = 1u << 24;
-#ifdef ITTAI_TILE_MFAST
-#define TILE_M(t) ((t) % tiles_m)
-#define TILE_N(t) ((t) / tiles_m)
-#else
+// tile order: N fastest (M-fastest measured the same)
 #define TILE_M(t) ((t) / tiles_n)
 #define TILE_N(t) ((t) % tiles_n)
-#endif
-#ifdef ITTAI_EPI_SKIP_STG
-#define EPI_STORE_LIMIT (g.M - 1000000)
-#else
-#define EPI_STORE_LIMIT g.M
-#endif
 constexpr uint32_t kTmemCols2 = 512;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -5,10 +5,6 @@
 
 #include "../../include/ittai_b200.h"
 
-#ifndef ITTAI_TMAP_L2PROMO
-#define ITTAI_TMAP_L2PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
-#endif
-
 namespace ittai {
 
 void set_error(const char* fmt, ...);
@@ -39,7 +35,7 @@ inline int make_tmap_bf16(CUtensorMap* tm, const void* ptr, long long rows, long
     const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, ITTAI_TMAP_L2PROMO,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld)", (int)r, rows, cols, ld); return ITTAI_E_CUDA; }
     return ITTAI_OK;
