@@ -175,8 +175,27 @@ int ittai_qwen3_phase_launch(const IttaiQwen3Decode* p, int phase, int layer, vo
 enum {
     ITTAI_EPI_NONE = 0,   /* out = bf16(acc [+ bias]) [then + residual, rounded again]                  */
     ITTAI_EPI_GELU = 1,   /* out = bf16(gelu_tanh(bf16(acc + bias)))                                      */
-    ITTAI_EPI_SWIGLU = 2  /* columns (2i, 2i+1) = (gate, up): out[:, i] = bf16(bf16(silu(gate)) * up); N/2 columns */
+    ITTAI_EPI_SWIGLU = 2, /* columns (2i, 2i+1) = (gate, up): out[:, i] = bf16(bf16(silu(gate)) * up); N/2 columns */
+    ITTAI_EPI_QKROPE = 3  /* Qwen3 QKV projection (N = 4096 = 16 q | 8 k | 8 v heads of 128, M > 128, no bias / residual):
+                             the work of ittai_qwen3_qk_rope_scatter inside the epilogue.  q heads: RMSNorm + RoPE, stored
+                             to `out`; k heads: RMSNorm + RoPE, stored to the cache row of the token; v heads: copied to
+                             the cache row.  The k and v columns of `out` are not written.  Needs IttaiGemm.qk_rope.
+                             (reference: the qkv epilogue, src/ittai/qwen3/base.py:84-109) */
 };
+
+/* Arguments of ITTAI_EPI_QKROPE: the same arrays ittai_qwen3_qk_rope_scatter takes (all device pointers). */
+typedef struct IttaiQkRope {
+    const void* qn;        /* [128] bf16 q_norm gain of this layer */
+    const void* kn;        /* [128] bf16 k_norm gain */
+    const void* rope;      /* [positions][128] bf16: cos[0..63] | sin[0..63] */
+    const int32_t* pos;    /* [M] rotary position of each token */
+    const int32_t* seq;    /* [M] cache sequence of each token */
+    const int32_t* slot;   /* [M] cache row of each token */
+    void* kcache_layer;    /* [B, 8, kv_cap, 128] bf16 */
+    void* vcache_layer;
+    int32_t kv_cap;
+    float eps;
+} IttaiQkRope;
 
 /* out[M, N] = a[M, K] * w[N, K]^T with fp32 accumulation.  a, w, residual, out are bf16 row-major; bias is fp32.
  * N must be a multiple of 256 and K of 64; leading dimensions of 0 mean "dense".  `status` must be zeroed by the
@@ -204,6 +223,7 @@ typedef struct IttaiGemm {
                                arriving tile, src/ittai/siglip/kernel.py:335-364); plain stores, no atomics */
     int32_t stats_parts;
     float stats_eps;        /* LayerNorm epsilon, used when stats_parts > 0 */
+    const IttaiQkRope* qk_rope; /* host pointer, read during the call; required by ITTAI_EPI_QKROPE, NULL otherwise */
 } IttaiGemm;
 
 /* Replaces the tiled GEMM main loops + epilogues of the reference's megakernels

@@ -25,7 +25,7 @@ EXPORTS = (
     "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows", "ittai_row_stats",
     "ittai_qwen3_qk_rope_scatter", "ittai_siglip_im2col", "ittai_embed_rows", "ittai_qwen3_final_pool",
 )
-EPI_NONE, EPI_GELU, EPI_SWIGLU = range(3)
+EPI_NONE, EPI_GELU, EPI_SWIGLU, EPI_QKROPE = range(4)
 
 
 class IttaiError(RuntimeError):
@@ -47,6 +47,14 @@ class Qwen3Decode(C.Structure):
     ]
 
 
+class QkRope(C.Structure):
+    """Mirror of ``struct IttaiQkRope``."""
+    _fields_ = [
+        ("qn", C.c_void_p), ("kn", C.c_void_p), ("rope", C.c_void_p), ("pos", C.c_void_p), ("seq", C.c_void_p),
+        ("slot", C.c_void_p), ("kcache_layer", C.c_void_p), ("vcache_layer", C.c_void_p), ("kv_cap", C.c_int32), ("eps", C.c_float),
+    ]
+
+
 class Gemm(C.Structure):
     """Mirror of ``struct IttaiGemm``."""
     _fields_ = [
@@ -54,7 +62,7 @@ class Gemm(C.Structure):
         ("ld_a", C.c_int32), ("ld_w", C.c_int32), ("ld_out", C.c_int32), ("ld_res", C.c_int32),
         ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
         ("out", C.c_void_p), ("status", C.c_void_p), ("row_stats", C.c_void_p), ("col_sums", C.c_void_p),
-        ("stats_out", C.c_void_p), ("stats_parts", C.c_int32), ("stats_eps", C.c_float),
+        ("stats_out", C.c_void_p), ("stats_parts", C.c_int32), ("stats_eps", C.c_float), ("qk_rope", C.POINTER(QkRope)),
     ]
 
 

@@ -83,6 +83,91 @@ __device__ __forceinline__ void umma_commit_pair(void* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
+// ITTAI_EPI_QKROPE: one warp = 32 tokens x one head (its 128 accumulator columns).  The thread that owns a token's row
+// rounds the 128 values to bf16 (the Linear output), and for q / k heads applies the head RMSNorm and the half-split
+// rotary embedding with the rounding steps of the eager modules (the arithmetic of qk_rope_scatter_kernel); q goes
+// to the output matrix through the staging tile and a TMA store, k and v go to their cache rows through the staging
+// tile with four lanes per 64-byte row piece (whole sectors), each lane having looked up the rows it stores.
+__device__ __forceinline__ void epilogue_qkrope(const GemmArgs& g, const CUtensorMap* tm_out, uint32_t t_addr, unsigned char* so,
+                                                const uint32_t* sgain, uint32_t& cc, int row0, int col0, int lane) {
+    constexpr int HD = ITTAI_Q3_HD, NKV = ITTAI_Q3_NKV;
+    const int head = col0 / HD, t = row0 + lane;
+    const bool valid = t < g.M;
+    uint32_t pk[64];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + 32 * ch, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[16 * ch + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    }
+    if (head < 24) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) { const float lo = bf_lo(pk[i]), hi = bf_hi(pk[i]); ss = fmaf(lo, lo, fmaf(hi, hi, ss)); }
+        const float rstd = 1.0f / sqrtf(ss * (1.0f / HD) + g.rope.eps);
+        const bf16* rp = reinterpret_cast<const bf16*>(g.rope.rope) + (size_t)(valid ? g.rope.pos[t] : 0) * HD;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {                  // elements 8jj .. 8jj+7 and their partners 64 + the same
+            const uint4 cw = *reinterpret_cast<const uint4*>(rp + 8 * jj), sw = *reinterpret_cast<const uint4*>(rp + HD / 2 + 8 * jj);
+            const uint4 ga = *reinterpret_cast<const uint4*>(sgain + 4 * jj), gb = *reinterpret_cast<const uint4*>(sgain + 32 + 4 * jj);
+            const uint32_t wc[4] = {cw.x, cw.y, cw.z, cw.w}, ws[4] = {sw.x, sw.y, sw.z, sw.w};
+            const uint32_t wga[4] = {ga.x, ga.y, ga.z, ga.w}, wgb[4] = {gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float lo[2], hi[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float xa = h ? bf_hi(pk[4 * jj + j]) : bf_lo(pk[4 * jj + j]), xb = h ? bf_hi(pk[32 + 4 * jj + j]) : bf_lo(pk[32 + 4 * jj + j]);
+                    const float g0 = h ? bf_hi(wga[j]) : bf_lo(wga[j]), g1 = h ? bf_hi(wgb[j]) : bf_lo(wgb[j]);
+                    const float cs = h ? bf_hi(wc[j]) : bf_lo(wc[j]), sn = h ? bf_hi(ws[j]) : bf_lo(ws[j]);
+                    const float x0 = bf16r(bf16r(xa * rstd) * g0), x1 = bf16r(bf16r(xb * rstd) * g1);
+                    lo[h] = bf16r(bf16r(x0 * cs) + bf16r(-x1 * sn));
+                    hi[h] = bf16r(bf16r(x1 * cs) + bf16r(x0 * sn));
+                }
+                pk[4 * jj + j] = pack_bf16x2(lo[0], lo[1]);
+                pk[32 + 4 * jj + j] = pack_bf16x2(hi[0], hi[1]);
+            }
+        }
+    }
+    const int swz = (lane >> 1) & 3;
+    // cache rows of the four tokens this lane stores pieces of (k / v heads)
+    bf16* dst[4] = {nullptr, nullptr, nullptr, nullptr};
+    if (head >= 16) {
+        bf16* cache = reinterpret_cast<bf16*>(head < 24 ? g.rope.kcache_layer : g.rope.vcache_layer);
+        const int kvh = head < 24 ? head - 16 : head - 24;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int tt = row0 + (lane >> 2) + 8 * i;
+            if (tt < g.M) dst[i] = cache + (((size_t)g.rope.seq[tt] * NKV + kvh) * g.rope.kv_cap + g.rope.slot[tt]) * HD + 8 * (lane & 3);
+        }
+    }
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch, ++cc) {
+        unsigned char* sto = so + (cc % 3u) * 2048;
+        if (lane == 0) tma_store_wait_read<2>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(sto + lane * 64 + ((j ^ swz) << 4)) = make_uint4(pk[16 * ch + 4 * j], pk[16 * ch + 4 * j + 1], pk[16 * ch + 4 * j + 2], pk[16 * ch + 4 * j + 3]);
+        if (head < 16) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) { tma_store_2d(tm_out, sto, col0 + 32 * ch, row0); tma_store_commit(); }
+        } else {
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int rr = (lane >> 2) + 8 * i;
+                const uint4 val = *reinterpret_cast<const uint4*>(sto + rr * 64 + (((lane & 3) ^ ((rr >> 1) & 3)) << 4));
+                if (dst[i] != nullptr) *reinterpret_cast<uint4*>(dst[i] + 32 * ch) = val;
+            }
+            __syncwarp();
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res, const GemmArgs g) {
@@ -228,6 +313,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 }
             }
             float st1 = 0.f, st2 = 0.f;                               // statistics of this row's output slice
+            if (g.epi == ITTAI_EPI_QKROPE && col0 < ITTAI_Q3_DQ + ITTAI_Q3_DKV && lane < 16)   // this head's norm gain, 128 bf16
+                *reinterpret_cast<uint4*>(sbias + 4 * lane) = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(col0 < ITTAI_Q3_DQ ? g.rope.qn : g.rope.kn) + 8 * lane);
             __syncwarp();
             bool ok = true;
             GEMM_PROF(long long t0 = clock64();)
@@ -240,6 +327,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if (!ok) { *abort_flag = 1; break; }
             GEMM_PROF(long long t1 = clock64(); e_wait += t1 - t0;)
             tc_fence_after();
+            if (g.epi == ITTAI_EPI_QKROPE) {
+                epilogue_qkrope(g, &tm_out, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + kEpiCols * cq), so,
+                                reinterpret_cast<const uint32_t*>(sbias), cc, row0, col0, lane);
+            } else
 #pragma unroll 1
             for (uint32_t ch = 0; ch < kChunks && ok; ++ch, ++cc) {
                 // 32 accumulator columns of this thread's row -> bias, activation, rounding -> 16 packed words

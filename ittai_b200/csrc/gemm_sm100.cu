@@ -182,7 +182,15 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
         set_error("gemm shape M=%d N=%d K=%d: N must be a multiple of %d and K of %d", a->m, a->n, a->k, GN, GK);
         return ITTAI_E_ARG;
     }
-    if (a->epi < ITTAI_EPI_NONE || a->epi > ITTAI_EPI_SWIGLU) { set_error("unknown epilogue %d", a->epi); return ITTAI_E_ARG; }
+    if (a->epi < ITTAI_EPI_NONE || a->epi > ITTAI_EPI_QKROPE) { set_error("unknown epilogue %d", a->epi); return ITTAI_E_ARG; }
+    if (a->epi == ITTAI_EPI_QKROPE) {
+        const IttaiQkRope* r = a->qk_rope;
+        if (a->n != ITTAI_Q3_DQKV || a->m <= GM || a->bias || a->residual || a->row_stats || a->stats_out || !r || !r->qn || !r->kn || !r->rope ||
+            !r->pos || !r->seq || !r->slot || !r->kcache_layer || !r->vcache_layer || r->kv_cap < 1) {
+            set_error("the QK-norm + RoPE epilogue needs N = %d, M > %d, no bias / residual / statistics and a complete IttaiQkRope", ITTAI_Q3_DQKV, GM);
+            return ITTAI_E_ARG;
+        }
+    }
     if (a->epi == ITTAI_EPI_SWIGLU && a->residual) { set_error("SwiGLU epilogue takes no residual"); return ITTAI_E_ARG; }
     if ((a->row_stats == nullptr) != (a->col_sums == nullptr) || (a->row_stats != nullptr && a->m <= GM)) {
         set_error("a folded LayerNorm needs both row_stats and col_sums, and M > %d", GM);
@@ -228,6 +236,7 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.stats_out = a->stats_out;
     g.stats_parts = a->stats_parts;
     g.stats_eps = a->stats_eps;
+    if (a->epi == ITTAI_EPI_QKROPE) g.rope = *a->qk_rope; else g.rope = IttaiQkRope{};
 #ifdef ITTAI_GEMM_PROFILE
     extern long long* g_gemm_clk;
     g.clk = g_gemm_clk;

@@ -24,13 +24,15 @@ def _stream(t: torch.Tensor):
 def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None,
          row_stats: torch.Tensor | None = None, col_sums: torch.Tensor | None = None, stats_out: torch.Tensor | None = None,
-         stats_eps: float = 0.0) -> torch.Tensor:
+         stats_eps: float = 0.0, qk_rope: dict | None = None) -> torch.Tensor:
     """``out = epilogue(a @ w.T)`` on the tcgen05 GEMM: a [M, K] and w [N, K] bf16 (last dim contiguous), bias fp32 [N],
     residual bf16 [M, N].  SwiGLU takes interleaved (gate, up) weight rows and returns [M, N/2].  ``row_stats`` (fp32
     [M, 2] from ``row_stats``) with ``col_sums`` (fp32 [N]) folds a LayerNorm over ``a`` into the GEMM: ``w`` is then the
     weight scaled by the LayerNorm gain along K and ``bias`` includes ``W @ beta`` (see ``fold_layernorm``).  ``stats_out``
     (fp32 [M, N/128, 2]) receives the (sum, sum of squares) of every 128-column slice of the output rows; passed as the
-    ``row_stats`` of the next GEMM (3-D, with ``stats_eps``) it replaces the separate statistics pass."""
+    ``row_stats`` of the next GEMM (3-D, with ``stats_eps``) it replaces the separate statistics pass.  ``epi=EPI_QKROPE``
+    (Qwen3 QKV projection, N = 4096, M > 128) takes ``qk_rope`` = dict(qn, kn, rope, pos, seq, slot, kcache, vcache,
+    kv_cap, eps) and does the work of the QK-norm + RoPE + cache-scatter pass in its epilogue."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
     m, k = a.shape
     n = w.shape[0]
@@ -58,6 +60,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Ten
     if stats_out is not None:
         assert stats_out.dtype == torch.float32 and stats_out.is_contiguous() and tuple(stats_out.shape) == (m, n // 128, 2)
         g.stats_out = stats_out.data_ptr()
+    if epi == _C.EPI_QKROPE:
+        r = _C.QkRope()
+        r.qn, r.kn, r.rope = qk_rope["qn"].data_ptr(), qk_rope["kn"].data_ptr(), qk_rope["rope"].data_ptr()
+        r.pos, r.seq, r.slot = qk_rope["pos"].data_ptr(), qk_rope["seq"].data_ptr(), qk_rope["slot"].data_ptr()
+        r.kcache_layer, r.vcache_layer = qk_rope["kcache"].data_ptr(), qk_rope["vcache"].data_ptr()
+        r.kv_cap, r.eps = qk_rope["kv_cap"], qk_rope["eps"]
+        g.qk_rope = C.pointer(r)
     _C.check(_C.lib().ittai_gemm_bf16_launch(C.byref(g), _stream(a)))
     return out
 

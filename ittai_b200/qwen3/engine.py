@@ -65,10 +65,15 @@ class PrefillCore:
         for l in range(self.L):
             kc, vc = kv_layer(l)
             ops.rmsnorm_rows(h, w["ln1"][l], EPS, out=xn)
-            ops.gemm(xn, w["wqkv"][l], st, out=qkv)
-            _C.check(L.ittai_qwen3_qk_rope_scatter(qkv.data_ptr(), w["qn"][l].data_ptr(), w["kn"][l].data_ptr(), rope.data_ptr(),
-                                                   pos.data_ptr(), seq.data_ptr(), slot.data_ptr(), kc.data_ptr(), vc.data_ptr(),
-                                                   T, kv_cap, EPS, s))
+            if T > 128:
+                # QK-norm + RoPE + cache scatter inside the QKV GEMM's epilogue (the reference's qkv epilogue, base.py:84-109)
+                ops.gemm(xn, w["wqkv"][l], st, out=qkv, epi=_C.EPI_QKROPE,
+                         qk_rope=dict(qn=w["qn"][l], kn=w["kn"][l], rope=rope, pos=pos, seq=seq, slot=slot, kcache=kc, vcache=vc, kv_cap=kv_cap, eps=EPS))
+            else:
+                ops.gemm(xn, w["wqkv"][l], st, out=qkv)
+                _C.check(L.ittai_qwen3_qk_rope_scatter(qkv.data_ptr(), w["qn"][l].data_ptr(), w["kn"][l].data_ptr(), rope.data_ptr(),
+                                                       pos.data_ptr(), seq.data_ptr(), slot.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                       T, kv_cap, EPS, s))
             ops.attention(qkv, kc, vc, attn, seqs, n_heads=NH, group=NH // NKV, head_dim=HD, causal=True, max_q_len=max_q_len,
                           q_strides=(DQKV, HD), k_strides=k_strides, v_strides=k_strides, o_strides=(DQ, HD),
                           q_rows_total=T, kv_rows_total=kc.numel() // HD, status=st)

@@ -163,6 +163,39 @@ def test_qk_rope_scatter_matches_oracle(tiny_hf):
 
 
 @gpu
+def test_qkv_gemm_with_rope_epilogue_matches_the_separate_pass():
+    """QKV projection with QK-norm + RoPE + cache scatter in the GEMM epilogue against GEMM followed by the row-wise pass:
+    same rounding steps, so q, the K cache and the V cache agree except where the different summation order of the
+    RMS statistic flips a rounding (a handful of values, by one bf16 step)."""
+    from ittai_b200 import _C, ops
+    from ittai_b200.qwen3.decoder import rope_table
+    T, cap, B = 700, 512, 2
+    x, w = _rand(T, 1024, seed=31), _rand(4096, 1024, scale=0.05, seed=32)
+    qn, kn = (_rand(128, seed=33).float() * 0.2 + 1).to(torch.bfloat16), (_rand(128, seed=34).float() * 0.2 + 1).to(torch.bfloat16)
+    rope = rope_table(cap, "cuda")
+    pos = (torch.arange(T, device="cuda") % 350).int()
+    seq = (torch.arange(T, device="cuda") // 350).int()
+    slot = pos.clone()
+    st = ops.new_status("cuda")
+    L = _C.lib()
+    kc1, vc1 = torch.zeros(B, 8, cap, 128, dtype=torch.bfloat16, device="cuda"), torch.zeros(B, 8, cap, 128, dtype=torch.bfloat16, device="cuda")
+    qkv1 = ops.gemm(x, w, st)
+    _C.check(L.ittai_qwen3_qk_rope_scatter(qkv1.data_ptr(), qn.data_ptr(), kn.data_ptr(), rope.data_ptr(), pos.data_ptr(), seq.data_ptr(),
+                                           slot.data_ptr(), kc1.data_ptr(), vc1.data_ptr(), T, cap, 1e-6, ops._stream(x)))
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    qkv2 = torch.zeros(T, 4096, dtype=torch.bfloat16, device="cuda")
+    ops.gemm(x, w, st, out=qkv2, epi=_C.EPI_QKROPE,
+             qk_rope=dict(qn=qn, kn=kn, rope=rope, pos=pos, seq=seq, slot=slot, kcache=kc2, vcache=vc2, kv_cap=cap, eps=1e-6))
+    ops.check_status(st)
+    assert torch.equal(vc1, vc2), "V cache differs"
+    for name, a, b in (("q", qkv1[:, :2048], qkv2[:, :2048]), ("K cache", kc1, kc2)):
+        diff = (a.float() - b.float()).abs()
+        frac = (diff > 0).float().mean().item()
+        assert frac < 1e-3 and diff.max().item() <= 2.0 ** -6 * a.float().abs().max().item(), f"{name}: {frac:.2e} of the values differ, max {diff.max().item():.4g}"
+    assert not qkv2[:, 2048:].any(), "k / v columns of the output matrix were written"
+
+
+@gpu
 def test_im2col_embed_pool():
     from ittai_b200 import _C
     L = _C.lib()
