@@ -135,7 +135,7 @@ def siglip_leg(dev, rank, barrier, iters: int = 20):
     barrier()
     eng.check()
     return {"ms": e0.elapsed_time(e1), "iters": iters, "images": iters * SIGLIP_BATCH, "flops_reference_formula": iters * eng.flops("reference"),
-            "launches_per_forward": 2 + 12 * 7 + 8}
+            "launches_per_forward": 2 + 12 * 5 + 6}
 
 
 def cpu_reference(steps: int, warmup: int):
@@ -286,6 +286,8 @@ def main():
                           "batch": SIGLIP_BATCH, "ms_per_batch": sig_ms / sig["iters"], "dtype": "bf16",
                           "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                        "frac": tf / world / peaks["bf16_tflops"], "peak_kind": peak_kind,
+                                       "frac_of_sustained_peak": (tf / world / peaks["bf16_tflops_sustained"]) if "bf16_tflops_sustained" in peaks else None,
+                                       "timing": "20 forwards back to back (sustained, power-capped clocks); benchmarks/siglip.py times single forwards",
                                        "flops": "reference benchmark formula: B*L*(2*S*D*(4D+2F) + 4*S*S*D)"},
                           "gpu_launches_per_forward": sig["launches_per_forward"]}
     if not args.no_cpu_baseline and world == 1:
