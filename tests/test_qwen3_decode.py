@@ -218,8 +218,9 @@ def test_full_model_config1(full_hf, golden_dir):
     while same < 64 and out[same] == int(g["ids"][same]):
         same += 1
     report.update(free_running_prefix_equal=same, first_flip_gap=float(gaps[same]) if same < 64 else None)
-    if os.path.isdir("gpurun_out"):
-        json.dump(report, open("gpurun_out/parity_config1.json", "w"), indent=1)
+    report_dir = os.environ.get("ITTAI_REPORT_DIR")
+    if report_dir and os.path.isdir(report_dir):
+        json.dump(report, open(os.path.join(report_dir, "parity_config1.json"), "w"), indent=1)
     print(report)
     # the eager model's own backends differ by 0.051 max-abs on this config; the gate is 3e-2 + that floor
     assert worst_cos >= 0.9995 and norm_rel <= 5e-3
