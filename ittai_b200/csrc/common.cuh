@@ -132,6 +132,15 @@ __device__ __forceinline__ void st_flagged(uint64_t* p, uint32_t payload, uint32
     const uint64_t v = ((uint64_t)tag << 32) | payload;
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// 128-bit flagged words: three 32-bit payloads + the tag, moved by single-copy-atomic .b128 accesses.  They carry the
+// vectors whose consumers would otherwise poll several 64-bit words one after the other.
+__device__ __forceinline__ void ld_flagged128(const void* p, uint64_t& lo, uint64_t& hi) {
+    asm volatile("{\n.reg .b128 t;\nld.relaxed.gpu.global.b128 t, [%2];\nmov.b128 {%0, %1}, t;\n}\n" : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_flagged128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t tag) {
+    const uint64_t lo = ((uint64_t)b << 32) | a, hi = ((uint64_t)tag << 32) | c;
+    asm volatile("{\n.reg .b128 t;\nmov.b128 t, {%1, %2};\nst.relaxed.gpu.global.b128 [%0], t;\n}\n" ::"l"(p), "l"(lo), "l"(hi) : "memory");
+}
 // Two floats -> packed bf16 pair (round to nearest even), one conversion instruction.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t d;
@@ -177,6 +186,24 @@ __device__ __forceinline__ bool wait_word(const Waiter& w, const uint64_t* p, ui
             if (ld_relaxed(&w.sync[1]) != 0u) return false;
             if (spins >= w.limit) {
                 report_status(w.status, w.sync, ITTAI_ST_FLAG_TIMEOUT, (uint32_t)what, blockIdx.x, (uint32_t)(v >> 32), tag);
+                return false;
+            }
+        }
+    }
+}
+
+
+// The same for a 128-bit word: payloads a, b, c.
+__device__ __forceinline__ bool wait_word128(const Waiter& w, const void* p, uint32_t tag, uint32_t& a, uint32_t& b, uint32_t& c, int what) {
+    uint32_t spins = 0;
+    for (;;) {
+        uint64_t lo, hi;
+        ld_flagged128(p, lo, hi);
+        if ((uint32_t)(hi >> 32) == tag) { a = (uint32_t)lo; b = (uint32_t)(lo >> 32); c = (uint32_t)hi; return true; }
+        if (((++spins) & 1023u) == 0u) {
+            if (ld_relaxed(&w.sync[1]) != 0u) return false;
+            if (spins >= w.limit) {
+                report_status(w.status, w.sync, ITTAI_ST_FLAG_TIMEOUT, (uint32_t)what, blockIdx.x, (uint32_t)(hi >> 32), tag);
                 return false;
             }
         }

@@ -44,6 +44,7 @@ struct SmemAttn {
     float wm[kWarps][2], wl[kWarps][2];          // per-warp running max and sum
     bf16 knew[HD];
     bf16 vnew[HD];
+    uint32_t pub[HD];                            // merged output pairs of this CTA on their way into 128-bit words
     float ored[kWarps][2][HD];
 };
 constexpr size_t kHdrBytes = (sizeof(SmemHdr) + 255) / 256 * 256;
@@ -135,7 +136,8 @@ __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     stride[ITTAI_PH_OPROJ] = (size_t)D * DQ * 2; nbytes[ITTAI_PH_OPROJ] = (uint32_t)(hi - lo) * 2 * DQ * 2;
     base[ITTAI_PH_DOWN] = reinterpret_cast<const char*>(p.wd) + (size_t)2 * lo * FF * 2;
     stride[ITTAI_PH_DOWN] = (size_t)D * FF * 2; nbytes[ITTAI_PH_DOWN] = (uint32_t)(hi - lo) * 2 * FF * 2;
-    split_range(FF / 2, c.ncta, c.cta, lo, hi);
+    split_range(FF / 6, c.ncta, c.cta, lo, hi);      // 128-bit words of the SwiGLU output: three units of four rows each
+    lo *= 3; hi *= 3;
     base[ITTAI_PH_GU] = reinterpret_cast<const char*>(p.wgu) + (size_t)4 * lo * D * 2;
     stride[ITTAI_PH_GU] = (size_t)DGU * D * 2; nbytes[ITTAI_PH_GU] = (uint32_t)(hi - lo) * 4 * D * 2;
     base[ITTAI_PH_ATTN] = nullptr; stride[ITTAI_PH_ATTN] = (size_t)p.batch * NKV * p.kv_cap * HD * 2; nbytes[ITTAI_PH_ATTN] = 0;
@@ -227,19 +229,21 @@ __device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[N
     return true;
 }
 
-// Waits for NB rows of K bf16 values in flagged-word format and spreads them into xs as fp32.
+// Waits for NB rows of K bf16 values in 128-bit flagged words and spreads them into xs: K = 2048 (attention output) has
+// four values per word, K = 3072 (SwiGLU output) six, so every thread polls exactly one word per row.
 template <int NB, int K>
 __device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, uint32_t tag, int what, const bf16** ring_entry = nullptr) {
+    constexpr int V = K / kThreads;              // values per word
+    static_assert(V == 4 || V == 6, "one 128-bit word per thread");
     bool ok = true;
 #pragma unroll
-    for (int b = 0; b < NB; ++b)
-#pragma unroll
-        for (int i = 0; i < K / 2 / kThreads; ++i) {
-            const int wd = c.tid + i * kThreads;
-            uint32_t u = 0;
-            ok = ok && wait_word(c.w, src + (size_t)b * (K / 2) + wd, tag, u, what);
-            c.xs[b * (FF / 2) + wd] = u;
-        }
+    for (int b = 0; b < NB; ++b) {
+        uint32_t u0 = 0, u1 = 0, u2 = 0;
+        ok = ok && wait_word128(c.w, reinterpret_cast<const uint4*>(src) + (size_t)b * kThreads + c.tid, tag, u0, u1, u2, what);
+        uint32_t* dst = c.xs + b * (FF / 2) + c.tid * (V / 2);
+        dst[0] = u0; dst[1] = u1;
+        if constexpr (V == 6) dst[2] = u2;
+    }
     if (ring_entry != nullptr) {
         const unsigned char* ptr = stream_wait(c.st, c.st.consumed, c.w);
         *ring_entry = reinterpret_cast<const bf16*>(ptr);
@@ -623,10 +627,15 @@ __device__ bool phase_attn(Cta& c, int l) {
             const float M = warp_max(m);
             const float wk = ex2_approx(m - (M == -INFINITY ? 0.f : M));
             const float Ls = warp_sum(l * wk), O0 = warp_sum(o0 * wk), O1 = warp_sum(o1 * wk);
-            if (c.lane == 0)
-                st_flagged(c.ws.attn + (size_t)b * (DQ / 2) + ((2 * g + h) * HD + d0 + dd) / 2, pack_bf16x2(O0 / Ls, O1 / Ls), tag);
+            if (c.lane == 0) at->pub[pr] = pack_bf16x2(O0 / Ls, O1 / Ls);
         }
         if (!all_ok(ok)) return false;
+        // two adjacent pairs (four outputs of one head) leave as one 128-bit word
+        if (c.tid < dpc / 2) {
+            const int h = c.tid / (dpc / 4), k4 = c.tid % (dpc / 4);
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.attn) + (size_t)b * (DQ / 4) + ((2 * g + h) * HD + d0) / 4 + k4,
+                          at->pub[2 * c.tid], at->pub[2 * c.tid + 1], 0u, tag);
+        }
     }
     return true;
 }
@@ -713,12 +722,14 @@ __device__ bool phase_gu(Cta& c, int l) {
 #pragma unroll
     for (int b = 0; b < NB; ++b) ok = ok && wait_word(c.w, c.ws.hmid + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_GU);
     int u0, u1;
-    split_range(FF / 2, c.ncta, c.cta, u0, u1);      // unit = two activations = four weight rows = one flagged word
+    split_range(FF / 6, c.ncta, c.cta, u0, u1);      // 128-bit words: three units of two activations = four weight rows each
+    u0 *= 3; u1 *= 3;
     const bf16* W = nullptr;
     if (!norm_pairs_to_smem<NB>(c, u, gw, ok, u1 > u0 ? &W : nullptr)) return false;
     if (u1 == u0) return true;
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
+    uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [unit][sequence]
     for (int un = u0 + c.warp; un < u1; un += kWarps) {
         const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
         float a0[NB], a1[NB];
@@ -740,10 +751,16 @@ __device__ bool phase_gu(Cta& c, int l) {
         }
         if (c.lane == 0) {
 #pragma unroll
-            for (int b = 0; b < NB; ++b) st_flagged(c.ws.act + (size_t)b * (FF / 2) + un, pack_bf16x2(a0[b], a1[b]), tag);
+            for (int b = 0; b < NB; ++b) pub[(un - u0) * NB + b] = pack_bf16x2(a0[b], a1[b]);
         }
     }
-    stream_release(c.st, 1);
+    stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
+    // three units (six activations) leave as one 128-bit word
+    for (int i = c.tid; i < (u1 - u0) / 3 * NB; i += kThreads) {
+        const int wq = i / NB, b = i % NB;
+        st_flagged128(reinterpret_cast<uint4*>(c.ws.act) + (size_t)b * (FF / 6) + u0 / 3 + wq,
+                      pub[(3 * wq) * NB + b], pub[(3 * wq + 1) * NB + b], pub[(3 * wq + 2) * NB + b], tag);
+    }
     return true;
 }
 

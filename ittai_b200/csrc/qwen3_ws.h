@@ -24,9 +24,9 @@ struct Q3Workspace {
     uint32_t* sync;
     uint64_t* h;        // [B, 512]  residual stream entering a layer (bf16 pairs)
     uint64_t* qkv;      // [B, 2048] raw q|k|v projections of the current token
-    uint64_t* attn;     // [B, 1024] attention output
+    uint64_t* attn;     // [B, 512] 128-bit words: attention output, four bf16 per word
     uint64_t* hmid;     // [B, 512]  residual stream after o_proj
-    uint64_t* act;      // [B, 1536] SwiGLU output
+    uint64_t* act;      // [B, 512] 128-bit words: SwiGLU output, six bf16 per word (the region keeps its 64-bit-word size)
     uint64_t* part;     // [Q3_MAX_CTAS, Q3_PART_WORDS] split-K partials (fp32 payloads)
     uint64_t* cand_val; // [Q3_MAX_CTAS, ITTAI_MAX_BATCH] per-CTA best logit (fp32 payload)
     uint64_t* cand_idx; // [Q3_MAX_CTAS, ITTAI_MAX_BATCH] its index

@@ -252,18 +252,25 @@ class Qwen3Decoder:
         _C.check(self.lib.ittai_qwen3_phase_launch(C.byref(p), phase, layer, self._stream()))
         self.check_status()
 
-    # The vectors one phase hands to the next live in the workspace as flagged 64-bit words: two bf16 values in the low
-    # half, the tag of the producing (step, layer) in the high half.  These helpers let tests and profiles read a
-    # phase's output and plant a phase's input; a phase launch runs at step 0, where layer l's tag is l + 1.
+    # The vectors one phase hands to the next live in the workspace as flagged words.  h, qkv and hmid use 64-bit words:
+    # two bf16 values in the low half, the tag of the producing (step, layer) in the high half.  attn and act, whose
+    # readers need the whole vector, use 128-bit words of three 32-bit payloads + tag: four bf16 values per word for
+    # attn (the third payload is unused), six for act.  These helpers let tests and profiles read a phase's output and
+    # plant a phase's input; a phase launch runs at step 0, where layer l's tag is l + 1.
     _FLAGGED = (("h", D), ("qkv", DQKV), ("attn", DQ), ("hmid", D), ("act", FF))
+    _WIDE = {"attn": 4, "act": 6}       # bf16 values per 128-bit word
 
     def _flagged_words(self, name: str) -> torch.Tensor:
+        """int64 view of buffer ``name``: ``[B, n/2]`` for 64-bit words, ``[B, 512, 2]`` (low, high half) for 128-bit ones."""
         off = self._ws_ptr - self.workspace.data_ptr()
         up = lambda n: (n + 255) // 256 * 256
         o = off + up(64 * 4)
         for nm, n in self._FLAGGED:
             nb = self.B * (n // 2) * 8
             if nm == name:
+                if nm in self._WIDE:
+                    words = n // self._WIDE[nm]
+                    return self.workspace[o:o + self.B * words * 16].view(torch.int64).view(self.B, words, 2)
                 return self.workspace[o:o + nb].view(torch.int64).view(self.B, n // 2)
             o += up(nb)
         raise KeyError(name)
@@ -271,13 +278,25 @@ class Qwen3Decoder:
     def read_buf(self, name: str) -> torch.Tensor:
         """bf16 ``[B, n]`` payload of the flagged buffer ``name`` (h, qkv, attn, hmid, act)."""
         w = self._flagged_words(name)
-        pair = torch.stack([w & 0xFFFF, (w >> 16) & 0xFFFF], -1).to(torch.int32).to(torch.int16)
-        return pair.view(torch.bfloat16).reshape(self.B, -1)
+        if name in self._WIDE:
+            lo, hi = w[..., 0], w[..., 1]
+            vals = [lo & 0xFFFF, (lo >> 16) & 0xFFFF, (lo >> 32) & 0xFFFF, (lo >> 48) & 0xFFFF, hi & 0xFFFF, (hi >> 16) & 0xFFFF]
+            pair = torch.stack(vals[:self._WIDE[name]], -1)
+        else:
+            pair = torch.stack([w & 0xFFFF, (w >> 16) & 0xFFFF], -1)
+        return pair.to(torch.int32).to(torch.int16).view(torch.bfloat16).reshape(self.B, -1)
 
     def write_buf(self, name: str, values: torch.Tensor, layer: int) -> None:
         """Plant ``values`` ([B, n] or [n]) in flagged buffer ``name`` with the tag of (step 0, ``layer``)."""
-        v = values.to(torch.bfloat16).reshape(self.B, -1, 2).to(self.dev).view(torch.int16).to(torch.int64) & 0xFFFF
-        self._flagged_words(name).copy_(v[..., 0] | (v[..., 1] << 16) | ((layer + 1) << 32))
+        per = self._WIDE.get(name, 2)
+        v = values.to(torch.bfloat16).reshape(self.B, -1, per).to(self.dev).view(torch.int16).to(torch.int64) & 0xFFFF
+        tag = (layer + 1) << 32
+        if name in self._WIDE:
+            lo = v[..., 0] | (v[..., 1] << 16) | (v[..., 2] << 32) | (v[..., 3] << 48)
+            hi = (v[..., 4] | (v[..., 5] << 16) if per == 6 else torch.zeros_like(lo)) | tag
+            self._flagged_words(name).copy_(torch.stack([lo, hi], -1))
+        else:
+            self._flagged_words(name).copy_(v[..., 0] | (v[..., 1] << 16) | tag)
 
     @torch.no_grad()
     def generate(self, prompt_host: torch.Tensor, n_steps: int) -> torch.Tensor:
