@@ -128,7 +128,8 @@ __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     const char* base[kStreamPhases];
     size_t stride[kStreamPhases];
     uint32_t nbytes[kStreamPhases];
-    split_range(DQKV / 2, c.ncta, c.cta, lo, hi);
+    split_range(DQKV / 4, c.ncta, c.cta, lo, hi);    // 128-bit words of the projection: two row pairs each
+    lo *= 2; hi *= 2;
     base[ITTAI_PH_QKV] = reinterpret_cast<const char*>(p.wqkv) + (size_t)2 * lo * D * 2;
     stride[ITTAI_PH_QKV] = (size_t)DQKV * D * 2; nbytes[ITTAI_PH_QKV] = (uint32_t)(hi - lo) * 2 * D * 2;
     split_range(D / 2, c.ncta, c.cta, lo, hi);
@@ -343,22 +344,29 @@ __device__ bool phase_qkv(Cta& c, int l) {
         else ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_QKV);
     }
     int p0, p1;
-    split_range(DQKV / 2, c.ncta, c.cta, p0, p1);
+    split_range(DQKV / 4, c.ncta, c.cta, p0, p1);    // 128-bit words: two row pairs (four outputs) each
+    p0 *= 2; p1 *= 2;
     const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
     if (!norm_pairs_to_smem<NB>(c, u, gw, ok, p1 > p0 ? &W : nullptr)) return false;
     if (p1 == p0) return true;
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
+    uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [row pair][sequence]
     for (int pr = p0 + c.warp; pr < p1; pr += kWarps) {
         const bf16* wp[2] = {W + (size_t)(2 * (pr - p0)) * D, W + (size_t)(2 * (pr - p0) + 1) * D};
         float acc[2][NB];
         dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
         if (c.lane == 0) {
 #pragma unroll
-            for (int b = 0; b < NB; ++b) st_flagged(c.ws.qkv + b * (DQKV / 2) + pr, pack_bf16x2(acc[0][b], acc[1][b]), tag);
+            for (int b = 0; b < NB; ++b) pub[(pr - p0) * NB + b] = pack_bf16x2(acc[0][b], acc[1][b]);
         }
     }
-    stream_release(c.st, 1);
+    stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
+    for (int i = c.tid; i < (p1 - p0) / 2 * NB; i += kThreads) {
+        const int wq = i / NB, b = i % NB;
+        st_flagged128(reinterpret_cast<uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4) + p0 / 2 + wq,
+                      pub[(2 * wq) * NB + b], pub[(2 * wq + 1) * NB + b], 0u, tag);
+    }
     return true;
 }
 
@@ -386,69 +394,60 @@ __device__ bool phase_attn(Cta& c, int l) {
     if (it.active) {
         const int b = it.b, g = it.g, pos = it.pos;
         const bool has_new = it.has_new;
-        const uint64_t* qw = c.ws.qkv + (size_t)b * (DQKV / 2);
         const size_t head_off = ((((size_t)l * B + b) * NKV + g) * (size_t)p.kv_cap) * HD;
         bf16* kc = reinterpret_cast<bf16*>(p.kcache) + head_off;
         bf16* vc = reinterpret_cast<bf16*>(p.vcache) + head_off;
 
         // -- norm + rotate q (warps 0,1) and the new key (warp 2); copy the new value (warp 3).
-        //    A lane owns elements 2*lane, 2*lane+1 and their rotation partners 64 + the same.
-        //    Gains and the rotary row are fetched before the wait, so their latency hides behind it.
+        //    The row arrives as 32 words of four values: a lane owns elements 4*lane .. 4*lane+3, and the rotation
+        //    partner (element +-64) of each sits in lane ^ 16.  Gains and the rotary row are fetched before the wait, so
+        //    their latency hides behind it.
+        const uint4* qw = reinterpret_cast<const uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4);
         bool ok = true;
         if (c.warp < 3 && (c.warp < 2 || has_new)) {
             const bool is_k = c.warp == 2;
             const int e0 = is_k ? DQ + g * HD : (2 * g + c.warp) * HD;
             const bf16* gain = reinterpret_cast<const bf16*>(is_k ? p.kn : p.qn) + (size_t)l * HD;
             const bf16* rp = reinterpret_cast<const bf16*>(p.rope) + (size_t)pos * HD;
-            const uint32_t ga = *reinterpret_cast<const uint32_t*>(gain + 2 * c.lane);
-            const uint32_t gb = *reinterpret_cast<const uint32_t*>(gain + HD / 2 + 2 * c.lane);
-            const uint32_t cw = *reinterpret_cast<const uint32_t*>(rp + 2 * c.lane);
-            const uint32_t sw = *reinterpret_cast<const uint32_t*>(rp + HD / 2 + 2 * c.lane);
-            uint32_t ua = 0, ub = 0;
-            ok = wait_word(c.w, qw + e0 / 2 + c.lane, tag, ua, ITTAI_PH_ATTN);
-            ok = ok && wait_word(c.w, qw + e0 / 2 + 32 + c.lane, tag, ub, ITTAI_PH_ATTN);
+            const int hi_half = c.lane >> 4, ei = 4 * (c.lane & 15);        // rotation index of this lane's first element
+            const uint2 gq = *reinterpret_cast<const uint2*>(gain + 4 * c.lane);
+            const uint2 cq = *reinterpret_cast<const uint2*>(rp + ei);
+            const uint2 sq = *reinterpret_cast<const uint2*>(rp + HD / 2 + ei);
+            uint32_t ua = 0, ub = 0, uc = 0;
+            ok = wait_word128(c.w, qw + e0 / 4 + c.lane, tag, ua, ub, uc, ITTAI_PH_ATTN);
             float x[4] = {bf_lo(ua), bf_hi(ua), bf_lo(ub), bf_hi(ub)};
             const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
             const float rstd = 1.0f / sqrtf(ss * (1.0f / HD) + p.eps);
-            x[0] = bf16r(bf16r(x[0] * rstd) * bf_lo(ga));
-            x[1] = bf16r(bf16r(x[1] * rstd) * bf_hi(ga));
-            x[2] = bf16r(bf16r(x[2] * rstd) * bf_lo(gb));
-            x[3] = bf16r(bf16r(x[3] * rstd) * bf_hi(gb));
-            float lo[2], hi[2];
+            const float gn[4] = {bf_lo(gq.x), bf_hi(gq.x), bf_lo(gq.y), bf_hi(gq.y)};
+            const float cs[4] = {bf_lo(cq.x), bf_hi(cq.x), bf_lo(cq.y), bf_hi(cq.y)};
+            const float sn[4] = {bf_lo(sq.x), bf_hi(sq.x), bf_lo(sq.y), bf_hi(sq.y)};
+            float r[4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {      // pair (i, i+64), i = 2*lane + j
-                const float cs = j ? bf_hi(cw) : bf_lo(cw), sn = j ? bf_hi(sw) : bf_lo(sw);
-                const float a = x[j], bb = x[j + 2];
-                lo[j] = bf16r(bf16r(a * cs) + bf16r(-bb * sn));
-                hi[j] = bf16r(bf16r(bb * cs) + bf16r(a * sn));
+            for (int j = 0; j < 4; ++j) {
+                x[j] = bf16r(bf16r(x[j] * rstd) * gn[j]);
+                const float y = __shfl_xor_sync(0xffffffffu, x[j], 16);      // element j +- 64
+                // pair (i, i+64): out[i] = x_i cos_i - x_{i+64} sin_i,  out[i+64] = x_{i+64} cos_i + x_i sin_i
+                r[j] = hi_half ? bf16r(bf16r(x[j] * cs[j]) + bf16r(y * sn[j])) : bf16r(bf16r(x[j] * cs[j]) + bf16r(-y * sn[j]));
             }
             if (is_k) {
-                const uint32_t wlo = pack_bf16x2(lo[0], lo[1]), whi = pack_bf16x2(hi[0], hi[1]);
-                *reinterpret_cast<uint32_t*>(at->knew + 2 * c.lane) = wlo;
-                *reinterpret_cast<uint32_t*>(at->knew + HD / 2 + 2 * c.lane) = whi;
+                const uint2 wk = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+                *reinterpret_cast<uint2*>(at->knew + 4 * c.lane) = wk;
                 if (ok) {
-                    *reinterpret_cast<uint32_t*>(kc + (size_t)pos * HD + 2 * c.lane) = wlo;
-                    *reinterpret_cast<uint32_t*>(kc + (size_t)pos * HD + HD / 2 + 2 * c.lane) = whi;
+                    *reinterpret_cast<uint2*>(kc + (size_t)pos * HD + 4 * c.lane) = wk;
                     __threadfence();
                     fence_proxy_async();       // later tokens read this row through the TMA unit
                 }
             } else {
                 const float qscale = 0.08838834764831845f * kLog2e;   // head_dim^-0.5 * log2(e)
-                at->qs[c.warp][2 * c.lane] = lo[0] * qscale;
-                at->qs[c.warp][2 * c.lane + 1] = lo[1] * qscale;
-                at->qs[c.warp][HD / 2 + 2 * c.lane] = hi[0] * qscale;
-                at->qs[c.warp][HD / 2 + 2 * c.lane + 1] = hi[1] * qscale;
+                *reinterpret_cast<float4*>(&at->qs[c.warp][4 * c.lane]) = make_float4(r[0] * qscale, r[1] * qscale, r[2] * qscale, r[3] * qscale);
             }
         } else if (c.warp == 3 && has_new) {
             const int e0 = DQ + DKV + g * HD;
-            uint32_t ua = 0, ub = 0;
-            ok = wait_word(c.w, qw + e0 / 2 + c.lane, tag, ua, ITTAI_PH_ATTN);
-            ok = ok && wait_word(c.w, qw + e0 / 2 + 32 + c.lane, tag, ub, ITTAI_PH_ATTN);
-            *reinterpret_cast<uint32_t*>(at->vnew + 2 * c.lane) = ua;
-            *reinterpret_cast<uint32_t*>(at->vnew + HD / 2 + 2 * c.lane) = ub;
+            uint32_t ua = 0, ub = 0, uc = 0;
+            ok = wait_word128(c.w, qw + e0 / 4 + c.lane, tag, ua, ub, uc, ITTAI_PH_ATTN);
+            *reinterpret_cast<uint2*>(at->vnew + 4 * c.lane) = make_uint2(ua, ub);
             if (ok) {
-                *reinterpret_cast<uint32_t*>(vc + (size_t)pos * HD + 2 * c.lane) = ua;
-                *reinterpret_cast<uint32_t*>(vc + (size_t)pos * HD + HD / 2 + 2 * c.lane) = ub;
+                *reinterpret_cast<uint2*>(vc + (size_t)pos * HD + 4 * c.lane) = make_uint2(ua, ub);
                 __threadfence();
                 fence_proxy_async();
             }

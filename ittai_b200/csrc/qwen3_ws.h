@@ -23,7 +23,7 @@ constexpr int Q3_SYNC_WORDS = 64;        // [1] abort flag; the rest is spare
 struct Q3Workspace {
     uint32_t* sync;
     uint64_t* h;        // [B, 512]  residual stream entering a layer (bf16 pairs)
-    uint64_t* qkv;      // [B, 2048] raw q|k|v projections of the current token
+    uint64_t* qkv;      // [B, 1024] 128-bit words: raw q|k|v projections of the current token, four bf16 per word
     uint64_t* attn;     // [B, 512] 128-bit words: attention output, four bf16 per word
     uint64_t* hmid;     // [B, 512]  residual stream after o_proj
     uint64_t* act;      // [B, 512] 128-bit words: SwiGLU output, six bf16 per word (the region keeps its 64-bit-word size)

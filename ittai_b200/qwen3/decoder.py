@@ -252,13 +252,13 @@ class Qwen3Decoder:
         _C.check(self.lib.ittai_qwen3_phase_launch(C.byref(p), phase, layer, self._stream()))
         self.check_status()
 
-    # The vectors one phase hands to the next live in the workspace as flagged words.  h, qkv and hmid use 64-bit words:
-    # two bf16 values in the low half, the tag of the producing (step, layer) in the high half.  attn and act, whose
-    # readers need the whole vector, use 128-bit words of three 32-bit payloads + tag: four bf16 values per word for
-    # attn (the third payload is unused), six for act.  These helpers let tests and profiles read a phase's output and
+    # The vectors one phase hands to the next live in the workspace as flagged words.  h and hmid use 64-bit words:
+    # two bf16 values in the low half, the tag of the producing (step, layer) in the high half.  qkv, attn and act use
+    # 128-bit words of three 32-bit payloads + tag: four bf16 values per word for qkv and attn (the third payload is
+    # unused), six for act.  These helpers let tests and profiles read a phase's output and
     # plant a phase's input; a phase launch runs at step 0, where layer l's tag is l + 1.
     _FLAGGED = (("h", D), ("qkv", DQKV), ("attn", DQ), ("hmid", D), ("act", FF))
-    _WIDE = {"attn": 4, "act": 6}       # bf16 values per 128-bit word
+    _WIDE = {"qkv": 4, "attn": 4, "act": 6}       # bf16 values per 128-bit word
 
     def _flagged_words(self, name: str) -> torch.Tensor:
         """int64 view of buffer ``name``: ``[B, n/2]`` for 64-bit words, ``[B, 512, 2]`` (low, high half) for 128-bit ones."""
