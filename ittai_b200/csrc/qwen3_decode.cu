@@ -1,7 +1,7 @@
 // Qwen3-0.6B decode: one persistent cooperative kernel per launch runs n_steps tokens; the chosen token id is fed
 // back on the device.
 //
-//  * Data flow instead of grid barriers: every vector one phase hands to the next travels as flagged 64-bit words
+//  * Data flow instead of grid barriers: every vector one phase hands to the next travels as flagged 64- or 128-bit words
 //    (payload + tag of the producing step and layer), and a consumer polls exactly the words it needs (qwen3_ws.h).
 //  * Weight stream: each CTA's slices of the layer matrices and of the KV cache are pulled into a shared-memory ring by
 //    TMA bulk copies issued far ahead of use (weight_stream.cuh), so HBM keeps streaming while phases wait on each other.
