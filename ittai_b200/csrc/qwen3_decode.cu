@@ -5,8 +5,9 @@
 //    (payload + tag of the producing step and layer), and a consumer polls exactly the words it needs (qwen3_ws.h).
 //  * Weight stream: each CTA's slices of the layer matrices and of the KV cache are pulled into a shared-memory ring by
 //    TMA bulk copies issued far ahead of use (weight_stream.cuh), so HBM keeps streaming while phases wait on each other.
-//  * Batch-1 decode is HBM-bound (about 1.4 flop per weight byte), so there are no tensor-core tiles here: each warp
-//    multiplies whole 1024-column weight sub-rows with 128-bit accesses and reduces with shuffles.
+//  * Batch-1 decode is HBM-bound (about 1.4 flop per weight byte): each warp multiplies whole 1024-column weight
+//    sub-rows with 128-bit accesses and reduces with shuffles.  With several sequences the GEMV phases use warp-level
+//    tensor-core tiles with the sequences as the N dimension (gemv_tile).
 //
 // Rounding points follow the eager modules: every Linear output, norm output, rotary product and sum, SiLU, gate*up
 // product and residual sum is rounded to bf16 exactly once.  The math per phase mirrors the fused epilogues of the
@@ -24,6 +25,7 @@ constexpr int D = ITTAI_Q3_D, NKV = ITTAI_Q3_NKV, HD = ITTAI_Q3_HD, FF = ITTAI_Q
 constexpr int DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV, DGU = ITTAI_Q3_DGU;
 constexpr int kTile = 128;                       // cache positions per attention tile = one ring entry of K and one of V
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kPartFloats = 12 * 16;             // at most 12 tiles (16 rows x 256 columns) per CTA and phase
 constexpr int kStreamPhases = 5;                 // phases of a layer that read streamed data (the head reads HBM directly)
 
 // ---- shared-memory plan (dynamic): header | activations or attention scratch | weight ring -----------------
@@ -35,7 +37,7 @@ struct SmemHdr {
     int tok_s[ITTAI_MAX_BATCH];
     float bestv[kWarps];
     int besti[kWarps];
-    float sub[64 * ITTAI_MAX_BATCH];             // per-sub-row partial dot products
+    float sub[kPartFloats * ITTAI_MAX_BATCH];    // partial dot products of the GEMV tiles: [task][16 rows][sequence]
     float candv[Q3_MAX_CTAS];                    // argmax candidates of every CTA
     int candi[Q3_MAX_CTAS];
 };
@@ -330,6 +332,62 @@ __device__ __forceinline__ void dot_rows_k1024(Cta& c, const bf16* const (&wp)[R
     }
 }
 
+// ---- GEMV tiles on the tensor cores --------------------------------------------------------------------
+// One warp multiplies 16 weight rows x 256 columns with the activations of up to eight sequences: D[row, seq] as
+// sixteen m16n8k16 MMAs, the sequences as the N dimension (at batch 1 seven of the eight columns repeat the first and
+// are ignored).  A lane reads 8 consecutive weights of row g and of row g + 8 per 32-column window (one 128-bit access
+// each) and the matching 8 activations of sequence g; which of the window's columns an MMA k-index stands for is free
+// as long as A and B agree, so no transposing load is needed.  Rows past `n_rows` repeat the last row (their results
+// are dropped by the caller).  `W`: row-major slice in shared memory, `ld` elements per row; `xs`: packed bf16 pairs,
+// FF/2 words per sequence.  Replaces 12 instructions per 8 weights (unpack + packed FMAs) by 3 per 128.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <int NB>
+__device__ __forceinline__ void gemv_tile(const bf16* W, int ld, int r0, int n_rows, const uint32_t* xs, int k0, int lane, float (&d)[4]) {
+    const int g = lane >> 2, t = lane & 3;
+    const int ra = r0 + g < n_rows ? r0 + g : n_rows - 1, rb = r0 + g + 8 < n_rows ? r0 + g + 8 : n_rows - 1;
+    const bf16* pa = W + (size_t)ra * ld + k0 + 8 * t;
+    const bf16* pb = W + (size_t)rb * ld + k0 + 8 * t;
+    const uint32_t* px = xs + (g % NB) * (FF / 2) + (k0 >> 1) + 4 * t;
+    float e[4] = {0.f, 0.f, 0.f, 0.f}, f[4] = {0.f, 0.f, 0.f, 0.f}, h[4] = {0.f, 0.f, 0.f, 0.f};
+    d[0] = 0.f; d[1] = 0.f; d[2] = 0.f; d[3] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w += 2) {                 // four independent accumulation chains of four MMAs each
+        const uint4 va = *reinterpret_cast<const uint4*>(pa + 32 * w), va2 = *reinterpret_cast<const uint4*>(pa + 32 * w + 32);
+        const uint4 vb = *reinterpret_cast<const uint4*>(pb + 32 * w), vb2 = *reinterpret_cast<const uint4*>(pb + 32 * w + 32);
+        const uint4 vx = *reinterpret_cast<const uint4*>(px + 16 * w), vx2 = *reinterpret_cast<const uint4*>(px + 16 * w + 16);
+        mma_bf16_16816(d, va.x, vb.x, va.y, vb.y, vx.x, vx.y);      // columns 8t .. 8t+3 of the window
+        mma_bf16_16816(e, va.z, vb.z, va.w, vb.w, vx.z, vx.w);      // columns 8t+4 .. 8t+7
+        mma_bf16_16816(f, va2.x, vb2.x, va2.y, vb2.y, vx2.x, vx2.y);
+        mma_bf16_16816(h, va2.z, vb2.z, va2.w, vb2.w, vx2.z, vx2.w);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[i] = (d[i] + e[i]) + (f[i] + h[i]);
+}
+// Lane (g, t) holds rows g, g + 8 of sequences 2t, 2t + 1: part[(task * 16 + row) * NB + seq].
+template <int NB>
+__device__ __forceinline__ void gemv_store(float* part, int task, int lane, const float (&d)[4]) {
+    const int g = lane >> 2, t = lane & 3;
+    float* p0 = part + (size_t)(task * 16 + g) * NB;
+    float* p1 = part + (size_t)(task * 16 + g + 8) * NB;
+    if (2 * t < NB) { p0[2 * t] = d[0]; p1[2 * t] = d[2]; }
+    if (2 * t + 1 < NB) { p0[2 * t + 1] = d[1]; p1[2 * t + 1] = d[3]; }
+}
+// Sum of the NK column-block partials of local row `row` for sequence b, in fixed order.
+template <int NB, int NK>
+__device__ __forceinline__ float gemv_sum(const float* part, int row, int b) {
+    const int blk = row >> 4, rr = row & 15;
+    float v[NK];
+#pragma unroll
+    for (int kq = 0; kq < NK; ++kq) v[kq] = part[(size_t)((blk * NK + kq) * 16 + rr) * NB + b];
+    float s = v[0];
+#pragma unroll
+    for (int kq = 1; kq < NK; ++kq) s += v[kq];
+    return s;
+}
+
 // ---- phase: embed gather (layer 0) + RMSNorm + QKV GEMV ------------------------------------------------
 template <int NB>
 __device__ bool phase_qkv(Cta& c, int l) {
@@ -349,23 +407,43 @@ __device__ bool phase_qkv(Cta& c, int l) {
     const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
     if (!norm_pairs_to_smem<NB>(c, u, gw, ok, p1 > p0 ? &W : nullptr)) return false;
     if (p1 == p0) return true;
-    float xr[32];
-    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
-    uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [row pair][sequence]
-    for (int pr = p0 + c.warp; pr < p1; pr += kWarps) {
-        const bf16* wp[2] = {W + (size_t)(2 * (pr - p0)) * D, W + (size_t)(2 * (pr - p0) + 1) * D};
-        float acc[2][NB];
-        dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
-        if (c.lane == 0) {
+    if constexpr (NB == 1) {
+        // one sequence: a row pair per warp on the fp32 pipes (the tensor-core tiles below are no faster here)
+        float xr[32];
+        if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
+        uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [row pair][sequence]
+        for (int pr = p0 + c.warp; pr < p1; pr += kWarps) {
+            const bf16* wp[2] = {W + (size_t)(2 * (pr - p0)) * D, W + (size_t)(2 * (pr - p0) + 1) * D};
+            float acc[2][NB];
+            dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
+            if (c.lane == 0) {
 #pragma unroll
-            for (int b = 0; b < NB; ++b) pub[(pr - p0) * NB + b] = pack_bf16x2(acc[0][b], acc[1][b]);
+                for (int b = 0; b < NB; ++b) pub[(pr - p0) * NB + b] = pack_bf16x2(acc[0][b], acc[1][b]);
+            }
         }
-    }
-    stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
-    for (int i = c.tid; i < (p1 - p0) / 2 * NB; i += kThreads) {
-        const int wq = i / NB, b = i % NB;
-        st_flagged128(reinterpret_cast<uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4) + p0 / 2 + wq,
-                      pub[(2 * wq) * NB + b], pub[(2 * wq + 1) * NB + b], 0u, tag);
+        stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
+        for (int i = c.tid; i < (p1 - p0) / 2 * NB; i += kThreads) {
+            const int wq = i / NB, b = i % NB;
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4) + p0 / 2 + wq,
+                          pub[(2 * wq) * NB + b], pub[(2 * wq + 1) * NB + b], 0u, tag);
+        }
+    } else {
+        // tiles of 16 rows x 256 columns over the warps; the four column blocks of a row meet in shared memory
+        const int n_rows = 2 * (p1 - p0), n_tasks = (n_rows + 15) / 16 * 4;
+        float* part = c.hdr->sub;
+        for (int task = c.warp; task < n_tasks; task += kWarps) {
+            float d[4];
+            gemv_tile<NB>(W, D, (task >> 2) * 16, n_rows, c.xs, (task & 3) * 256, c.lane, d);
+            gemv_store<NB>(part, task, c.lane, d);
+        }
+        stream_release(c.st, 1);                         // its barrier also publishes `part` to the CTA
+        for (int i = c.tid; i < (p1 - p0) / 2 * NB; i += kThreads) {     // four rows leave as one 128-bit word
+            const int wq = i / NB, b = i % NB;
+            const float r0 = gemv_sum<NB, 4>(part, 4 * wq, b), r1 = gemv_sum<NB, 4>(part, 4 * wq + 1, b);
+            const float r2 = gemv_sum<NB, 4>(part, 4 * wq + 2, b), r3 = gemv_sum<NB, 4>(part, 4 * wq + 3, b);
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4) + p0 / 2 + wq,
+                          pack_bf16x2(r0, r1), pack_bf16x2(r2, r3), 0u, tag);
+        }
     }
     return true;
 }
@@ -665,6 +743,32 @@ __device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uin
     if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what, p1 > p0 ? &W : nullptr)) return false;
     c.t_ready = clock64();
     if (p1 == p0) return all_ok(ok);
+    if constexpr (NB > 1) {
+        // several sequences: tiles of up to 16 rows x 256 columns on the tensor cores, one column block per warp
+        constexpr int NK = K / 256;
+        const int n_rows = 2 * (p1 - p0);            // at most 16: the launch requires 128 CTAs or more
+        float* part = c.hdr->sub;
+        for (int task = c.warp; task < NK; task += kWarps) {
+            float d[4];
+            gemv_tile<NB>(W, K, 0, n_rows, c.xs, task * 256, c.lane, d);
+            gemv_store<NB>(part, task, c.lane, d);
+        }
+        cta_sync();
+        for (int i = c.tid; i < (p1 - p0) * NB; i += kThreads) {
+            const int pp = i / NB, b = i % NB, pair = p0 + pp;
+            const float s0 = gemv_sum<NB, NK>(part, 2 * pp, b), s1 = gemv_sum<NB, NK>(part, 2 * pp + 1, b);
+            uint32_t rw = rw_early;
+            if (i != c.tid || i >= early_pairs * NB) {
+                if (res_src == nullptr)
+                    rw = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
+                else
+                    ok = ok && wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw, 32 + what);
+            }
+            st_flagged(dst + (size_t)b * (D / 2) + pair, pack_bf16x2(bf_lo(rw) + bf16r(s0), bf_hi(rw) + bf16r(s1)), dst_tag);
+        }
+        stream_release(c.st, 1);
+        return all_ok(ok);
+    }
     const int n_sub = 2 * (p1 - p0) * S;
     float* sub = c.hdr->sub;
     for (int base = 0; base < n_sub; base += kSlots) {
@@ -726,39 +830,64 @@ __device__ bool phase_gu(Cta& c, int l) {
     const bf16* W = nullptr;
     if (!norm_pairs_to_smem<NB>(c, u, gw, ok, u1 > u0 ? &W : nullptr)) return false;
     if (u1 == u0) return true;
-    float xr[32];
-    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
-    uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [unit][sequence]
-    for (int un = u0 + c.warp; un < u1; un += kWarps) {
-        const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
-        float a0[NB], a1[NB];
-        if constexpr (NB == 1) {
-            const bf16* wp[4] = {wu, wu + D, wu + 2 * D, wu + 3 * D};
-            float acc[4][NB];
-            dot_rows_k1024<false, NB, 4>(c, wp, xr, acc);
-            a0[0] = swiglu(acc[0][0], acc[1][0]);
-            a1[0] = swiglu(acc[2][0], acc[3][0]);
-        } else {
+    if constexpr (NB == 1) {
+        float xr[32];
+        if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
+        uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [unit][sequence]
+        for (int un = u0 + c.warp; un < u1; un += kWarps) {
+            const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
+            float a0[NB], a1[NB];
+            if constexpr (NB == 1) {
+                const bf16* wp[4] = {wu, wu + D, wu + 2 * D, wu + 3 * D};
+                float acc[4][NB];
+                dot_rows_k1024<false, NB, 4>(c, wp, xr, acc);
+                a0[0] = swiglu(acc[0][0], acc[1][0]);
+                a1[0] = swiglu(acc[2][0], acc[3][0]);
+            } else {
 #pragma unroll
-            for (int hsel = 0; hsel < 2; ++hsel) {
-                const bf16* wp[2] = {wu + (2 * hsel) * D, wu + (2 * hsel + 1) * D};
-                float acc[2][NB];
-                dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
+                for (int hsel = 0; hsel < 2; ++hsel) {
+                    const bf16* wp[2] = {wu + (2 * hsel) * D, wu + (2 * hsel + 1) * D};
+                    float acc[2][NB];
+                    dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
 #pragma unroll
-                for (int b = 0; b < NB; ++b) (hsel ? a1[b] : a0[b]) = swiglu(acc[0][b], acc[1][b]);
+                    for (int b = 0; b < NB; ++b) (hsel ? a1[b] : a0[b]) = swiglu(acc[0][b], acc[1][b]);
+                }
+            }
+            if (c.lane == 0) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b) pub[(un - u0) * NB + b] = pack_bf16x2(a0[b], a1[b]);
             }
         }
-        if (c.lane == 0) {
-#pragma unroll
-            for (int b = 0; b < NB; ++b) pub[(un - u0) * NB + b] = pack_bf16x2(a0[b], a1[b]);
+        stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
+        // three units (six activations) leave as one 128-bit word
+        for (int i = c.tid; i < (u1 - u0) / 3 * NB; i += kThreads) {
+            const int wq = i / NB, b = i % NB;
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.act) + (size_t)b * (FF / 6) + u0 / 3 + wq,
+                          pub[(3 * wq) * NB + b], pub[(3 * wq + 1) * NB + b], pub[(3 * wq + 2) * NB + b], tag);
         }
-    }
-    stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
-    // three units (six activations) leave as one 128-bit word
-    for (int i = c.tid; i < (u1 - u0) / 3 * NB; i += kThreads) {
-        const int wq = i / NB, b = i % NB;
-        st_flagged128(reinterpret_cast<uint4*>(c.ws.act) + (size_t)b * (FF / 6) + u0 / 3 + wq,
-                      pub[(3 * wq) * NB + b], pub[(3 * wq + 1) * NB + b], pub[(3 * wq + 2) * NB + b], tag);
+    } else {
+        const int n_rows = 4 * (u1 - u0), n_tasks = (n_rows + 15) / 16 * 4;
+        float* part = c.hdr->sub;
+        for (int task = c.warp; task < n_tasks; task += kWarps) {
+            float d[4];
+            gemv_tile<NB>(W, D, (task >> 2) * 16, n_rows, c.xs, (task & 3) * 256, c.lane, d);
+            gemv_store<NB>(part, task, c.lane, d);
+        }
+        stream_release(c.st, 1);                         // its barrier also publishes `part` to the CTA
+        // a lane per unit (four rows, two activations) in groups of four lanes, the fourth idle: the first lane of a group
+        // collects its neighbours' pairs and sends the three units (six activations) off as one 128-bit word
+        const int n_words = (u1 - u0) / 3 * NB;
+        for (int i0 = 0; i0 < n_words * 4; i0 += kThreads) {
+            const int i = i0 + c.tid, wi = i >> 2, k = i & 3;
+            const bool live = wi < n_words && k < 3;
+            const int wq = live ? wi / NB : 0, b = live ? wi % NB : 0;
+            const int r = 12 * wq + 4 * k;               // rows: gate, up, gate, up of two adjacent activations
+            uint32_t w = 0;
+            if (live) w = pack_bf16x2(swiglu(gemv_sum<NB, 4>(part, r, b), gemv_sum<NB, 4>(part, r + 1, b)),
+                                      swiglu(gemv_sum<NB, 4>(part, r + 2, b), gemv_sum<NB, 4>(part, r + 3, b)));
+            const uint32_t w1 = __shfl_down_sync(0xffffffffu, w, 1), w2 = __shfl_down_sync(0xffffffffu, w, 2);
+            if (live && k == 0) st_flagged128(reinterpret_cast<uint4*>(c.ws.act) + (size_t)b * (FF / 6) + u0 / 3 + wq, w, w1, w2, tag);
+        }
     }
     return true;
 }
@@ -792,6 +921,36 @@ __device__ bool phase_head(Cta& c) {
         const bf16* W = stream_acquire(c, c.st.consumed, okw);     // rows [e0, e0 + kHeadRows) of the table
         if (!okw) return false;
         const int rows_here = r1 - e0 < kHeadRows ? r1 - e0 : kHeadRows;
+        if constexpr (NB > 1) {
+            // several sequences: the entry's 32 rows as two 16-row blocks x four column blocks on the tensor cores, then
+            // warp b scans sequence b's 32 logits (lane = row) for the entry's best
+            static_assert(kHeadRows == 32, "one lane per row of an entry");
+            float* part = c.hdr->sub;
+            if (c.warp < 8) {
+                float d[4];
+                gemv_tile<NB>(W, D, (c.warp >> 2) * 16, rows_here, c.xs, (c.warp & 3) * 256, c.lane, d);
+                gemv_store<NB>(part, c.warp, c.lane, d);
+            }
+            cta_sync();
+            if (c.warp < NB) {
+                const int b = c.warp, row = e0 + c.lane;
+                const bool live = c.lane < rows_here;
+                float v = live ? bf16r(gemv_sum<NB, 4>(part, c.lane, b)) : -INFINITY;
+                if (live && p.write_logits) logits[(size_t)b * p.vocab + row] = __float2bfloat16_rn(v);
+                int ix = live ? row : 0x7fffffff;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {       // highest value, lowest row on ties
+                    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+                    if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+                }
+#pragma unroll
+                for (int bb = 0; bb < NB; ++bb)
+                    if (bb == b && v > bv[bb]) { bv[bb] = v; bi[bb] = ix; }      // entries ascend: the first maximum is kept
+            }
+            stream_release(c.st, 1);
+            continue;
+        }
         const int lr = c.warp * R;                                 // this warp's first row inside the entry
         if (lr < rows_here) {
             const bf16* wp[R];
@@ -1049,6 +1208,7 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
     int rc = device_info();
     if (rc != ITTAI_OK) return rc;
     const int grid = g_info.n_sms < Q3_MAX_CTAS ? g_info.n_sms : Q3_MAX_CTAS;
+    if (grid < 128) { set_error("the decode kernel's GEMV tiling needs at least 128 SMs (found %d)", grid); return ITTAI_E_DEVICE; }
     if (grid < p->batch * NKV) { set_error("%d SMs cannot hold one attention item per CTA at batch %d", grid, p->batch); return ITTAI_E_DEVICE; }
     // all the shared memory a CTA may have: header + activations + the weight ring
     const size_t fixed = q3_fixed_smem_bytes(NB);
