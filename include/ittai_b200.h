@@ -148,7 +148,8 @@ int ittai_qwen3_decode_workspace_bytes(int batch, size_t* bytes);
 /* One persistent cooperative launch that runs p->n_steps tokens: per layer RMSNorm+QKV, QK-norm+RoPE+
  * KV append + split-K GQA attention, O-proj+residual, gate/up SwiGLU, down+residual, then final norm +
  * tied lm_head + argmax, with the chosen id fed back on the device.  Replaces the launch of
- * engine.py:153-155 (`_graph_body`) for the decode loop the reference does not have. */
+ * engine.py:153-155 (`_graph_body`) for the decode loop the reference does not have.  One CTA per SM; a device with
+ * fewer than 128 SMs is refused with ITTAI_E_DEVICE (the per-CTA weight slices are sized for a B200's 148). */
 int ittai_qwen3_decode_launch(const IttaiQwen3Decode* p, void* stream);
 
 /* The same launch for callers that cannot allocate device memory at call time (a process whose GPU memory was all handed
