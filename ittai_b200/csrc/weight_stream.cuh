@@ -15,6 +15,10 @@
 #pragma once
 #include "common.cuh"
 
+#ifndef ITTAI_STREAM_EVICT_FIRST
+#define ITTAI_STREAM_EVICT_FIRST 1
+#endif
+
 namespace ittai {
 
 constexpr int kStreamSlots = 16;           // entries in flight at most
@@ -52,8 +56,17 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
 // Contiguous global -> shared copy by the TMA unit; completion is counted in bytes on `bar`.  The destination is this
 // CTA's own shared memory (a shared::cta address is a valid shared::cluster address of the executing CTA).
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, void* bar) {
+#if ITTAI_STREAM_EVICT_FIRST
+    // every streamed byte is read once per token: mark its L2 lines first in line for eviction, so that the stream does
+    // not push out what is reused (flagged words, instruction lines, the other CTAs' polled partials)
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
+#else
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+#endif
 }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Orders this thread's earlier generic-proxy writes before later async-proxy (TMA) accesses to the same memory.
