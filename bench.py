@@ -109,7 +109,7 @@ class ClockSampler:
 SIGLIP_BATCH = 64
 # dram__bytes_read.sum + dram__bytes_write.sum of q3_decode_kernel<1> per decoded token at cache length 4096, from the ncu
 # capture of an 8-token launch summarised under profiles/ (traffic grows with tokens, so it is scaled by the step's 256)
-NCU_DRAM_BYTES_PER_TOKEN = (13.317866e9 + 32.293888e6) / 8
+NCU_DRAM_BYTES_PER_TOKEN = (13.296941e9 + 20.676864e6) / 8
 
 
 def siglip_leg(dev, rank, barrier, iters: int = 20):
