@@ -30,11 +30,24 @@ struct StreamShared {
     uint32_t q_bytes[kStreamSlots];        // its size rounded up to kStreamAlign
     uint32_t issued;                       // entries issued so far (written by the issuing lane)
     uint32_t head;                         // next free ring offset (issuing lane)
-    volatile uint32_t consumed;            // entries released so far (written by compute thread 0)
+    uint32_t consumed;                     // entries released so far (compute thread 0, release / acquire accesses)
     volatile uint32_t stop;                // compute threads are leaving early: issue nothing more
+    volatile uint32_t kv_epoch;            // 1 + index of the last (step, layer) whose attention output this CTA has seen whole
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// The ring's space goes back to the issuing lane through `consumed`: the compute threads' reads of an entry come before
+// the release store (they all passed a CTA barrier before thread 0 stores), the issuing lane's TMA write into that space
+// comes after its acquire load.
+__device__ __forceinline__ void st_release_cta(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ void mbar_init(void* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -89,6 +102,7 @@ __device__ __forceinline__ void stream_init(Stream& s, int tid) {
         s.sh->head = 0;
         s.sh->consumed = 0;
         s.sh->stop = 0;
+        s.sh->kv_epoch = 0;
         fence_mbar_init();
     }
     __syncthreads();        // all kBlock threads: both roles see the initialised barriers
@@ -97,7 +111,7 @@ __device__ __forceinline__ void stream_init(Stream& s, int tid) {
 // Issuing lane: find room for `bytes` (no entry wraps around the end of the ring).  Returns false when the ring is full.
 __device__ __forceinline__ bool stream_alloc(const Stream& s, uint32_t bytes, uint32_t& off) {
     StreamShared* sh = s.sh;
-    const uint32_t consumed = sh->consumed;
+    const uint32_t consumed = ld_acquire_cta(&sh->consumed);
     if (sh->issued - consumed >= (uint32_t)kStreamSlots) return false;
     if (sh->issued == consumed) { off = 0; return bytes <= s.ring_bytes; }   // empty: restart at the base
     const uint32_t tail = sh->q_off[consumed % kStreamSlots];
@@ -141,10 +155,13 @@ __device__ __forceinline__ const unsigned char* stream_wait(const Stream& s, uin
 }
 
 // Compute threads: everyone has finished reading the `n` oldest entries; hand their space back to the issuing lane.
+__device__ __forceinline__ void stream_release_synced(Stream& s, int n) {      // after a barrier that follows the last read
+    s.consumed += (uint32_t)n;
+    if (threadIdx.x == 0) st_release_cta(&s.sh->consumed, s.consumed);
+}
 __device__ __forceinline__ void stream_release(Stream& s, int n) {
     cta_sync();
-    s.consumed += (uint32_t)n;
-    if (threadIdx.x == 0) s.sh->consumed = s.consumed;
+    stream_release_synced(s, n);
 }
 
 // Issuing lane, before it exits: let every copy it launched land (bounded), so none is in flight when the CTA retires.

@@ -37,8 +37,30 @@ def qwen3_tiny():
     print("qwen3_tiny", picks.tolist())
 
 
+def _distance(logits, picks, free, ref_logits, ref_ids, top_i):
+    """How far one run of the oracle is from the pinned one, in the units the parity tests use."""
+    a, b = logits.float(), ref_logits.float()
+    sa, sb = a[:, ::1009], b[:, ::1009]
+    same = 0
+    while same < len(ref_ids) and int(free[same]) == int(ref_ids[same]):
+        same += 1
+    return dict(strided_max_abs=(sa - sb).abs().max().item(),
+                strided_min_cos=torch.nn.functional.cosine_similarity(sa, sb, dim=-1).min().item(),
+                full_max_abs=(a - b).abs().max().item(),
+                strided_rms=(sa - sb).pow(2).mean().sqrt().item(), full_rms=(a - b).pow(2).mean().sqrt().item(),
+                full_min_cos=torch.nn.functional.cosine_similarity(a, b, dim=-1).min().item(),
+                top8_max_abs=(torch.gather(a, 1, top_i) - torch.gather(b, 1, top_i)).abs().max().item(),
+                argmax_agree=int((picks == ref_ids).sum()), free_running_prefix_equal=same)
+
+
 def qwen3_full():
-    """BASELINE config 1: full 28-layer model, 32-id prompt seed 0, 64 greedy steps on CPU."""
+    """BASELINE config 1: full 28-layer model, 32-id prompt seed 0, 64 greedy steps on CPU.
+
+    Besides the pinned run (bf16, sdpa attention) the fixture records how far the oracle's own variants are from it
+    on the same weights and ids: bf16 with the eager attention backend, and fp32.  Each variant is teacher-forced on
+    the pinned ids (every step judged on its own) and also run freely.  The parity tests use these distances as the
+    noise floor of the comparison instead of a hand-picked constant.
+    """
     from oracle import qwen3_hf as hf
     dims = hf.FULL
     m = hf.build_hf(dims, seed=0)
@@ -46,10 +68,18 @@ def qwen3_full():
     picks, logits, cache = hf.greedy(m, ids, 64)
     top_v, top_i = logits.float().topk(8, dim=-1)
     k0, v0 = hf.cache_kv(cache, dims.n_layers - 1)
+    floor = {}
+    for name, kw in (("bf16_eager_attention", dict(attn="eager")), ("fp32_sdpa", dict(dtype=torch.float32))):
+        mv = hf.build_hf(dims, seed=0, **kw)
+        p_tf, l_tf, _ = hf.greedy(mv, ids, 64, forced=picks)
+        p_free, _, _ = hf.greedy(mv, ids, 64)
+        floor[name] = _distance(l_tf, p_tf, p_free, logits, picks, top_i)
+        print(name, floor[name])
+        del mv
     torch.save(dict(meta=dict(_versions(), dims=dims.__dict__, seed=0, prompt_seed=0, attn="sdpa", dtype="bf16"),
                     prompt=ids, ids=picks, top_values=top_v.to(torch.bfloat16), top_indices=top_i.to(torch.int32),
                     strided_logits=logits[:, ::1009].clone(), logit_norm=logits.float().norm(dim=-1),
-                    k_last_layer_head0=k0[0, 0].clone()),
+                    k_last_layer_head0=k0[0, 0].clone(), variant_distance=floor),
                os.path.join(HERE, "qwen3_full_c1.pt"))
     print("qwen3_full", picks.tolist())
 
