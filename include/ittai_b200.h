@@ -141,39 +141,21 @@ int ittai_decode_status(const uint32_t* status_host, char* msg, size_t msg_len);
 
 /* ---- Qwen3 decode ------------------------------------------------------------------------------- */
 
-/* Scratch bytes the decode kernels need for `batch` sequences (1, 2, 4 or 8): the mailboxes through which the CTAs
- * hand activations, split-K partials and argmax candidates to each other, and the abort flag.  Replaces the buffer
- * plan of engine.py:123-134. */
+/* Scratch bytes the decode kernels need for `batch` (1, 2, 4 or 8) sequences (activations, split-K partials, argmax
+ * candidates, barrier and arrival counters).  Replaces the buffer plan of engine.py:123-134. */
 int ittai_qwen3_decode_workspace_bytes(int batch, size_t* bytes);
-
-/* Where the mailboxes sit inside the workspace and how the kernel cuts the work on a device with `n_sms` SMs, for tests
- * and profiles that plant a phase's input or read a phase's output (ittai_qwen3_phase_launch).  Every CTA owns one
- * mailbox per kind of vector; a mail word is 128 bits: payload in bits 0..111 (seven bf16 values, or four with the rest
- * unused for the projections), tag 1 + (step * (n_layers + 1) + layer) % 65535 in bits 112..127.
- *   h, hmid: word [cta][b][p] holds CTA p's rows [1024 p / n, 1024 (p+1) / n) of sequence b (mail_stride slots per row);
- *   act:     words [cta][b][p][0..act_words) hold CTA p's values [3072 p / n, 3072 (p+1) / n), seven per word;
- *   attn:    words [cta][b][g][j * attn_words_per_owner + k] hold, seven per word, the 2 * 128 / merge_ctas values that
- *            merging CTA j of kv head g owns: dims [j, j+1) * 128 / merge_ctas of head 2g, then of head 2g + 1;
- *   qkv:     words [cta][which * 32 + i] hold elements 4i..4i+3 of q head 2g (which 0), q head 2g+1 (1), k head g (2),
- *            v head g (3) for the CTA whose attention item is (b, g, split) = cta index in that order.
- * No counterpart in the reference (its kernels keep one copy of every activation matrix in global memory). */
-typedef struct IttaiQwen3Layout {
-    size_t bytes, off_h, off_hmid, off_act, off_attn, off_qkv, off_part, off_cand;
-    int32_t n_ctas, mail_stride, act_words, attn_words, qkv_words, n_splits, merge_ctas, attn_words_per_owner;
-} IttaiQwen3Layout;
-int ittai_qwen3_decode_layout(int batch, int n_sms, IttaiQwen3Layout* out);
 
 /* One persistent cooperative launch that runs p->n_steps tokens: per layer RMSNorm+QKV, QK-norm+RoPE+
  * KV append + split-K GQA attention, O-proj+residual, gate/up SwiGLU, down+residual, then final norm +
  * tied lm_head + argmax, with the chosen id fed back on the device.  Replaces the launch of
  * engine.py:153-155 (`_graph_body`) for the decode loop the reference does not have.  One CTA per SM; a device with
- * fewer than 147 SMs is refused with ITTAI_E_DEVICE (weight slices and mailboxes are sized for a B200's 148). */
+ * fewer than 128 SMs is refused with ITTAI_E_DEVICE (the per-CTA weight slices are sized for a B200's 148). */
 int ittai_qwen3_decode_launch(const IttaiQwen3Decode* p, void* stream);
 
 /* The same launch for callers that cannot allocate device memory at call time (a process whose GPU memory was all handed
  * to a pool at start-up, a host runtime without a device allocator, a loop that cannot afford cudaMalloc's device-wide
  * synchronisation).  p->workspace is ignored: the scratch is a static device array inside the library, at most
- * ITTAI_STATIC_DECODE_MAX_BATCH sequences (about 7.5 MB, held by every GPU that loads the library until the process
+ * ITTAI_STATIC_DECODE_MAX_BATCH sequences (about 2.3 MB, held by every GPU that loads the library until the process
  * exits); a larger p->batch is rejected with ITTAI_E_ARG.  The call itself allocates nothing (no cudaMalloc / cudaFree,
  * no allocating library routine).  Its first call on a device looks up the array's device address
  * (cudaGetSymbolAddress): make that first call outside any stream capture.  All calls share the one array and it keeps

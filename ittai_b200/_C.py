@@ -20,7 +20,7 @@ PH_QKV, PH_ATTN, PH_OPROJ, PH_GU, PH_DOWN, PH_HEAD = range(6)
 # every symbol include/ittai_b200.h declares
 EXPORTS = (
     "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
-    "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_layout", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
+    "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
     "ittai_qwen3_decode_launch_static",
     "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows", "ittai_row_stats",
     "ittai_qwen3_qk_rope_scatter", "ittai_siglip_im2col", "ittai_embed_rows", "ittai_qwen3_final_pool",
@@ -45,13 +45,6 @@ class Qwen3Decode(C.Structure):
         ("forced", C.c_void_p), ("out_ids", C.c_void_p), ("logits", C.c_void_p),
         ("workspace", C.c_void_p), ("status", C.c_void_p), ("step_ns", C.c_void_p), ("phase_clk", C.c_void_p),
     ]
-
-
-class Qwen3Layout(C.Structure):
-    """Mirror of ``struct IttaiQwen3Layout``."""
-    _fields_ = [(n, C.c_size_t) for n in ("bytes", "off_h", "off_hmid", "off_act", "off_attn", "off_qkv", "off_part", "off_cand")] + \
-               [(n, C.c_int32) for n in ("n_ctas", "mail_stride", "act_words", "attn_words", "qkv_words", "n_splits", "merge_ctas",
-                                         "attn_words_per_owner")]
 
 
 class QkRope(C.Structure):
@@ -102,7 +95,6 @@ def lib() -> C.CDLL:
     L.ittai_device_check.argtypes = [C.c_int, C.POINTER(C.c_int)]
     L.ittai_decode_status.argtypes = [C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]
     L.ittai_qwen3_decode_workspace_bytes.argtypes = [C.c_int, C.POINTER(C.c_size_t)]
-    L.ittai_qwen3_decode_layout.argtypes = [C.c_int, C.c_int, C.POINTER(Qwen3Layout)]
     L.ittai_qwen3_decode_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
     L.ittai_qwen3_phase_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_int, C.c_int, C.c_void_p]
     L.ittai_qwen3_decode_launch_static.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]

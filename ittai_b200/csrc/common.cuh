@@ -120,16 +120,25 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
-// ---- mail words: payload + tag in one 128-bit word ---------------------------------------------------------
+// ---- flagged words: payload + tag in one 64-bit word -------------------------------------------------------
 // The role of the reference's arrive/ready flags (src/ittai/qwen3/base.py:42-78), which spin without a limit; here
-// the flag travels with the data and every wait is bounded.  Bits 0..111 carry the payload (seven bf16 values or three
-// fp32 values), bits 112..127 the tag.  Moved by single-copy-atomic .b128 accesses.
-__device__ __forceinline__ void ld_mail(const void* p, uint64_t& lo, uint64_t& hi) {
+// the flag travels with the data and every wait is bounded.
+__device__ __forceinline__ uint64_t ld_flagged(const uint64_t* p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_flagged(uint64_t* p, uint32_t payload, uint32_t tag) {
+    const uint64_t v = ((uint64_t)tag << 32) | payload;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// 128-bit flagged words: three 32-bit payloads + the tag, moved by single-copy-atomic .b128 accesses.  They carry the
+// vectors whose consumers would otherwise poll several 64-bit words one after the other.
+__device__ __forceinline__ void ld_flagged128(const void* p, uint64_t& lo, uint64_t& hi) {
     asm volatile("{\n.reg .b128 t;\nld.relaxed.gpu.global.b128 t, [%2];\nmov.b128 {%0, %1}, t;\n}\n" : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
 }
-// a, b, c: payload words 0..2; d16: payload bits 96..111.
-__device__ __forceinline__ void st_mail(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d16, uint32_t tag) {
-    const uint64_t lo = ((uint64_t)b << 32) | a, hi = ((uint64_t)((tag << 16) | (d16 & 0xffffu)) << 32) | c;
+__device__ __forceinline__ void st_flagged128(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t tag) {
+    const uint64_t lo = ((uint64_t)b << 32) | a, hi = ((uint64_t)tag << 32) | c;
     asm volatile("{\n.reg .b128 t;\nmov.b128 t, {%1, %2};\nst.relaxed.gpu.global.b128 [%0], t;\n}\n" ::"l"(p), "l"(lo), "l"(hi) : "memory");
 }
 // Two floats -> packed bf16 pair (round to nearest even), one conversion instruction.
@@ -167,29 +176,38 @@ __device__ __forceinline__ void report_status(uint32_t* status, uint32_t* sync, 
     atomicExch(&sync[1], 1u);
 }
 
-// The slow side of a poll loop, entered once per 1024 polls: has another CTA aborted, has this wait run out?  Kept out of
-// line so that the dozens of poll sites stay a handful of instructions each.
-static __device__ __noinline__ bool keep_waiting(const Waiter& w, uint32_t spins, int what, uint32_t seen, uint32_t tag) {
-    if (ld_relaxed(&w.sync[1]) != 0u) return false;
-    if (spins >= w.limit) {
-        report_status(w.status, w.sync, ITTAI_ST_FLAG_TIMEOUT, (uint32_t)what, blockIdx.x, seen, tag);
+// The slow side of a poll loop, entered once per 1024 polls: has another CTA aborted, has this wait run out?  Inlined on
+// purpose: as a real call (arguments by value, cold path only) it cost 20 us per decoded token on a B200, the call's
+// register constraints reaching into the hot loops around it.
+static __device__ __forceinline__ bool keep_waiting(uint32_t* sync, uint32_t* status, uint32_t limit, uint32_t spins, int what,
+                                                    uint32_t seen, uint32_t tag) {
+    if (ld_relaxed(&sync[1]) != 0u) return false;
+    if (spins >= limit) {
+        report_status(status, sync, ITTAI_ST_FLAG_TIMEOUT, (uint32_t)what, blockIdx.x, seen, tag);
         return false;
     }
     return true;
 }
 
-// Polls one mail word until its tag matches; v[0..2] = payload words, v[3] = payload bits 96..111 (and the tag above
-// them).  Returns false when the wait ran out or another CTA aborted.
-__device__ __forceinline__ bool wait_mail(const Waiter& w, const void* p, uint32_t tag, uint32_t (&v)[4], int what) {
+// Polls one word until its tag matches; returns false when the wait ran out or another CTA aborted.
+__device__ __forceinline__ bool wait_word(const Waiter& w, const uint64_t* p, uint32_t tag, uint32_t& payload, int what) {
+    uint32_t spins = 0;
+    for (;;) {
+        const uint64_t v = ld_flagged(p);
+        if ((uint32_t)(v >> 32) == tag) { payload = (uint32_t)v; return true; }
+        if (((++spins) & 1023u) == 0u && !keep_waiting(w.sync, w.status, w.limit, spins, what, (uint32_t)(v >> 32), tag)) return false;
+    }
+}
+
+
+// The same for a 128-bit word: payloads a, b, c.
+__device__ __forceinline__ bool wait_word128(const Waiter& w, const void* p, uint32_t tag, uint32_t& a, uint32_t& b, uint32_t& c, int what) {
     uint32_t spins = 0;
     for (;;) {
         uint64_t lo, hi;
-        ld_mail(p, lo, hi);
-        if ((uint32_t)(hi >> 48) == tag) {
-            v[0] = (uint32_t)lo; v[1] = (uint32_t)(lo >> 32); v[2] = (uint32_t)hi; v[3] = (uint32_t)(hi >> 32);
-            return true;
-        }
-        if (((++spins) & 1023u) == 0u && !keep_waiting(w, spins, what, (uint32_t)(hi >> 48), tag)) return false;
+        ld_flagged128(p, lo, hi);
+        if ((uint32_t)(hi >> 32) == tag) { a = (uint32_t)lo; b = (uint32_t)(lo >> 32); c = (uint32_t)hi; return true; }
+        if (((++spins) & 1023u) == 0u && !keep_waiting(w.sync, w.status, w.limit, spins, what, (uint32_t)(hi >> 32), tag)) return false;
     }
 }
 

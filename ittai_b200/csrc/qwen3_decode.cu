@@ -1,13 +1,12 @@
 // Qwen3-0.6B decode: one persistent cooperative kernel per launch runs n_steps tokens; the chosen token id is fed
 // back on the device.
 //
-//  * Data flow instead of grid barriers: every vector one phase hands to the next travels as 128-bit mail words
-//    (payload + tag of the producing step and layer) that the producer writes into a private mailbox of every CTA
-//    that needs them, and a consumer polls exactly the words of its own mailbox (qwen3_ws.h).
+//  * Data flow instead of grid barriers: every vector one phase hands to the next travels as flagged 64- or 128-bit words
+//    (payload + tag of the producing step and layer), and a consumer polls exactly the words it needs (qwen3_ws.h).
 //  * Weight stream: each CTA's slices of the layer matrices and of the KV cache are pulled into a shared-memory ring by
 //    TMA bulk copies issued far ahead of use (weight_stream.cuh), so HBM keeps streaming while phases wait on each other.
-//  * Batch-1 decode is HBM-bound (about 1.4 flop per weight byte): each warp multiplies whole weight sub-rows with
-//    128-bit accesses and reduces with shuffles.  With several sequences the GEMV phases use warp-level
+//  * Batch-1 decode is HBM-bound (about 1.4 flop per weight byte): each warp multiplies whole 1024-column weight
+//    sub-rows with 128-bit accesses and reduces with shuffles.  With several sequences the GEMV phases use warp-level
 //    tensor-core tiles with the sequences as the N dimension (gemv_tile).
 //
 // Rounding points follow the eager modules: every Linear output, norm output, rotary product and sum, SiLU, gate*up
@@ -16,8 +15,6 @@
 // re-cut for one token: the row-norm scale is applied before the GEMV instead of after the GEMM, and keys and values go
 // straight into the cache instead of a staging matrix.  KV cache, split-K decode attention, lm_head and argmax have no
 // counterpart in the reference.
-#include <cstdio>
-
 #include "common.cuh"
 #include "qwen3_ws.h"
 #include "weight_stream.cuh"
@@ -25,26 +22,22 @@
 namespace ittai {
 
 constexpr int D = ITTAI_Q3_D, NKV = ITTAI_Q3_NKV, HD = ITTAI_Q3_HD, FF = ITTAI_Q3_FF;
-constexpr int DQ = ITTAI_Q3_DQ, DQKV = ITTAI_Q3_DQKV, DGU = ITTAI_Q3_DGU;
-constexpr int MS = Q3_MAIL_STRIDE;
+constexpr int DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV, DGU = ITTAI_Q3_DGU;
 constexpr int kTile = 128;                       // cache positions per attention tile = one ring entry of K and one of V
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kPartFloats = 12 * 16;             // at most 12 tiles (16 rows x 256 columns) per CTA and phase
-constexpr int kStreamPhases = 5;                 // phases of a layer whose weights or cache rows come through the ring
-constexpr int kPubHalves = 32;                   // outputs of one CTA and sequence in a GEMV phase (at most 28)
-constexpr int kMsgFloats = 4 + 2 * HD;           // one split's partial: m[2], l[2], o[2][128]
+constexpr int kStreamPhases = 5;                 // phases of a layer whose weights or cache rows come through the ring (as does the head's table)
 
 // ---- shared-memory plan (dynamic): header | activations or attention scratch | weight ring -----------------
 struct SmemHdr {
     StreamShared stream;
+    float red[kWarps * ITTAI_MAX_BATCH];         // per-warp partial sums of the norm
     int pos0[ITTAI_MAX_BATCH];                   // cache lengths at kernel entry
     int pos_s[ITTAI_MAX_BATCH];
     int tok_s[ITTAI_MAX_BATCH];
     float bestv[kWarps];
     int besti[kWarps];
-    float sub[kPartFloats * ITTAI_MAX_BATCH];    // partial dot products: [task] at batch 1, [task][16 rows][sequence] for the tiles
-    uint16_t pub[kPubHalves * ITTAI_MAX_BATCH];  // this CTA's bf16 outputs of the running phase, [sequence][row]
-    uint16_t res[8 * ITTAI_MAX_BATCH];           // the residual rows this CTA owns, [sequence][row]
+    float sub[kPartFloats * ITTAI_MAX_BATCH];    // partial dot products of the GEMV tiles: [task][16 rows][sequence]
     float candv[Q3_MAX_CTAS];                    // argmax candidates of every CTA
     int candi[Q3_MAX_CTAS];
 };
@@ -53,8 +46,8 @@ struct SmemAttn {
     float wm[kWarps][2], wl[kWarps][2];          // per-warp running max and sum
     bf16 knew[HD];
     bf16 vnew[HD];
-    float msg[kMsgFloats];                       // this split's partial as it is mailed: m[2], l[2], o[2][128]
-    float ored[kWarps][2][HD];                   // per-warp outputs; later the partials of all splits, [split][3 * words]
+    uint32_t pub[HD];                            // merged output pairs of this CTA on their way into 128-bit words
+    float ored[kWarps][2][HD];
 };
 constexpr size_t kHdrBytes = (sizeof(SmemHdr) + 255) / 256 * 256;
 __host__ __device__ constexpr size_t q3_fixed_smem_bytes(int nb) {
@@ -62,7 +55,6 @@ __host__ __device__ constexpr size_t q3_fixed_smem_bytes(int nb) {
     size_t at = sizeof(SmemAttn);
     return kHdrBytes + ((xs > at ? xs : at) + 255) / 256 * 256;
 }
-static_assert(Q3_PART_WORDS * 3 <= kWarps * 2 * HD, "the partials of all splits must fit the per-warp output scratch");
 
 struct Cta {
     const IttaiQwen3Decode& p;
@@ -78,9 +70,8 @@ struct Cta {
     long long t_ready;  // cycle counter when the current phase had its inputs (in-kernel profile)
 };
 
-// Tag of the data a (step, layer) produces; layer n_layers names the stream entering the head.  Never zero, and two
-// versions of a word that follow each other (one layer or one step apart) never share a tag.
-__device__ __forceinline__ uint32_t tag_of(const Cta& c, int step, int l) { return 1u + (uint32_t)(step * (c.p.n_layers + 1) + l) % 65535u; }
+// Tag of the data a (step, layer) produces; layer n_layers names the stream entering the head.  Never zero.
+__device__ __forceinline__ uint32_t tag_of(const Cta& c, int step, int l) { return (uint32_t)(step * (c.p.n_layers + 1) + l + 1); }
 
 // CTA-uniform verdict on per-thread waits.
 __device__ __forceinline__ bool all_ok(bool ok) { return !cta_or(!ok); }
@@ -88,6 +79,11 @@ __device__ __forceinline__ bool all_ok(bool ok) { return !cta_or(!ok); }
 __host__ __device__ __forceinline__ void split_range(int n, int parts, int i, int& lo, int& hi) {
     lo = (int)(((unsigned)n * (unsigned)i) / (unsigned)parts);          // n * parts stays far below 2^32
     hi = (int)(((unsigned)n * (unsigned)(i + 1)) / (unsigned)parts);
+}
+
+__device__ __forceinline__ int attn_splits(int ncta, int batch) {
+    int s = ncta / (batch * NKV);
+    return s < 1 ? 1 : (s > Q3_MAX_SPLITS ? Q3_MAX_SPLITS : s);
 }
 
 // The attention work of this CTA at one step: item (b, g, s) = CTA index; its cache range [start, start + n_old) of
@@ -99,7 +95,7 @@ struct AttnItem {
 };
 __device__ __forceinline__ AttnItem attn_item(const Cta& c, int step) {
     AttnItem it;
-    const int B = c.p.batch, n_splits = q3_attn_splits(c.ncta, B);
+    const int B = c.p.batch, n_splits = attn_splits(c.ncta, B);
     it.active = c.cta < B * NKV * n_splits;
     const int item = it.active ? c.cta : 0;
     it.b = item / (NKV * n_splits); it.g = (item / n_splits) % NKV; it.s = item % n_splits;
@@ -122,21 +118,16 @@ constexpr int kHeadRows = 32;                    // table rows per streamed head
 
 __device__ __forceinline__ bool head_runs(const Cta& c, int step) { return step >= c.p.n_forced - 1; }
 
-// This CTA's rows of each layer matrix: quads of projection rows, rows of the two residual projections, SwiGLU outputs
-// (two weight rows each).
-__host__ __device__ __forceinline__ void qkv_rows(int ncta, int cta, int& r0, int& r1) { split_range(DQKV / 4, ncta, cta, r0, r1); r0 *= 4; r1 *= 4; }
-__host__ __device__ __forceinline__ void res_rows(int ncta, int cta, int& r0, int& r1) { split_range(D, ncta, cta, r0, r1); }
-__host__ __device__ __forceinline__ void act_cols(int ncta, int cta, int& a0, int& a1) { split_range(FF, ncta, cta, a0, a1); }
-
 // The issuing lane's whole life: walk phases [k_begin, k_end) in execution order, launch every slice as soon as the
 // ring has room, then wait for the last copies to land.  It stops early when the compute threads raise `stop`.
 // Slice addresses are linear in the layer index, so everything but one small division per step is hoisted.
 //
 // Cache tiles and the row appended one step earlier: the K/V tiles of (step s, layer l) contain the row that some CTA
-// appended at (step s - 1, layer l).  That store is ordered before the attention output of (s - 1, l) (the appending
-// thread fences before its CTA publishes its partial, and the output needs every partial), so the tiles are held back
-// until this CTA's compute threads have received that whole output (`kv_epoch`), and a fence pair orders the copy
-// after what they observed.  The hold costs nothing: the condition was met a whole token ago.
+// appended at (step s - 1, layer l).  That store (and the fences behind it) comes before the appending CTA publishes its
+// split's partial, and the attention output of (s - 1, l) needs every partial; so the tiles are held back until this
+// CTA's compute threads have received that whole output and said so in `kv_epoch`.  The hold costs nothing (the condition
+// was met a whole token ago, except with a single layer), and it replaces an ordering that used to rest on the ring being
+// smaller than what a CTA streams between the two points.
 __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t limit = c.w.limit;
@@ -146,17 +137,19 @@ __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     const char* base[kStreamPhases];
     size_t stride[kStreamPhases];
     uint32_t nbytes[kStreamPhases];
-    qkv_rows(c.ncta, c.cta, lo, hi);
-    base[ITTAI_PH_QKV] = reinterpret_cast<const char*>(p.wqkv) + (size_t)lo * D * 2;
-    stride[ITTAI_PH_QKV] = (size_t)DQKV * D * 2; nbytes[ITTAI_PH_QKV] = (uint32_t)(hi - lo) * D * 2;
-    res_rows(c.ncta, c.cta, lo, hi);
-    base[ITTAI_PH_OPROJ] = reinterpret_cast<const char*>(p.wo) + (size_t)lo * DQ * 2;
-    stride[ITTAI_PH_OPROJ] = (size_t)D * DQ * 2; nbytes[ITTAI_PH_OPROJ] = (uint32_t)(hi - lo) * DQ * 2;
-    base[ITTAI_PH_DOWN] = reinterpret_cast<const char*>(p.wd) + (size_t)lo * FF * 2;
-    stride[ITTAI_PH_DOWN] = (size_t)D * FF * 2; nbytes[ITTAI_PH_DOWN] = (uint32_t)(hi - lo) * FF * 2;
-    act_cols(c.ncta, c.cta, lo, hi);
-    base[ITTAI_PH_GU] = reinterpret_cast<const char*>(p.wgu) + (size_t)2 * lo * D * 2;
-    stride[ITTAI_PH_GU] = (size_t)DGU * D * 2; nbytes[ITTAI_PH_GU] = (uint32_t)(hi - lo) * 2 * D * 2;
+    split_range(DQKV / 4, c.ncta, c.cta, lo, hi);    // 128-bit words of the projection: two row pairs each
+    lo *= 2; hi *= 2;
+    base[ITTAI_PH_QKV] = reinterpret_cast<const char*>(p.wqkv) + (size_t)2 * lo * D * 2;
+    stride[ITTAI_PH_QKV] = (size_t)DQKV * D * 2; nbytes[ITTAI_PH_QKV] = (uint32_t)(hi - lo) * 2 * D * 2;
+    split_range(D / 2, c.ncta, c.cta, lo, hi);
+    base[ITTAI_PH_OPROJ] = reinterpret_cast<const char*>(p.wo) + (size_t)2 * lo * DQ * 2;
+    stride[ITTAI_PH_OPROJ] = (size_t)D * DQ * 2; nbytes[ITTAI_PH_OPROJ] = (uint32_t)(hi - lo) * 2 * DQ * 2;
+    base[ITTAI_PH_DOWN] = reinterpret_cast<const char*>(p.wd) + (size_t)2 * lo * FF * 2;
+    stride[ITTAI_PH_DOWN] = (size_t)D * FF * 2; nbytes[ITTAI_PH_DOWN] = (uint32_t)(hi - lo) * 2 * FF * 2;
+    split_range(FF / 6, c.ncta, c.cta, lo, hi);      // 128-bit words of the SwiGLU output: three units of four rows each
+    lo *= 3; hi *= 3;
+    base[ITTAI_PH_GU] = reinterpret_cast<const char*>(p.wgu) + (size_t)4 * lo * D * 2;
+    stride[ITTAI_PH_GU] = (size_t)DGU * D * 2; nbytes[ITTAI_PH_GU] = (uint32_t)(hi - lo) * 4 * D * 2;
     base[ITTAI_PH_ATTN] = nullptr; stride[ITTAI_PH_ATTN] = (size_t)p.batch * NKV * p.kv_cap * HD * 2; nbytes[ITTAI_PH_ATTN] = 0;
     int h_lo, h_hi;
     split_range(p.vocab, c.ncta, c.cta, h_lo, h_hi);
@@ -175,11 +168,9 @@ __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
             if (ph == ITTAI_PH_ATTN && n > 0 && step > 0) {
                 const uint32_t need = (uint32_t)((step - 1) * L + l) + 1u;
                 uint32_t spins = 0;
-                while (c.st.sh->kv_epoch < need) {
+                while (ld_acquire_cta(&c.st.sh->kv_epoch) < need) {
                     if (c.st.sh->stop != 0u || ++spins > (limit << 4)) { stream_drain(c.st, limit); return; }
                 }
-                asm volatile("fence.acq_rel.gpu;" ::: "memory");
-                fence_proxy_async();
             }
             for (int tile = 0; tile < n; ++tile) {
                 const char* src;
@@ -214,39 +205,6 @@ __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     stream_drain(c.st, limit);
 }
 
-// ---- mail helpers ------------------------------------------------------------------------------------
-// Seven bf16 values of a word into consecutive halves of shared memory (`cnt` of them are real).
-__device__ __forceinline__ void unpack7(const uint32_t (&v)[4], uint16_t* d, int cnt) {
-#pragma unroll
-    for (int e = 0; e < 7; ++e)
-        if (e < cnt) d[e] = (uint16_t)(v[e >> 1] >> ((e & 1) * 16));
-}
-// Up to seven bf16 values from shared memory as one word.
-__device__ __forceinline__ void send7(void* dst, const uint16_t* s, int cnt, uint32_t tag) {
-    uint32_t h[7];
-#pragma unroll
-    for (int e = 0; e < 7; ++e) h[e] = e < cnt ? (uint32_t)s[e] : 0u;
-    st_mail(dst, h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6], tag);
-}
-
-// Collects an N-value bf16 vector per sequence that arrives as K words of up to seven values from every producer CTA
-// (producer p owns values split_range(N, ncta, p)) into dst[b * FF + i].  `mail`: this CTA's mailbox, [NB][MS][K].
-// Returns this thread's verdict; the caller's next barrier collects the verdicts and publishes the values.
-template <int NB, int K>
-__device__ __forceinline__ bool gather7(Cta& c, const uint4* mail, int N, uint32_t tag, int what, uint16_t* dst) {
-    const int per = c.ncta * K;
-    for (int i = c.tid; i < per * NB; i += kThreads) {
-        const int b = NB == 1 ? 0 : i / per, r = i - b * per, pr = r / K, j = r - pr * K;
-        int lo, hi;
-        split_range(N, c.ncta, pr, lo, hi);
-        const int start = lo + 7 * j;
-        uint32_t v[4];
-        if (!wait_mail(c.w, mail + ((size_t)b * MS + pr) * K + j, tag, v, what)) return false;
-        unpack7(v, dst + b * FF + start, hi - start);
-    }
-    return true;
-}
-
 // Entry number n of the stream, with a CTA-uniform verdict.
 __device__ __forceinline__ const bf16* stream_acquire(Cta& c, uint32_t n, bool& ok) {
     const unsigned char* ptr = stream_wait(c.st, n, c.w);
@@ -254,65 +212,95 @@ __device__ __forceinline__ const bf16* stream_acquire(Cta& c, uint32_t n, bool& 
     return reinterpret_cast<const bf16*>(ptr);
 }
 
-// ---- activations of one 1024-wide row in registers ---------------------------------------------------------
-// Lane owns the 16-byte chunks lane, lane+32, lane+64, lane+96 of a row: 32 values.
-__device__ __forceinline__ void unpack8(const uint4& q, float* x) {
-    x[0] = bf_lo(q.x); x[1] = bf_hi(q.x); x[2] = bf_lo(q.y); x[3] = bf_hi(q.y);
-    x[4] = bf_lo(q.z); x[5] = bf_hi(q.z); x[6] = bf_lo(q.w); x[7] = bf_hi(q.w);
-}
-__device__ __forceinline__ void load_gains(const bf16* gain, int lane, uint4 (&gq)[4]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) gq[i] = *reinterpret_cast<const uint4*>(gain + (lane + 32 * i) * 8);
-}
-// RMSNorm of the row on the way into registers: xr = bf16(bf16(x * rstd) * gain), the value the following Linear sees
-// in the eager model.  The lanes of a warp hold the whole row between them, so every warp reduces the sum of squares
-// itself and the norm costs no CTA barrier.  `gq`: this lane's gains, loaded by the caller BEFORE it waits for the
-// input: a global load issued after the wait would put a memory round trip on the critical path of every layer.
-__device__ __forceinline__ void load_xreg_norm(const uint32_t* xs, const uint4 (&gq)[4], float eps, int lane, float (&xr)[32]) {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        unpack8(*reinterpret_cast<const uint4*>(xs + (lane + 32 * i) * 4), &xr[i * 8]);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ss = fmaf(xr[i * 8 + e], xr[i * 8 + e], ss);
-    }
-    ss = warp_sum(ss);
-    const float rstd = 1.0f / sqrtf(ss * (1.0f / D) + eps);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float g[8];
-        unpack8(gq[i], g);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) xr[i * 8 + e] = bf16r(bf16r(xr[i * 8 + e] * rstd) * g[e]);
-    }
-}
-// Several sequences: the rows are normalised in place in shared memory (a warp per row), for the tensor-core tiles.
+// ---- RMSNorm of one row (already in registers, one bf16 pair per thread) into shared memory --------------
+// xs[i] = bf16(bf16(x*rstd) * gain): the value the following Linear sees in the eager model.
+// NB rows (one bf16 pair per thread each) -> xs[b][i] = bf16(bf16(x*rstd) * gain), the value the following Linear sees in
+// the eager model.  `gw` is this thread's pair of gains, loaded by the caller BEFORE it waits for the input: a global
+// load issued after the wait would put a full memory round trip on the critical path of every layer.  `ok` is this
+// thread's verdict on the waits that produced `u`; the first barrier both publishes the per-warp sums of squares and
+// collects the verdicts.  Returns false (uniformly) when any thread's wait failed.
+// With `ring_entry` non-null the wait for this phase's weights in the ring is folded in: its verdict rides on the barrier
+// that publishes xs, instead of costing a barrier of its own.
 template <int NB>
-__device__ __forceinline__ void norm_rows_smem(Cta& c, const bf16* gain) {
-    for (int b = c.warp; b < NB; b += kWarps) {
-        uint32_t* row = c.xs + b * (FF / 2);
-        uint4 gq[4];
-        float xr[32];
-        load_gains(gain, c.lane, gq);
-        load_xreg_norm(row, gq, c.p.eps, c.lane, xr);
+__device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[NB], uint32_t gw, bool ok,
+                                                   const bf16** ring_entry = nullptr) {
+    static_assert(kThreads * 2 == D, "one bf16 pair per thread");
+    static_assert(NB * kWarps <= 32 * 4, "per-warp partial sums must fit the scratch");
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            *reinterpret_cast<uint4*>(row + (c.lane + 32 * i) * 4) =
-                make_uint4(pack_bf16x2(xr[i * 8], xr[i * 8 + 1]), pack_bf16x2(xr[i * 8 + 2], xr[i * 8 + 3]),
-                           pack_bf16x2(xr[i * 8 + 4], xr[i * 8 + 5]), pack_bf16x2(xr[i * 8 + 6], xr[i * 8 + 7]));
+    for (int b = 0; b < NB; ++b) {
+        const float x0 = bf_lo(u[b]), x1 = bf_hi(u[b]);
+        const float v = warp_sum(x0 * x0 + x1 * x1);
+        if (c.lane == 0) c.hdr->red[b * kWarps + c.warp] = v;
+    }
+    if (cta_or(!ok)) return false;
+    c.t_ready = clock64();
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < kWarps; ++i) tot += c.hdr->red[b * kWarps + i];
+        const float rstd = 1.0f / sqrtf(tot * (1.0f / D) + c.p.eps);
+        c.xs[b * (FF / 2) + c.tid] = pack_bf16x2(bf16r(bf_lo(u[b]) * rstd) * bf_lo(gw), bf16r(bf_hi(u[b]) * rstd) * bf_hi(gw));
+    }
+    if (ring_entry != nullptr) {
+        const unsigned char* ptr = stream_wait(c.st, c.st.consumed, c.w);
+        *ring_entry = reinterpret_cast<const bf16*>(ptr);
+        return !cta_or(ptr == nullptr);
     }
     cta_sync();
+    return true;
 }
 
-// ---- sub-row dot products ------------------------------------------------------------------------------
-// R rows of 1024 columns against the lane's 32 activations: four independent 128-bit accesses per row.
-template <int R>
-__device__ __forceinline__ void dot_rows_xreg(const bf16* const (&wp)[R], const float (&xr)[32], int lane, float (&acc)[R]) {
+// Waits for NB rows of K bf16 values in 128-bit flagged words and spreads them into xs: K = 2048 (attention output) has
+// four values per word, K = 3072 (SwiGLU output) six, so every thread polls exactly one word per row.
+template <int NB, int K>
+__device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, uint32_t tag, int what, const bf16** ring_entry = nullptr) {
+    constexpr int V = K / kThreads;              // values per word
+    static_assert(V == 4 || V == 6, "one 128-bit word per thread");
+    bool ok = true;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        uint32_t u0 = 0, u1 = 0, u2 = 0;
+        ok = ok && wait_word128(c.w, reinterpret_cast<const uint4*>(src) + (size_t)b * kThreads + c.tid, tag, u0, u1, u2, what);
+        uint32_t* dst = c.xs + b * (FF / 2) + c.tid * (V / 2);
+        dst[0] = u0; dst[1] = u1;
+        if constexpr (V == 6) dst[2] = u2;
+    }
+    if (ring_entry != nullptr) {
+        const unsigned char* ptr = stream_wait(c.st, c.st.consumed, c.w);
+        *ring_entry = reinterpret_cast<const bf16*>(ptr);
+        ok = ok && ptr != nullptr;
+    }
+    return all_ok(ok);
+}
+
+// ---- 1024-column sub-row dot products ------------------------------------------------------------------
+// Lane owns the 16-byte chunks lane, lane+32, lane+64, lane+96 of a sub-row: four independent 128-bit accesses per
+// sub-row, R sub-rows at a time.  Batch 1 keeps its 32 activations in registers; larger batches read shared memory.
+// GLOBAL selects streaming global loads (the head's table) over the shared-memory ring.
+template <bool GLOBAL>
+__device__ __forceinline__ uint4 load_w(const bf16* p) {
+    if constexpr (GLOBAL) return ldg_stream(p);
+    else return *reinterpret_cast<const uint4*>(p);
+}
+
+__device__ __forceinline__ void load_xreg(const uint32_t* xs, int lane, float (&xr)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint4 q = *reinterpret_cast<const uint4*>(xs + (lane + 32 * i) * 4);
+        xr[i * 8 + 0] = bf_lo(q.x); xr[i * 8 + 1] = bf_hi(q.x); xr[i * 8 + 2] = bf_lo(q.y); xr[i * 8 + 3] = bf_hi(q.y);
+        xr[i * 8 + 4] = bf_lo(q.z); xr[i * 8 + 5] = bf_hi(q.z); xr[i * 8 + 6] = bf_lo(q.w); xr[i * 8 + 7] = bf_hi(q.w);
+    }
+}
+
+template <bool GLOBAL, int R>
+__device__ __forceinline__ void dot_subrows_xreg(const bf16* const (&wp)[R], const float (&xr)[32], int lane,
+                                                 float (&acc)[R]) {
     uint4 w[R][4];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) w[r][i] = *reinterpret_cast<const uint4*>(wp[r] + (lane + 32 * i) * 8);
+        for (int i = 0; i < 4; ++i) w[r][i] = load_w<GLOBAL>(wp[r] + (lane + 32 * i) * 8);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         float a[4];
@@ -321,26 +309,46 @@ __device__ __forceinline__ void dot_rows_xreg(const bf16* const (&wp)[R], const 
         acc[r] = warp_sum((a[0] + a[1]) + (a[2] + a[3]));
     }
 }
-// One sub-row of CH * 256 columns against activations in shared memory (packed bf16 pairs).
-template <int CH>
-__device__ __forceinline__ float dot_subrow_smem(const bf16* w, const uint32_t* x, int lane) {
-    uint4 wv[CH], xv[CH];
+
+// xseg points at the 1024-value segment (512 words) this sub-row multiplies, for batch row 0; batch rows are FF/2 words apart.
+template <bool GLOBAL, int NB, int R>
+__device__ __forceinline__ void dot_subrows_smem(const bf16* const (&wp)[R], const uint32_t* const (&xseg)[R], int lane,
+                                                 float (&acc)[R][NB]) {
+    uint4 w[R][4];
 #pragma unroll
-    for (int i = 0; i < CH; ++i) {
-        wv[i] = *reinterpret_cast<const uint4*>(w + (lane + 32 * i) * 8);
-        xv[i] = *reinterpret_cast<const uint4*>(x + (lane + 32 * i) * 4);
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[r][i] = load_w<GLOBAL>(wp[r] + (lane + 32 * i) * 8);
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 q = *reinterpret_cast<const uint4*>(xseg[r] + b * (FF / 2) + (lane + 32 * i) * 4);
+                const float xv[8] = {bf_lo(q.x), bf_hi(q.x), bf_lo(q.y), bf_hi(q.y), bf_lo(q.z), bf_hi(q.z), bf_lo(q.w), bf_hi(q.w)};
+                a = dot8(w[r][i], xv, a);
+            }
+            acc[r][b] = warp_sum(a);
+        }
+}
+
+// Generic "R sub-rows" step used by all K=1024 phases.
+template <bool GLOBAL, int NB, int R>
+__device__ __forceinline__ void dot_rows_k1024(Cta& c, const bf16* const (&wp)[R], const float (&xr)[32],
+                                               float (&acc)[R][NB]) {
+    if constexpr (NB == 1) {
+        float a[R];
+        dot_subrows_xreg<GLOBAL, R>(wp, xr, c.lane, a);
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r][0] = a[r];
+    } else {
+        const uint32_t* xseg[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) xseg[r] = c.xs;
+        dot_subrows_smem<GLOBAL, NB, R>(wp, xseg, c.lane, acc);
     }
-    float a[CH];
-#pragma unroll
-    for (int i = 0; i < CH; ++i) {
-        float xf[8];
-        unpack8(xv[i], xf);
-        a[i] = dot8(wv[i], xf, 0.f);
-    }
-    float s = a[0];
-#pragma unroll
-    for (int i = 1; i < CH; ++i) s += a[i];
-    return warp_sum(s);
 }
 
 // ---- GEMV tiles on the tensor cores --------------------------------------------------------------------
@@ -400,51 +408,47 @@ __device__ __forceinline__ float gemv_sum(const float* part, int row, int b) {
 }
 
 // ---- phase: embed gather (layer 0) + RMSNorm + QKV GEMV ------------------------------------------------
-// This CTA's rows are whole quads (four consecutive outputs, which never straddle a head); a quad travels as one word
-// to every CTA whose attention item belongs to the quad's kv head.
 template <int NB>
 __device__ bool phase_qkv(Cta& c, int l) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t tag = tag_of(c, c.step, l);
-    const bf16* gain = reinterpret_cast<const bf16*>(p.ln1) + (size_t)l * D;
-    uint4 gq[4];
-    if constexpr (NB == 1) load_gains(gain, c.lane, gq);
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.ln1) + (size_t)l * D + 2 * c.tid);
+    uint32_t u[NB];
     bool ok = true;
-    if (l == 0) {
-        for (int i = c.tid; i < NB * (D / 2); i += kThreads) {
-            const int b = i / (D / 2), t = i - b * (D / 2);
-            c.xs[b * (FF / 2) + t] = ldcg32(reinterpret_cast<const bf16*>(p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * t);
-        }
-    } else {
-        ok = gather7<NB, Q3_ROW_WORDS>(c, c.ws.mail_h + (size_t)c.cta * NB * MS, D, tag, ITTAI_PH_QKV, reinterpret_cast<uint16_t*>(c.xs));
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        if (l == 0) u[b] = ldcg32(reinterpret_cast<const bf16*>(p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * c.tid);
+        else ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_QKV);
     }
-    int r0, r1;
-    qkv_rows(c.ncta, c.cta, r0, r1);
-    const bf16* W = nullptr;                                   // this CTA's rows [r0, r1), contiguous in the ring
-    if (r1 > r0) {
-        W = reinterpret_cast<const bf16*>(stream_wait(c.st, c.st.consumed, c.w));
-        ok = ok && W != nullptr;
-    }
-    if (!all_ok(ok)) return false;
-    c.t_ready = clock64();
-    if constexpr (NB > 1) norm_rows_smem<NB>(c, gain);
-    if (r1 == r0) return true;
-    const int n_rows = r1 - r0;
-    uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->pub);      // packed output pairs, [sequence][kPubHalves / 2]
+    int p0, p1;
+    split_range(DQKV / 4, c.ncta, c.cta, p0, p1);    // 128-bit words: two row pairs (four outputs) each
+    p0 *= 2; p1 *= 2;
+    const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok, p1 > p0 ? &W : nullptr)) return false;
+    if (p1 == p0) return true;
     if constexpr (NB == 1) {
         // one sequence: a row pair per warp on the fp32 pipes (the tensor-core tiles below are no faster here)
         float xr[32];
-        load_xreg_norm(c.xs, gq, p.eps, c.lane, xr);
-        for (int pr = c.warp; 2 * pr < n_rows; pr += kWarps) {
-            const bf16* wp[2] = {W + (size_t)(2 * pr) * D, W + (size_t)(2 * pr + 1) * D};
-            float acc[2];
-            dot_rows_xreg<2>(wp, xr, c.lane, acc);
-            if (c.lane == 0) pub[pr] = pack_bf16x2(acc[0], acc[1]);
+        if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
+        uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [row pair][sequence]
+        for (int pr = p0 + c.warp; pr < p1; pr += kWarps) {
+            const bf16* wp[2] = {W + (size_t)(2 * (pr - p0)) * D, W + (size_t)(2 * (pr - p0) + 1) * D};
+            float acc[2][NB];
+            dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
+            if (c.lane == 0) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b) pub[(pr - p0) * NB + b] = pack_bf16x2(acc[0][b], acc[1][b]);
+            }
         }
         stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
+        for (int i = c.tid; i < (p1 - p0) / 2 * NB; i += kThreads) {
+            const int wq = i / NB, b = i % NB;
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4) + p0 / 2 + wq,
+                          pub[(2 * wq) * NB + b], pub[(2 * wq + 1) * NB + b], 0u, tag);
+        }
     } else {
         // tiles of 16 rows x 256 columns over the warps; the four column blocks of a row meet in shared memory
-        const int n_tasks = (n_rows + 15) / 16 * 4;
+        const int n_rows = 2 * (p1 - p0), n_tasks = (n_rows + 15) / 16 * 4;
         float* part = c.hdr->sub;
         for (int task = c.warp; task < n_tasks; task += kWarps) {
             float d[4];
@@ -452,21 +456,13 @@ __device__ bool phase_qkv(Cta& c, int l) {
             gemv_store<NB>(part, task, c.lane, d);
         }
         stream_release(c.st, 1);                         // its barrier also publishes `part` to the CTA
-        for (int i = c.tid; i < n_rows / 2 * NB; i += kThreads) {
-            const int b = i / (n_rows / 2), pr = i - b * (n_rows / 2);
-            pub[b * (kPubHalves / 2) + pr] = pack_bf16x2(gemv_sum<NB, 4>(part, 2 * pr, b), gemv_sum<NB, 4>(part, 2 * pr + 1, b));
+        for (int i = c.tid; i < (p1 - p0) / 2 * NB; i += kThreads) {     // four rows leave as one 128-bit word
+            const int wq = i / NB, b = i % NB;
+            const float r0 = gemv_sum<NB, 4>(part, 4 * wq, b), r1 = gemv_sum<NB, 4>(part, 4 * wq + 1, b);
+            const float r2 = gemv_sum<NB, 4>(part, 4 * wq + 2, b), r3 = gemv_sum<NB, 4>(part, 4 * wq + 3, b);
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4) + p0 / 2 + wq,
+                          pack_bf16x2(r0, r1), pack_bf16x2(r2, r3), 0u, tag);
         }
-        cta_sync();
-    }
-    // quad q of sequence b -> the n_splits CTAs of (b, kv head of the quad)
-    const int n_splits = q3_attn_splits(c.ncta, p.batch), n_quads = n_rows / 4;
-    for (int i = c.tid; i < n_quads * n_splits * NB; i += kThreads) {
-        const int s = i % n_splits, r = i / n_splits, qi = r % n_quads, b = r / n_quads;
-        const int q = r0 / 4 + qi, head = q >> 5;                  // 32 quads per head; heads: 16 q | 8 k | 8 v
-        const int g = head < 16 ? head >> 1 : (head - 16) & 7, which = head < 16 ? head & 1 : (head < 24 ? 2 : 3);
-        const int dst = (b * NKV + g) * n_splits + s;
-        st_mail(c.ws.mail_qkv + (size_t)dst * Q3_QKV_WORDS + which * 32 + (q & 31),
-                pub[b * (kPubHalves / 2) + 2 * qi], pub[b * (kPubHalves / 2) + 2 * qi + 1], 0u, 0u, tag);
     }
     return true;
 }
@@ -483,41 +479,40 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // Work item = (sequence b, kv head g, split s) = CTA index.  Scores live in the log2 domain with the softmax scale
 // folded into q, as the reference does (src/ittai/qwen3/config.py:6-7).  Old cache rows arrive through the ring in tiles
 // of 128 positions (a K entry and a V entry per tile); the row of the token being computed is taken from shared memory
-// and appended to the cache by the split that owns its position.  Each split mails (m, l, o-slice) to the first `nc`
-// splits of its head, which each merge a slice of the 256 outputs and mail it to every CTA.
+// and appended to the cache by the split that owns its position.  Each split publishes (m, l, o[2][128]); the first
+// `nc` splits of a head then each merge a slice of the 256 outputs.
 __device__ bool phase_attn(Cta& c, int l) {
     const IttaiQwen3Decode& p = c.p;
     const int B = p.batch;
-    const int n_splits = q3_attn_splits(c.ncta, B), nc = q3_merge_ctas(n_splits), dpc = HD / nc;
-    const int MW = q3_part_words_per_msg(nc), WPO = q3_attn_words_per_owner(nc);
+    const int n_splits = attn_splits(c.ncta, B);
     const uint32_t tag = tag_of(c, c.step, l);
     SmemAttn* at = c.at;
     const AttnItem it = attn_item(c, c.step);
-    if (!it.active) { c.t_ready = clock64(); return true; }
-    const int b = it.b, g = it.g, pos = it.pos;
-    {
+    if (it.active) {
+        const int b = it.b, g = it.g, pos = it.pos;
         const bool has_new = it.has_new;
         const size_t head_off = ((((size_t)l * B + b) * NKV + g) * (size_t)p.kv_cap) * HD;
         bf16* kc = reinterpret_cast<bf16*>(p.kcache) + head_off;
         bf16* vc = reinterpret_cast<bf16*>(p.vcache) + head_off;
 
         // -- norm + rotate q (warps 0,1) and the new key (warp 2); copy the new value (warp 3).
-        //    A head's row arrives as 32 words of four values: a lane owns elements 4*lane .. 4*lane+3, and the rotation
+        //    The row arrives as 32 words of four values: a lane owns elements 4*lane .. 4*lane+3, and the rotation
         //    partner (element +-64) of each sits in lane ^ 16.  Gains and the rotary row are fetched before the wait, so
         //    their latency hides behind it.
-        const uint4* qw = c.ws.mail_qkv + (size_t)c.cta * Q3_QKV_WORDS;
+        const uint4* qw = reinterpret_cast<const uint4*>(c.ws.qkv) + (size_t)b * (DQKV / 4);
         bool ok = true;
         if (c.warp < 3 && (c.warp < 2 || has_new)) {
             const bool is_k = c.warp == 2;
+            const int e0 = is_k ? DQ + g * HD : (2 * g + c.warp) * HD;
             const bf16* gain = reinterpret_cast<const bf16*>(is_k ? p.kn : p.qn) + (size_t)l * HD;
             const bf16* rp = reinterpret_cast<const bf16*>(p.rope) + (size_t)pos * HD;
             const int hi_half = c.lane >> 4, ei = 4 * (c.lane & 15);        // rotation index of this lane's first element
             const uint2 gq = *reinterpret_cast<const uint2*>(gain + 4 * c.lane);
             const uint2 cq = *reinterpret_cast<const uint2*>(rp + ei);
             const uint2 sq = *reinterpret_cast<const uint2*>(rp + HD / 2 + ei);
-            uint32_t u[4] = {0, 0, 0, 0};
-            ok = wait_mail(c.w, qw + c.warp * 32 + c.lane, tag, u, ITTAI_PH_ATTN);
-            float x[4] = {bf_lo(u[0]), bf_hi(u[0]), bf_lo(u[1]), bf_hi(u[1])};
+            uint32_t ua = 0, ub = 0, uc = 0;
+            ok = wait_word128(c.w, qw + e0 / 4 + c.lane, tag, ua, ub, uc, ITTAI_PH_ATTN);
+            float x[4] = {bf_lo(ua), bf_hi(ua), bf_lo(ub), bf_hi(ub)};
             const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
             const float rstd = 1.0f / sqrtf(ss * (1.0f / HD) + p.eps);
             const float gn[4] = {bf_lo(gq.x), bf_hi(gq.x), bf_lo(gq.y), bf_hi(gq.y)};
@@ -544,11 +539,12 @@ __device__ bool phase_attn(Cta& c, int l) {
                 *reinterpret_cast<float4*>(&at->qs[c.warp][4 * c.lane]) = make_float4(r[0] * qscale, r[1] * qscale, r[2] * qscale, r[3] * qscale);
             }
         } else if (c.warp == 3 && has_new) {
-            uint32_t u[4] = {0, 0, 0, 0};
-            ok = wait_mail(c.w, qw + 3 * 32 + c.lane, tag, u, ITTAI_PH_ATTN);
-            *reinterpret_cast<uint2*>(at->vnew + 4 * c.lane) = make_uint2(u[0], u[1]);
+            const int e0 = DQ + DKV + g * HD;
+            uint32_t ua = 0, ub = 0, uc = 0;
+            ok = wait_word128(c.w, qw + e0 / 4 + c.lane, tag, ua, ub, uc, ITTAI_PH_ATTN);
+            *reinterpret_cast<uint2*>(at->vnew + 4 * c.lane) = make_uint2(ua, ub);
             if (ok) {
-                *reinterpret_cast<uint2*>(vc + (size_t)pos * HD + 4 * c.lane) = make_uint2(u[0], u[1]);
+                *reinterpret_cast<uint2*>(vc + (size_t)pos * HD + 4 * c.lane) = make_uint2(ua, ub);
                 __threadfence();
                 fence_proxy_async();
             }
@@ -641,7 +637,8 @@ __device__ bool phase_attn(Cta& c, int l) {
             // per 128 KB instead of two per tile), which is everything at batch 1
             if (from_ring && j - rel == hold - 1) { stream_release(c.st, 2 * hold); rel += hold; }
         }
-        // -- merge the two halves of each warp, then the 16 warps: (m, l, o) of this split
+        if (n_ring_tiles > rel) stream_release(c.st, 2 * (n_ring_tiles - rel));
+        // -- merge the two halves of each warp, then the 16 warps, and publish (m, l, o) of this split
         {
             const float pm0 = __shfl_xor_sync(0xffffffffu, m0, 16), pm1 = __shfl_xor_sync(0xffffffffu, m1, 16);
             const float pl0 = __shfl_xor_sync(0xffffffffu, l0, 16), pl1 = __shfl_xor_sync(0xffffffffu, l1, 16);
@@ -663,9 +660,8 @@ __device__ bool phase_attn(Cta& c, int l) {
                 }
             }
         }
-        // this barrier publishes the per-warp partials, collects the ring verdicts and hands the last tiles back
         if (cta_or(!okr)) return false;
-        if (n_ring_tiles > rel) stream_release_synced(c.st, 2 * (n_ring_tiles - rel));
+        uint64_t* part = c.ws.part + (size_t)c.cta * Q3_PART_WORDS;
         if (c.tid < 2 * HD) {
             const int h = c.tid / HD, d = c.tid % HD;
             float M = -INFINITY;
@@ -679,156 +675,159 @@ __device__ bool phase_attn(Cta& c, int l) {
                 o = fmaf(at->ored[w][h][d], sc, o);
                 ls = fmaf(at->wl[w][h], sc, ls);
             }
-            at->msg[4 + h * HD + d] = o;
-            if (d == 0) { at->msg[h] = M; at->msg[2 + h] = ls; }
+            st_flagged(part + 4 + h * HD + d, __float_as_uint(o), tag);
+            if (d == 0) {
+                st_flagged(part + h, __float_as_uint(M), tag);
+                st_flagged(part + 2 + h, __float_as_uint(ls), tag);
+            }
         }
         cta_sync();
-        // -- mail the partial: owner j gets m[2], l[2] and its dpc dims of both heads, three floats per word
-        for (int i = c.tid; i < nc * MW; i += kThreads) {
-            const int j = i / MW, w = i - j * MW;
-            float f[3];
-#pragma unroll
-            for (int e = 0; e < 3; ++e) {
-                const int k = 3 * w + e, v = k - 4;
-                f[e] = k < 4 ? at->msg[k] : (v < 2 * dpc ? at->msg[4 + (v / dpc) * HD + j * dpc + v % dpc] : 0.f);
-            }
-            const int owner = (b * NKV + g) * n_splits + j;
-            st_mail(c.ws.mail_part + (size_t)owner * Q3_PART_WORDS + it.s * MW + w,
-                    __float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), 0u, tag);
-        }
+    } else {
+        c.t_ready = clock64();
     }
     // -- merge across splits: split s < nc of each (b, g) gathers, from every split of that head, the running max and
     //    sum and its own slice of the outputs
-    if (it.s < nc) {
-        float* pm = &at->ored[0][0][0];              // [split][3 * MW]: the messages as sent (all threads are past their reads of ored)
+    int nc = 1;
+    while (nc * 2 <= n_splits && nc < 16) nc *= 2;
+    const int dpc = HD / nc, W = 4 + 2 * dpc;
+    if (it.active && it.s < nc) {
+        // a warp per pair of adjacent outputs, lanes = splits: each lane fetches (m, l, o, o) of its split in one round
+        // trip, then three warp reductions finish the pair
+        const int b = it.b, g = it.g, d0 = it.s * dpc;
+        const uint64_t* base = c.ws.part + (size_t)(b * NKV + g) * n_splits * Q3_PART_WORDS;
         bool ok = true;
-        for (int i = c.tid; i < n_splits * MW; i += kThreads) {
-            uint32_t v[4];
-            if (!wait_mail(c.w, c.ws.mail_part + (size_t)c.cta * Q3_PART_WORDS + i, tag, v, 16 + ITTAI_PH_ATTN)) { ok = false; break; }
-            pm[3 * i] = __uint_as_float(v[0]); pm[3 * i + 1] = __uint_as_float(v[1]); pm[3 * i + 2] = __uint_as_float(v[2]);
-        }
-        if (!all_ok(ok)) return false;
-        // a warp per output, lanes = splits: three warp reductions finish it
-        uint16_t* pub = c.hdr->pub;
-        for (int v = c.warp; v < 2 * dpc; v += kWarps) {
-            const int h = v / dpc;
-            float m = -INFINITY, ls = 0.f, o = 0.f;
+        for (int pr = c.warp; pr < dpc; pr += kWarps) {
+            const int h = pr / (dpc / 2), dd = (pr % (dpc / 2)) * 2;
+            float m = -INFINITY, l = 0.f, o0 = 0.f, o1 = 0.f;
             if (c.lane < n_splits) {
-                const float* ms = pm + c.lane * 3 * MW;
-                m = ms[h]; ls = ms[2 + h]; o = ms[4 + v];
+                const uint64_t* pk = base + (size_t)c.lane * Q3_PART_WORDS;
+                const uint64_t* w4[4] = {pk + h, pk + 2 + h, pk + 4 + h * HD + d0 + dd, pk + 4 + h * HD + d0 + dd + 1};
+                uint32_t spins = 0;
+                for (;;) {
+                    const uint64_t v0 = ld_flagged(w4[0]), v1 = ld_flagged(w4[1]), v2 = ld_flagged(w4[2]), v3 = ld_flagged(w4[3]);
+                    if ((uint32_t)(v0 >> 32) == tag && (uint32_t)(v1 >> 32) == tag && (uint32_t)(v2 >> 32) == tag && (uint32_t)(v3 >> 32) == tag) {
+                        m = __uint_as_float((uint32_t)v0); l = __uint_as_float((uint32_t)v1);
+                        o0 = __uint_as_float((uint32_t)v2); o1 = __uint_as_float((uint32_t)v3);
+                        break;
+                    }
+                    if (((++spins) & 1023u) == 0u &&
+                        !keep_waiting(c.w.sync, c.w.status, c.w.limit, spins, 16 + ITTAI_PH_ATTN, (uint32_t)(v0 >> 32), tag)) { ok = false; break; }
+                }
             }
             const float M = warp_max(m);
             const float wk = ex2_approx(m - (M == -INFINITY ? 0.f : M));
-            const float Ls = warp_sum(ls * wk), O = warp_sum(o * wk);
-            if (c.lane == 0) pub[v] = __bfloat16_as_ushort(__float2bfloat16_rn(O / Ls));
+            const float Ls = warp_sum(l * wk), O0 = warp_sum(o0 * wk), O1 = warp_sum(o1 * wk);
+            if (c.lane == 0) at->pub[pr] = pack_bf16x2(O0 / Ls, O1 / Ls);
         }
-        cta_sync();
-        // the slice leaves as WPO words of seven values to every CTA
-        for (int i = c.tid; i < c.ncta * WPO; i += kThreads) {
-            const int dst = i / WPO, k = i - dst * WPO;
-            send7(c.ws.mail_attn + (((size_t)dst * B + b) * NKV + g) * Q3_ATTN_WORDS + it.s * WPO + k, pub + 7 * k, 2 * dpc - 7 * k, tag);
-        }
-    }
-    return true;
-}
-
-// Collects the attention output of every (sequence, kv head) from this CTA's mailbox into xs[b][2048].
-template <int NB>
-__device__ __forceinline__ bool gather_attn(Cta& c, uint32_t tag) {
-    const int n_splits = q3_attn_splits(c.ncta, c.p.batch), nc = q3_merge_ctas(n_splits), dpc = HD / nc;
-    const int WPO = q3_attn_words_per_owner(nc), per = nc * WPO;
-    uint16_t* dst = reinterpret_cast<uint16_t*>(c.xs);
-    const uint4* mail = c.ws.mail_attn + (size_t)c.cta * NB * NKV * Q3_ATTN_WORDS;
-    for (int i = c.tid; i < NB * NKV * per; i += kThreads) {
-        const int bg = i / per, r = i - bg * per, j = r / WPO, k = r - j * WPO;
-        const int b = bg / NKV, g = bg - b * NKV;
-        uint32_t v[4];
-        if (!wait_mail(c.w, mail + (size_t)bg * Q3_ATTN_WORDS + r, tag, v, ITTAI_PH_OPROJ)) return false;
-#pragma unroll
-        for (int e = 0; e < 7; ++e) {
-            const int x = 7 * k + e;                 // index into the owner's 2 * dpc values: head-major
-            if (x < 2 * dpc) dst[b * FF + (2 * g + x / dpc) * HD + j * dpc + x % dpc] = (uint16_t)(v[e >> 1] >> ((e & 1) * 16));
+        if (!all_ok(ok)) return false;
+        // two adjacent pairs (four outputs of one head) leave as one 128-bit word
+        if (c.tid < dpc / 2) {
+            const int h = c.tid / (dpc / 4), k4 = c.tid % (dpc / 4);
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.attn) + (size_t)b * (DQ / 4) + ((2 * g + h) * HD + d0) / 4 + k4,
+                          at->pub[2 * c.tid], at->pub[2 * c.tid + 1], 0u, tag);
         }
     }
     return true;
 }
 
 // ---- phases: O-proj + residual, down-proj + residual ---------------------------------------------------
-// K is 2048 or 3072: each of this CTA's six or seven rows is cut into two sub-rows, one per warp; the two partial sums
-// meet in shared memory.  out = bf16(resid + bf16(W x)) (reference base.py:110-123).  The residual rows are the ones
-// this CTA produced itself one phase pair earlier; they come back from its own mailbox (`res_mail` == nullptr takes
-// them from the embedding row: layer 0's o_proj).  The result leaves as one word per sequence to every CTA.
-enum { kFromAttn = 0, kFromAct = 1 };
-template <int NB, int K, int SRC>
-__device__ bool phase_proj_residual(Cta& c, int what, int l, uint32_t x_tag, const uint4* res_mail, uint32_t res_tag,
-                                    uint4* dst_mail, uint32_t dst_tag) {
-    constexpr int CH = K / 512;              // 16-byte chunks per lane of a half row (K / 2 columns)
-    int r0, r1;
-    res_rows(c.ncta, c.cta, r0, r1);
-    const int n_rows = r1 - r0;
-    // The residual rows were published phases ago: fetch them now, not after the GEMV.
+// K is 2048 or 3072: rows are cut into 1024-column sub-rows spread over the warps, partial sums meet in shared
+// memory and are added in a fixed order.  out = bf16(resid + bf16(W x)) (reference base.py:110-123).
+// `res_src` == nullptr takes the residual from the embedding row (layer 0's o_proj).
+template <int NB, int K>
+__device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uint32_t x_tag, const uint64_t* res_src,
+                                    uint32_t res_tag, uint64_t* dst, uint32_t dst_tag, uint32_t epoch) {
+    constexpr int S = K / 1024;
+    constexpr int kSlots = 60;               // sub-rows finished per pass: a multiple of 4 and of 6, so row pairs stay whole
+    int p0, p1;
+    split_range(D / 2, c.ncta, c.cta, p0, p1);
+    // The residual rows this CTA owns were published phases ago: fetch them now, not after the GEMV.
     bool ok = true;
-    if (c.tid < NB) {
-        const int b = c.tid;
-        uint16_t* res = c.hdr->res + b * 8;
-        if (res_mail == nullptr) {
-            for (int e = 0; e < n_rows; ++e)
-                res[e] = __bfloat16_as_ushort(reinterpret_cast<const bf16*>(c.p.embed)[(size_t)c.hdr->tok_s[b] * D + r0 + e]);
-        } else {
-            uint32_t v[4] = {0, 0, 0, 0};
-            ok = wait_mail(c.w, res_mail + ((size_t)c.cta * NB + b) * MS + c.cta, res_tag, v, 32 + what);
-            unpack7(v, res, n_rows);
-        }
+    uint32_t rw_early = 0;
+    const int early_pairs = (2 * (p1 - p0) * S < kSlots ? 2 * (p1 - p0) * S : kSlots) / (2 * S);
+    if (c.tid < early_pairs * NB) {
+        const int pair = p0 + c.tid / NB, b = c.tid % NB;
+        if (res_src == nullptr)
+            rw_early = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
+        else
+            ok = wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw_early, 32 + what);
     }
-    if constexpr (SRC == kFromAttn) ok = gather_attn<NB>(c, x_tag) && ok;
-    else ok = gather7<NB, Q3_ACT_WORDS>(c, c.ws.mail_act + (size_t)c.cta * NB * MS * Q3_ACT_WORDS, FF, x_tag, what, reinterpret_cast<uint16_t*>(c.xs)) && ok;
-    const bf16* W = nullptr;                                   // this CTA's rows [r0, r1), contiguous in the ring
-    if (n_rows > 0) {
-        W = reinterpret_cast<const bf16*>(stream_wait(c.st, c.st.consumed, c.w));
-        ok = ok && W != nullptr;
-    }
-    if (!all_ok(ok)) return false;
+    const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
+    if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what, p1 > p0 ? &W : nullptr)) return false;
     c.t_ready = clock64();
-    // every cache row appended up to (step, l) is ordered before what this CTA has now seen: the feeding lane may
-    // fetch the tiles of (step + 1, l)
-    if (SRC == kFromAttn && c.tid == 0) c.st.sh->kv_epoch = (uint32_t)(c.step * c.p.n_layers + l) + 1u;
-    if (n_rows == 0) return true;
-    float* sub = c.hdr->sub;
-    if constexpr (NB == 1) {
-        for (int t = c.warp; t < 2 * n_rows; t += kWarps) {
-            const int row = t >> 1, half = t & 1;
-            const float s = dot_subrow_smem<CH>(W + (size_t)row * K + half * (K / 2), c.xs + half * (K / 4), c.lane);
-            if (c.lane == 0) sub[t] = s;
-        }
-    } else {
+    if (what == ITTAI_PH_OPROJ && c.tid == kThreads - 1) {
+        // The whole attention output of (step, layer) is here, so every cache row appended up to (step, layer) is in
+        // place: the feeding lane may fetch the tiles of (step + 1, layer).  The fence makes what this CTA's threads
+        // observed before the barrier above an acquire of the appending CTAs' fenced stores (13 us per token of a
+        // 256-token run on a B200; the same fence pair executed by the feeding lane itself, with its bulk copies in
+        // flight, cost 210 us).
+        asm volatile("fence.acq_rel.gpu;" ::: "memory");
+        st_release_cta(&c.st.sh->kv_epoch, epoch);
+    }
+    if (p1 == p0) return all_ok(ok);
+    if constexpr (NB > 1) {
         // several sequences: tiles of up to 16 rows x 256 columns on the tensor cores, one column block per warp
         constexpr int NK = K / 256;
+        const int n_rows = 2 * (p1 - p0);            // at most 16: the launch requires 128 CTAs or more
+        float* part = c.hdr->sub;
         for (int task = c.warp; task < NK; task += kWarps) {
             float d[4];
             gemv_tile<NB>(W, K, 0, n_rows, c.xs, task * 256, c.lane, d);
-            gemv_store<NB>(sub, task, c.lane, d);
+            gemv_store<NB>(part, task, c.lane, d);
         }
-    }
-    cta_sync();
-    stream_release_synced(c.st, 1);
-    // every sending thread finishes the CTA's rows of its sequence itself (a dozen additions) and mails one word
-    for (int i = c.tid; i < c.ncta * NB; i += kThreads) {
-        const int dst = i / NB, b = i - dst * NB;
-        const uint16_t* res = c.hdr->res + b * 8;
-        uint32_t h[7];
-#pragma unroll
-        for (int e = 0; e < 7; ++e) {
-            float s = 0.f;
-            if (e < n_rows) {
-                if constexpr (NB == 1) s = sub[2 * e] + sub[2 * e + 1];
-                else s = gemv_sum<NB, K / 256>(sub, e, b);
+        cta_sync();
+        for (int i = c.tid; i < (p1 - p0) * NB; i += kThreads) {
+            const int pp = i / NB, b = i % NB, pair = p0 + pp;
+            const float s0 = gemv_sum<NB, NK>(part, 2 * pp, b), s1 = gemv_sum<NB, NK>(part, 2 * pp + 1, b);
+            uint32_t rw = rw_early;
+            if (i != c.tid || i >= early_pairs * NB) {
+                if (res_src == nullptr)
+                    rw = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
+                else
+                    ok = ok && wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw, 32 + what);
             }
-            const float y = __uint_as_float((uint32_t)res[e] << 16) + bf16r(s);
-            h[e] = e < n_rows ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(y)) : 0u;
+            st_flagged(dst + (size_t)b * (D / 2) + pair, pack_bf16x2(bf_lo(rw) + bf16r(s0), bf_hi(rw) + bf16r(s1)), dst_tag);
         }
-        st_mail(dst_mail + ((size_t)dst * NB + b) * MS + c.cta, h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6], dst_tag);
+        stream_release(c.st, 1);
+        return all_ok(ok);
     }
-    return true;
+    const int n_sub = 2 * (p1 - p0) * S;
+    float* sub = c.hdr->sub;
+    for (int base = 0; base < n_sub; base += kSlots) {
+        const int cnt = n_sub - base < kSlots ? n_sub - base : kSlots;
+        for (int sr = c.warp; sr < cnt; sr += kWarps) {
+            const int gsr = base + sr;
+            const int seg = gsr % S;
+            const bf16* wp[1] = {W + (size_t)gsr * 1024};
+            const uint32_t* xseg[1] = {c.xs + seg * 512};
+            float acc[1][NB];
+            dot_subrows_smem<false, NB, 1>(wp, xseg, c.lane, acc);
+            if (c.lane == 0) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b) sub[sr * NB + b] = acc[0][b];
+            }
+        }
+        cta_sync();
+        const int pairs_here = cnt / (2 * S);
+        for (int i = c.tid; i < pairs_here * NB; i += kThreads) {
+            const int pp = i / NB, b = i % NB;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int k = 0; k < S; ++k) { s0 += sub[((2 * pp) * S + k) * NB + b]; s1 += sub[((2 * pp + 1) * S + k) * NB + b]; }
+            const int pair = p0 + base / (2 * S) + pp;
+            uint32_t rw = rw_early;
+            if (base != 0 || i != c.tid) {       // only reached with fewer CTAs than a B200 has
+                if (res_src == nullptr)
+                    rw = ldcg32(reinterpret_cast<const bf16*>(c.p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * pair);
+                else
+                    ok = ok && wait_word(c.w, res_src + (size_t)b * (D / 2) + pair, res_tag, rw, 32 + what);
+            }
+            st_flagged(dst + (size_t)b * (D / 2) + pair, pack_bf16x2(bf_lo(rw) + bf16r(s0), bf_hi(rw) + bf16r(s1)), dst_tag);
+        }
+        cta_sync();
+    }
+    stream_release(c.st, 1);
+    return all_ok(ok);
 }
 
 // ---- phase: RMSNorm + gate/up GEMV + SwiGLU -----------------------------------------------------------
@@ -842,40 +841,54 @@ template <int NB>
 __device__ bool phase_gu(Cta& c, int l) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t tag = tag_of(c, c.step, l);
-    const bf16* gain = reinterpret_cast<const bf16*>(p.ln2) + (size_t)l * D;
-    uint4 gq[4];
-    if constexpr (NB == 1) load_gains(gain, c.lane, gq);
-    bool ok = gather7<NB, Q3_ROW_WORDS>(c, c.ws.mail_hmid + (size_t)c.cta * NB * MS, D, tag, ITTAI_PH_GU, reinterpret_cast<uint16_t*>(c.xs));
-    int a0, a1;
-    act_cols(c.ncta, c.cta, a0, a1);             // this CTA's SwiGLU outputs: weight rows 2 a0 .. 2 a1
-    const int n_act = a1 - a0;
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.ln2) + (size_t)l * D + 2 * c.tid);
+    uint32_t u[NB];
+    bool ok = true;
+#pragma unroll
+    for (int b = 0; b < NB; ++b) ok = ok && wait_word(c.w, c.ws.hmid + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_GU);
+    int u0, u1;
+    split_range(FF / 6, c.ncta, c.cta, u0, u1);      // 128-bit words: three units of two activations = four weight rows each
+    u0 *= 3; u1 *= 3;
     const bf16* W = nullptr;
-    if (n_act > 0) {
-        W = reinterpret_cast<const bf16*>(stream_wait(c.st, c.st.consumed, c.w));
-        ok = ok && W != nullptr;
-    }
-    if (!all_ok(ok)) return false;
-    c.t_ready = clock64();
-    if constexpr (NB > 1) norm_rows_smem<NB>(c, gain);
-    if (n_act == 0) return true;
-    uint16_t* pub = c.hdr->pub;                  // [sequence][kPubHalves]
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok, u1 > u0 ? &W : nullptr)) return false;
+    if (u1 == u0) return true;
     if constexpr (NB == 1) {
         float xr[32];
-        load_xreg_norm(c.xs, gq, p.eps, c.lane, xr);
-        for (int un = c.warp; 2 * un < n_act; un += kWarps) {        // two outputs = four weight rows per warp
-            const bool two = 2 * un + 1 < n_act;
-            const bf16* wu = W + (size_t)(4 * un) * D;
-            const bf16* wp[4] = {wu, wu + D, two ? wu + 2 * D : wu, two ? wu + 3 * D : wu + D};
-            float acc[4];
-            dot_rows_xreg<4>(wp, xr, c.lane, acc);
+        if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
+        uint32_t* pub = reinterpret_cast<uint32_t*>(c.hdr->sub);      // this CTA's packed outputs, [unit][sequence]
+        for (int un = u0 + c.warp; un < u1; un += kWarps) {
+            const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
+            float a0[NB], a1[NB];
+            if constexpr (NB == 1) {
+                const bf16* wp[4] = {wu, wu + D, wu + 2 * D, wu + 3 * D};
+                float acc[4][NB];
+                dot_rows_k1024<false, NB, 4>(c, wp, xr, acc);
+                a0[0] = swiglu(acc[0][0], acc[1][0]);
+                a1[0] = swiglu(acc[2][0], acc[3][0]);
+            } else {
+#pragma unroll
+                for (int hsel = 0; hsel < 2; ++hsel) {
+                    const bf16* wp[2] = {wu + (2 * hsel) * D, wu + (2 * hsel + 1) * D};
+                    float acc[2][NB];
+                    dot_rows_k1024<false, NB, 2>(c, wp, xr, acc);
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) (hsel ? a1[b] : a0[b]) = swiglu(acc[0][b], acc[1][b]);
+                }
+            }
             if (c.lane == 0) {
-                pub[2 * un] = __bfloat16_as_ushort(__float2bfloat16_rn(swiglu(acc[0], acc[1])));
-                if (two) pub[2 * un + 1] = __bfloat16_as_ushort(__float2bfloat16_rn(swiglu(acc[2], acc[3])));
+#pragma unroll
+                for (int b = 0; b < NB; ++b) pub[(un - u0) * NB + b] = pack_bf16x2(a0[b], a1[b]);
             }
         }
         stream_release(c.st, 1);                         // its barrier also publishes `pub` to the CTA
+        // three units (six activations) leave as one 128-bit word
+        for (int i = c.tid; i < (u1 - u0) / 3 * NB; i += kThreads) {
+            const int wq = i / NB, b = i % NB;
+            st_flagged128(reinterpret_cast<uint4*>(c.ws.act) + (size_t)b * (FF / 6) + u0 / 3 + wq,
+                          pub[(3 * wq) * NB + b], pub[(3 * wq + 1) * NB + b], pub[(3 * wq + 2) * NB + b], tag);
+        }
     } else {
-        const int n_rows = 2 * n_act, n_tasks = (n_rows + 15) / 16 * 4;
+        const int n_rows = 4 * (u1 - u0), n_tasks = (n_rows + 15) / 16 * 4;
         float* part = c.hdr->sub;
         for (int task = c.warp; task < n_tasks; task += kWarps) {
             float d[4];
@@ -883,38 +896,40 @@ __device__ bool phase_gu(Cta& c, int l) {
             gemv_store<NB>(part, task, c.lane, d);
         }
         stream_release(c.st, 1);                         // its barrier also publishes `part` to the CTA
-        for (int i = c.tid; i < n_act * NB; i += kThreads) {
-            const int b = i / n_act, a = i - b * n_act;
-            pub[b * kPubHalves + a] = __bfloat16_as_ushort(__float2bfloat16_rn(
-                swiglu(gemv_sum<NB, 4>(part, 2 * a, b), gemv_sum<NB, 4>(part, 2 * a + 1, b))));
+        // a lane per unit (four rows, two activations) in groups of four lanes, the fourth idle: the first lane of a group
+        // collects its neighbours' pairs and sends the three units (six activations) off as one 128-bit word
+        const int n_words = (u1 - u0) / 3 * NB;
+        for (int i0 = 0; i0 < n_words * 4; i0 += kThreads) {
+            const int i = i0 + c.tid, wi = i >> 2, k = i & 3;
+            const bool live = wi < n_words && k < 3;
+            const int wq = live ? wi / NB : 0, b = live ? wi % NB : 0;
+            const int r = 12 * wq + 4 * k;               // rows: gate, up, gate, up of two adjacent activations
+            uint32_t w = 0;
+            if (live) w = pack_bf16x2(swiglu(gemv_sum<NB, 4>(part, r, b), gemv_sum<NB, 4>(part, r + 1, b)),
+                                      swiglu(gemv_sum<NB, 4>(part, r + 2, b), gemv_sum<NB, 4>(part, r + 3, b)));
+            const uint32_t w1 = __shfl_down_sync(0xffffffffu, w, 1), w2 = __shfl_down_sync(0xffffffffu, w, 2);
+            if (live && k == 0) st_flagged128(reinterpret_cast<uint4*>(c.ws.act) + (size_t)b * (FF / 6) + u0 / 3 + wq, w, w1, w2, tag);
         }
-        cta_sync();
-    }
-    // the outputs leave as three words of seven values per sequence to every CTA
-    for (int i = c.tid; i < c.ncta * Q3_ACT_WORDS * NB; i += kThreads) {
-        const int k = i % Q3_ACT_WORDS, r = i / Q3_ACT_WORDS, b = r % NB, dst = r / NB;
-        send7(c.ws.mail_act + (((size_t)dst * NB + b) * MS + c.cta) * Q3_ACT_WORDS + k, pub + b * kPubHalves + 7 * k, n_act - 7 * k, tag);
     }
     return true;
 }
 
 // ---- phase: final RMSNorm + tied lm_head GEMV + argmax ------------------------------------------------
-// logits = bf16(W_embed x); argmax over the bf16 values, lowest index wins ties (torch semantics).  The table rows come
-// through the ring in entries of 32.  Every CTA mails its best (value, index) to every CTA, so each knows the next token
-// at once.
+// logits = bf16(W_embed x); argmax over the bf16 values, lowest index wins ties (torch semantics).  The table is read
+// straight from HBM with streaming loads (2 MB per CTA: far more than the ring holds, and nothing waits behind it).
+// Every CTA publishes its best (value, index); every CTA then gathers all of them, so each knows the next token at once.
 template <int NB>
 __device__ bool phase_head(Cta& c) {
     const IttaiQwen3Decode& p = c.p;
-    const bf16* gain = reinterpret_cast<const bf16*>(p.fin_w);
-    uint4 gq[4];
-    if constexpr (NB == 1) load_gains(gain, c.lane, gq);
-    bool ok = gather7<NB, Q3_ROW_WORDS>(c, c.ws.mail_h + (size_t)c.cta * NB * MS, D, tag_of(c, c.step, p.n_layers), ITTAI_PH_HEAD,
-                                        reinterpret_cast<uint16_t*>(c.xs));
-    if (!all_ok(ok)) return false;
-    c.t_ready = clock64();
+    const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.fin_w) + 2 * c.tid);
+    uint32_t u[NB];
+    bool ok = true;
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+        ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag_of(c, c.step, p.n_layers), u[b], ITTAI_PH_HEAD);
+    if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
     float xr[32];
-    if constexpr (NB == 1) load_xreg_norm(c.xs, gq, p.eps, c.lane, xr);
-    else norm_rows_smem<NB>(c, gain);
+    if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
     bf16* logits = reinterpret_cast<bf16*>(p.logits);
     int r0, r1;
     split_range(p.vocab, c.ncta, c.cta, r0, r1);
@@ -957,35 +972,35 @@ __device__ bool phase_head(Cta& c) {
             }
             stream_release(c.st, 1);
             continue;
-        } else {
-            const int lr = c.warp * R;                                 // this warp's first row inside the entry
-            if (lr < rows_here) {
-                const bf16* wp[R];
+        }
+        const int lr = c.warp * R;                                 // this warp's first row inside the entry
+        if (lr < rows_here) {
+            const bf16* wp[R];
 #pragma unroll
-                for (int r = 0; r < R; ++r) wp[r] = W + (size_t)(lr + r < rows_here ? lr + r : rows_here - 1) * D;
-                float acc[R];
-                dot_rows_xreg<R>(wp, xr, c.lane, acc);
+            for (int r = 0; r < R; ++r) wp[r] = W + (size_t)(lr + r < rows_here ? lr + r : rows_here - 1) * D;
+            float acc[R][NB];
+            dot_rows_k1024<false, NB, R>(c, wp, xr, acc);
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    if (lr + r < rows_here) {
-                        const int row = e0 + lr + r;
-                        const float v = bf16r(acc[r]);
-                        if (v > bv[0]) { bv[0] = v; bi[0] = row; }   // rows ascend within a warp: first max kept
-                        if (p.write_logits && c.lane == 0) logits[row] = __float2bfloat16_rn(v);
+            for (int r = 0; r < R; ++r) {
+                if (lr + r < rows_here) {
+                    const int row = e0 + lr + r;
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) {
+                        const float v = bf16r(acc[r][b]);
+                        if (v > bv[b]) { bv[b] = v; bi[b] = row; }   // rows ascend within a warp: first max kept
+                        if (p.write_logits && c.lane == 0) logits[(size_t)b * p.vocab + row] = __float2bfloat16_rn(v);
                     }
                 }
             }
-            stream_release(c.st, 1);
         }
+        stream_release(c.st, 1);
     }
-    const uint32_t tag = 1u + (uint32_t)c.step % 65535u;
+    const uint32_t tag = (uint32_t)c.step + 1u;
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
         if (c.lane == 0) { c.hdr->bestv[c.warp] = bv[b]; c.hdr->besti[c.warp] = bi[b]; }
         cta_sync();
-        bool okb = true;
-        if (c.tid < c.ncta) {
-            // every sending thread folds the warps' candidates itself and mails the CTA's best to CTA `tid` ...
+        if (c.tid == 0) {
             float v = c.hdr->bestv[0];
             int ix = c.hdr->besti[0];
             for (int w = 1; w < kWarps; ++w) {
@@ -993,12 +1008,20 @@ __device__ bool phase_head(Cta& c) {
                 const int iw = c.hdr->besti[w];
                 if (vw > v || (vw == v && iw < ix)) { v = vw; ix = iw; }
             }
-            st_mail(c.ws.mail_cand + ((size_t)c.tid * NB + b) * MS + c.cta, __float_as_uint(v), (uint32_t)ix, 0u, 0u, tag);
-            // ... and collects the best of CTA `tid`
-            uint32_t u[4] = {0, 0, 0, 0};
-            okb = wait_mail(c.w, c.ws.mail_cand + ((size_t)c.cta * NB + b) * MS + c.tid, tag, u, 16 + ITTAI_PH_HEAD);
-            c.hdr->candv[c.tid] = __uint_as_float(u[0]);
-            c.hdr->candi[c.tid] = (int)u[1];
+            st_flagged(c.ws.cand_val + c.cta * ITTAI_MAX_BATCH + b, __float_as_uint(v), tag);
+            st_flagged(c.ws.cand_idx + c.cta * ITTAI_MAX_BATCH + b, (uint32_t)ix, tag);
+        }
+        cta_sync();
+    }
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        bool okb = true;
+        for (int k = c.tid; k < c.ncta; k += kThreads) {
+            uint32_t uv = 0, ui = 0;
+            okb = okb && wait_word(c.w, c.ws.cand_val + k * ITTAI_MAX_BATCH + b, tag, uv, 16 + ITTAI_PH_HEAD);
+            okb = okb && wait_word(c.w, c.ws.cand_idx + k * ITTAI_MAX_BATCH + b, tag, ui, 16 + ITTAI_PH_HEAD);
+            c.hdr->candv[k] = __uint_as_float(uv);
+            c.hdr->candi[k] = (int)ui;
         }
         if (!all_ok(okb)) return false;
         if (c.warp == 0) {
@@ -1016,6 +1039,9 @@ __device__ bool phase_head(Cta& c) {
                 if (vo > v || (vo == v && io < ix)) { v = vo; ix = io; }
             }
             if (c.lane == 0) {
+                // no logit compared greater than -inf (a row of NaNs): report it instead of feeding the sentinel back
+                if (ix == 0x7fffffff && c.cta == 0)
+                    report_status(p.status, c.ws.sync, ITTAI_ST_BAD_TOKEN, (uint32_t)ix, (uint32_t)c.step, (uint32_t)c.hdr->pos_s[b], (uint32_t)b);
                 c.hdr->tok_s[b] = ix;
                 if (c.cta == 0) {
                     p.next_id[b] = ix;
@@ -1059,10 +1085,11 @@ __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
         case ITTAI_PH_QKV: return phase_qkv<NB>(c, l);
         case ITTAI_PH_ATTN: return phase_attn(c, l);
         case ITTAI_PH_OPROJ:
-            return phase_proj_residual<NB, DQ, kFromAttn>(c, ITTAI_PH_OPROJ, l, tag, l == 0 ? nullptr : c.ws.mail_h, tag, c.ws.mail_hmid, tag);
+            return phase_proj_residual<NB, DQ>(c, ITTAI_PH_OPROJ, c.ws.attn, tag, l == 0 ? nullptr : c.ws.h, tag, c.ws.hmid, tag,
+                                               (uint32_t)(c.step * c.p.n_layers + l) + 1u);
         case ITTAI_PH_GU: return phase_gu<NB>(c, l);
         case ITTAI_PH_DOWN:
-            return phase_proj_residual<NB, FF, kFromAct>(c, ITTAI_PH_DOWN, l, tag, c.ws.mail_hmid, tag, c.ws.mail_h, tag_of(c, c.step, l + 1));
+            return phase_proj_residual<NB, FF>(c, ITTAI_PH_DOWN, c.ws.act, tag, c.ws.hmid, tag, c.ws.h, tag_of(c, c.step, l + 1), 0u);
         default: return phase_head<NB>(c);
     }
 }
@@ -1102,9 +1129,13 @@ __global__ void __launch_bounds__(kBlock, 1) q3_decode_kernel(const __grid_const
         if (!run_head && c.cta == 0 && c.tid < p.batch) p.out_ids[(size_t)step * p.batch + c.tid] = -1;
         if (step > 0 && !prev_head) {
             // No head ran, so nothing yet orders this token after the previous one: wait for its last layer's output
-            // before any mailbox of the chain is written again.
-            ok = all_ok(gather7<NB, Q3_ROW_WORDS>(c, c.ws.mail_h + (size_t)c.cta * NB * MS, D, tag_of(c, step - 1, p.n_layers), 64,
-                                                 reinterpret_cast<uint16_t*>(c.xs)));
+            // before any buffer of the chain is written again.
+            bool okw = true;
+            for (int b = 0; b < p.batch; ++b) {
+                uint32_t u;
+                okw = okw && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag_of(c, step - 1, p.n_layers), u, 64);
+            }
+            ok = all_ok(okw);
             if (!ok) break;
         }
         for (int l = 0; l < p.n_layers && ok; ++l) {
@@ -1136,9 +1167,8 @@ __global__ void __launch_bounds__(kBlock, 1) q3_decode_kernel(const __grid_const
     if (c.cta == 0 && c.tid < p.batch) p.pos[c.tid] = c.hdr->pos0[c.tid] + p.n_steps;
 }
 
-// One phase on its own at step 0 (tags of step 0): unit tests and per-phase profiles.  The inputs must sit in the
-// mailboxes with the tag of (step 0, layer); launched cooperatively because the attention merge and the head wait on
-// other CTAs.
+// One phase on its own at step 0 (tags of step 0): unit tests and per-phase profiles.  Inputs must carry the tag of
+// (step 0, layer); launched cooperatively because the attention merge and the head wait on other CTAs.
 template <int NB>
 __global__ void __launch_bounds__(kBlock, 1) q3_phase_kernel(const __grid_constant__ IttaiQwen3Decode p,
                                                                const __grid_constant__ Q3Workspace wsp,
@@ -1178,42 +1208,6 @@ static int check_args(const IttaiQwen3Decode* p) {
     return ITTAI_OK;
 }
 
-// What the kernel's fixed-size buffers assume about the grid: checked on the host so that a device the plan does not
-// fit is refused instead of overrunning a mailbox or waiting for a slice the ring can never hold.
-int q3_check_plan(int grid, int batch, uint32_t ring_bytes, char* why, size_t why_len) {
-    int lo, hi, rows_max = 0, act_max = 0, qkv_max = 0;
-    for (int c = 0; c < grid; ++c) {
-        res_rows(grid, c, lo, hi); rows_max = hi - lo > rows_max ? hi - lo : rows_max;
-        act_cols(grid, c, lo, hi); act_max = hi - lo > act_max ? hi - lo : act_max;
-        qkv_rows(grid, c, lo, hi); qkv_max = hi - lo > qkv_max ? hi - lo : qkv_max;
-    }
-    if (grid < 1 || grid > Q3_MAX_CTAS) { snprintf(why, why_len, "grid %d outside 1..%d", grid, Q3_MAX_CTAS); return ITTAI_E_DEVICE; }
-    if (rows_max > 7 * Q3_ROW_WORDS || act_max > 7 * Q3_ACT_WORDS || qkv_max > kPubHalves) {
-        snprintf(why, why_len, "%d CTAs leave %d residual rows, %d SwiGLU outputs, %d projection rows to one CTA: more than its mail words hold", grid, rows_max, act_max, qkv_max);
-        return ITTAI_E_DEVICE;
-    }
-    if (grid < batch * NKV) { snprintf(why, why_len, "%d SMs cannot hold one attention item per CTA at batch %d", grid, batch); return ITTAI_E_DEVICE; }
-    const int n_splits = q3_attn_splits(grid, batch), nc = q3_merge_ctas(n_splits);
-    if (n_splits * q3_part_words_per_msg(nc) > Q3_PART_WORDS || nc * q3_attn_words_per_owner(nc) > Q3_ATTN_WORDS) {
-        snprintf(why, why_len, "%d cache splits merged by %d CTAs do not fit the attention mailboxes", n_splits, nc);
-        return ITTAI_E_DEVICE;
-    }
-    // Every slice must fit the ring on its own (an empty ring restarts at its base), and the attention phase holds two
-    // K and two V tiles before it hands any back.
-    size_t slice = (size_t)qkv_max * D * 2;
-    const size_t cand[] = {(size_t)act_max * 2 * D * 2, (size_t)rows_max * DQ * 2, (size_t)rows_max * FF * 2, (size_t)kHeadRows * D * 2,
-                           (size_t)4 * kTile * HD * 2};
-    for (size_t s : cand) slice = s > slice ? s : slice;
-    if (slice > ring_bytes) { snprintf(why, why_len, "a %zu-byte weight slice does not fit the %u-byte shared-memory ring", slice, ring_bytes); return ITTAI_E_DEVICE; }
-    return ITTAI_OK;
-}
-static int check_plan(int grid, int batch, uint32_t ring_bytes) {
-    char why[200];
-    const int rc = q3_check_plan(grid, batch, ring_bytes, why, sizeof why);
-    if (rc != ITTAI_OK) set_error("%s", why);
-    return rc;
-}
-
 struct DeviceInfo { int dev = -1; int n_sms = 0; int smem_optin = 0; bool attr_set[4] = {false, false, false, false}; };
 static thread_local DeviceInfo g_info;
 
@@ -1240,17 +1234,32 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
     int rc = device_info();
     if (rc != ITTAI_OK) return rc;
     const int grid = g_info.n_sms < Q3_MAX_CTAS ? g_info.n_sms : Q3_MAX_CTAS;
-    if (grid < Q3_MIN_CTAS) {
-        set_error("the decode kernel's mailboxes are sized for one CTA on each of a B200's %d SMs (found %d)", Q3_MAX_CTAS, g_info.n_sms);
-        return ITTAI_E_DEVICE;
-    }
+    if (grid < 128) { set_error("the decode kernel's GEMV tiling needs at least 128 SMs (found %d)", grid); return ITTAI_E_DEVICE; }
+    if (grid < p->batch * NKV) { set_error("%d SMs cannot hold one attention item per CTA at batch %d", grid, p->batch); return ITTAI_E_DEVICE; }
     // all the shared memory a CTA may have: header + activations + the weight ring
     const size_t fixed = q3_fixed_smem_bytes(NB);
     const size_t smem = (size_t)g_info.smem_optin;
     if (smem < fixed + 96 * 1024) { set_error("%zu bytes of shared memory per CTA leave no room for the weight ring", smem); return ITTAI_E_DEVICE; }
     uint32_t ring_bytes = (uint32_t)((smem - fixed) / 1024 * 1024);
-    rc = check_plan(grid, p->batch, ring_bytes);
-    if (rc != ITTAI_OK) return rc;
+    {   // every slice must fit the ring on its own (an empty ring restarts at its base), and the attention phase holds two K
+        // and two V tiles before it hands any back
+        int lo, hi;
+        size_t slice = 4 * (size_t)kTile * HD * 2;
+        for (int c = 0; c < grid; ++c) {
+            split_range(DQKV / 4, grid, c, lo, hi);
+            const size_t qkv = (size_t)(hi - lo) * 4 * D * 2;
+            split_range(D / 2, grid, c, lo, hi);
+            const size_t down = (size_t)(hi - lo) * 2 * FF * 2;
+            split_range(FF / 6, grid, c, lo, hi);
+            const size_t gu = (size_t)(hi - lo) * 12 * D * 2;
+            const size_t m = qkv > down ? (qkv > gu ? qkv : gu) : (down > gu ? down : gu);
+            slice = m > slice ? m : slice;
+        }
+        if (slice > ring_bytes) {
+            set_error("a %zu-byte weight slice does not fit the %u-byte shared-memory ring (%d CTAs)", slice, ring_bytes, grid);
+            return ITTAI_E_DEVICE;
+        }
+    }
     const void* fn_decode = (const void*)q3_decode_kernel<NB>;
     const void* fn_phase = (const void*)q3_phase_kernel<NB>;
     constexpr int slot = NB == 1 ? 0 : NB == 2 ? 1 : NB == 4 ? 2 : 3;
@@ -1269,9 +1278,9 @@ static int launch_nb(const IttaiQwen3Decode* p, int phase, int layer, cudaStream
     q3_ws_layout(p->batch, reinterpret_cast<char*>(p->workspace), &ws);
     cudaError_t e = cudaMemsetAsync(ws.sync, 0, Q3_SYNC_WORDS * sizeof(uint32_t), st);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(sync)");
-    if (phase < 0) {   // a phase launch keeps the mail its caller prepared
-        e = cudaMemsetAsync(ws.mail_h, 0, ws.mail_bytes, st);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(mailboxes)");
+    if (phase < 0) {   // a phase launch keeps the flagged words its caller prepared
+        e = cudaMemsetAsync(ws.h, 0, ws.flagged_bytes, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(flagged words)");
     }
     e = cudaMemsetAsync(p->status, 0, ITTAI_STATUS_WORDS * sizeof(uint32_t), st);
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
@@ -1308,30 +1317,6 @@ extern "C" int ittai_qwen3_decode_workspace_bytes(int batch, size_t* bytes) {
     return ITTAI_OK;
 }
 
-extern "C" int ittai_qwen3_decode_layout(int batch, int n_sms, IttaiQwen3Layout* out) {
-    if (!out || (batch != 1 && batch != 2 && batch != 4 && batch != 8)) { ittai::set_error("batch must be 1, 2, 4 or 8 and the output non-null"); return ITTAI_E_ARG; }
-    const int grid = n_sms < ittai::Q3_MAX_CTAS ? n_sms : ittai::Q3_MAX_CTAS;
-    char why[200];
-    if (ittai::q3_check_plan(grid, batch, 0xffffffffu, why, sizeof why) != ITTAI_OK || grid < ittai::Q3_MIN_CTAS) {
-        ittai::set_error("no decode plan for %d SMs at batch %d", n_sms, batch);
-        return ITTAI_E_DEVICE;
-    }
-    ittai::Q3Workspace ws;
-    size_t offs[ittai::Q3_N_REGIONS];
-    out->bytes = ittai::q3_ws_layout(batch, nullptr, &ws, offs);
-    out->off_h = offs[1]; out->off_hmid = offs[2]; out->off_act = offs[3]; out->off_attn = offs[4];
-    out->off_qkv = offs[5]; out->off_part = offs[6]; out->off_cand = offs[7];
-    out->n_ctas = grid;
-    out->mail_stride = ittai::Q3_MAIL_STRIDE;
-    out->act_words = ittai::Q3_ACT_WORDS;
-    out->attn_words = ittai::Q3_ATTN_WORDS;
-    out->qkv_words = ittai::Q3_QKV_WORDS;
-    out->n_splits = ittai::q3_attn_splits(grid, batch);
-    out->merge_ctas = ittai::q3_merge_ctas(out->n_splits);
-    out->attn_words_per_owner = ittai::q3_attn_words_per_owner(out->merge_ctas);
-    return ITTAI_OK;
-}
-
 extern "C" int ittai_qwen3_decode_launch(const IttaiQwen3Decode* p, void* stream) { return ittai::launch(p, -1, 0, stream); }
 
 extern "C" int ittai_qwen3_phase_launch(const IttaiQwen3Decode* p, int phase, int layer, void* stream) {
@@ -1344,13 +1329,15 @@ extern "C" int ittai_qwen3_phase_launch(const IttaiQwen3Decode* p, int phase, in
 // Some hosts of this library have no way to get scratch memory at call time: a serving process that handed the whole
 // GPU to its own pool at start-up (so a later cudaMalloc fails or fragments it), a C or Rust runtime that binds this
 // ABI without an allocator of its own, or a latency-critical loop in which cudaMalloc's device-wide synchronisation is
-// not acceptable.  For them the decode kernel's workspace (the CTAs' mailboxes and the abort flag) lives in this
-// file-scope device array instead of a caller buffer.  Every GPU that loads the library
+// not acceptable.  For them the decode kernel's workspace (flagged words, split-K partials, argmax candidates,
+// abort flag) lives in this file-scope device array instead of a caller buffer.  Every GPU that loads the library
 // holds these bytes until the process exits.
 namespace ittai {
 
 constexpr int kStaticMaxBatch = ITTAI_STATIC_DECODE_MAX_BATCH;
-constexpr size_t kStaticScratchBytes = q3_ws_bytes(kStaticMaxBatch);      // the mailboxes of two sequences: about 7.5 MB
+// q3_ws_layout(kStaticMaxBatch) rounded up: 128 B sync + (512+2048+1024+512+1536) words per sequence + partials + candidates
+constexpr size_t kStaticScratchBytes = 256 + (size_t)kStaticMaxBatch * 5632 * 8 + 1280 +
+                                       (size_t)Q3_MAX_CTAS * Q3_PART_WORDS * 8 + 2 * (size_t)Q3_MAX_CTAS * ITTAI_MAX_BATCH * 8;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
 
 // In host code `g_decode_scratch` is only a handle for the runtime, not a device address: the address the kernel needs

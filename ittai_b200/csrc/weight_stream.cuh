@@ -30,9 +30,10 @@ struct StreamShared {
     uint32_t q_bytes[kStreamSlots];        // its size rounded up to kStreamAlign
     uint32_t issued;                       // entries issued so far (written by the issuing lane)
     uint32_t head;                         // next free ring offset (issuing lane)
-    uint32_t consumed;                     // entries released so far (compute thread 0, release / acquire accesses)
+    uint32_t consumed;                     // entries released so far (compute thread 0; release / acquire accesses)
     volatile uint32_t stop;                // compute threads are leaving early: issue nothing more
-    volatile uint32_t kv_epoch;            // 1 + index of the last (step, layer) whose attention output this CTA has seen whole
+    uint32_t kv_epoch;                     // 1 + index (step * layers + layer) of the last attention output this CTA's compute
+                                           // threads have received whole (release / acquire accesses)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -155,13 +156,10 @@ __device__ __forceinline__ const unsigned char* stream_wait(const Stream& s, uin
 }
 
 // Compute threads: everyone has finished reading the `n` oldest entries; hand their space back to the issuing lane.
-__device__ __forceinline__ void stream_release_synced(Stream& s, int n) {      // after a barrier that follows the last read
-    s.consumed += (uint32_t)n;
-    if (threadIdx.x == 0) st_release_cta(&s.sh->consumed, s.consumed);
-}
 __device__ __forceinline__ void stream_release(Stream& s, int n) {
     cta_sync();
-    stream_release_synced(s, n);
+    s.consumed += (uint32_t)n;
+    if (threadIdx.x == 0) st_release_cta(&s.sh->consumed, s.consumed);
 }
 
 // Issuing lane, before it exits: let every copy it launched land (bounded), so none is in flight when the CTA retires.

@@ -15,8 +15,6 @@ import torch
 from .. import _C
 from .config import D, DGU, DQ, DQKV, EPS, FF, HD, NKV, THETA
 
-Q3_CTAS = 148      # mailbox rows in the decode workspace (one per CTA of the persistent grid)
-
 
 def _strip(sd: dict) -> dict:
     """Drop the ``model.`` prefix as the reference does (``src/ittai/qwen3/engine.py:91``)."""
@@ -100,6 +98,7 @@ class Qwen3Decoder:
         self.flags = 0
         self.spin_limit = 0                  # 0 = library default
         self.lengths = [0] * self.B          # host mirror of `pos`, for capacity checks without a device read
+        self._unchecked = 0                  # steps launched whose status has not been read yet
         self._keep = None
         self._phase_clk = None
         self._core = None                    # dense prefill buffers, created at the first long prompt
@@ -125,23 +124,35 @@ class Qwen3Decoder:
         return C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
 
     def check_status(self) -> None:
-        """Synchronise and raise if a bounded device wait ran out during the last launch."""
-        _C.decode_status(self.status.cpu().tolist())
+        """Synchronise and raise if a bounded device wait ran out during the last launch.
+
+        A launch that aborts leaves the device positions where they were (the kernel advances ``pos`` only when every
+        step completed), so the host mirror ``lengths`` is advanced here, after the verdict, and re-read from the device
+        when a launch failed: a later prefill or decode then works on consistent positions."""
+        try:
+            _C.decode_status(self.status.cpu().tolist())
+        except _C.IttaiError:
+            self._unchecked = 0
+            self.lengths = self.pos.cpu().tolist()
+            raise
+        self.lengths = [n + self._unchecked for n in self.lengths]
+        self._unchecked = 0
 
     def reset(self) -> None:
         self.pos.zero_()
         self.lengths = [0] * self.B
+        self._unchecked = 0
 
     def _launch(self, n_steps, forced=None, timed=False, check=True):
-        if max(self.lengths) + n_steps > self.cap:
-            raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths)} cached + {n_steps} steps")
+        if max(self.lengths) + self._unchecked + n_steps > self.cap:
+            raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths) + self._unchecked} cached + {n_steps} steps")
         n_forced = 0 if forced is None else forced.shape[0]
         out_ids = torch.empty(n_steps, self.B, dtype=torch.int32, device=self.dev)
         step_ns = torch.zeros(n_steps, dtype=torch.int64, device=self.dev) if timed else None
         p = self._params(n_steps, n_forced, forced, out_ids, step_ns)
         self._keep = (p, forced, out_ids, step_ns)
         _C.check(self.lib.ittai_qwen3_decode_launch(C.byref(p), self._stream()))
-        self.lengths = [n + n_steps for n in self.lengths]
+        self._unchecked += n_steps
         if check:
             self.check_status()
         return out_ids, step_ns
@@ -174,6 +185,10 @@ class Qwen3Decoder:
         """Append ``ids`` ([B, n]) to every sequence's cache with the dense prefill kernels."""
         from .engine import PrefillCore
         B, n = ids.shape
+        if self._unchecked:
+            self.check_status()
+        if int(ids.min()) < 0 or int(ids.max()) >= self.V:
+            raise ValueError(f"token id outside [0, {self.V})")
         if max(self.lengths) + n > self.cap:
             raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths)} cached + {n} prompt tokens")
         if self._core is None or self._core.M < B * n:
@@ -214,7 +229,7 @@ class Qwen3Decoder:
         p.workspace = None
         self._keep = (p, out_ids)
         _C.check(self.lib.ittai_qwen3_decode_launch_static(C.byref(p), self._stream()))
-        self.lengths = [n + n_steps for n in self.lengths]
+        self._unchecked += n_steps
         self.check_status()
         return out_ids.t()
 
@@ -254,90 +269,51 @@ class Qwen3Decoder:
         _C.check(self.lib.ittai_qwen3_phase_launch(C.byref(p), phase, layer, self._stream()))
         self.check_status()
 
-    # The vectors one phase hands to the next travel as 128-bit mail words (seven bf16 values + a 16-bit tag) that the
-    # producing CTA writes into a mailbox of every consuming CTA; ``ittai_qwen3_decode_layout`` describes where.  These
-    # helpers let tests and profiles read a phase's output and plant a phase's input; a phase launch runs at step 0, where
-    # the data of layer l carries tag l + 1.
-    _WIDTH = {"h": D, "hmid": D, "act": FF, "attn": DQ, "qkv": DQKV}
+    # The vectors one phase hands to the next live in the workspace as flagged words.  h and hmid use 64-bit words:
+    # two bf16 values in the low half, the tag of the producing (step, layer) in the high half.  qkv, attn and act use
+    # 128-bit words of three 32-bit payloads + tag: four bf16 values per word for qkv and attn (the third payload is
+    # unused), six for act.  These helpers let tests and profiles read a phase's output and
+    # plant a phase's input; a phase launch runs at step 0, where layer l's tag is l + 1.
+    _FLAGGED = (("h", D), ("qkv", DQKV), ("attn", DQ), ("hmid", D), ("act", FF))
+    _WIDE = {"qkv": 4, "attn": 4, "act": 6}       # bf16 values per 128-bit word
 
-    def _layout(self) -> _C.Qwen3Layout:
-        if getattr(self, "_lay", None) is None:
-            lay = _C.Qwen3Layout()
-            _C.check(self.lib.ittai_qwen3_decode_layout(self.B, self.n_sms, C.byref(lay)))
-            self._lay = lay
-        return self._lay
-
-    def _mail(self, name: str) -> torch.Tensor:
-        """int16 view of the mailboxes of kind ``name``: ``[cta, ..., 8]``, halves 0..6 payload, half 7 the tag."""
-        lay = self._layout()
+    def _flagged_words(self, name: str) -> torch.Tensor:
+        """int64 view of buffer ``name``: ``[B, n/2]`` for 64-bit words, ``[B, 512, 2]`` (low, high half) for 128-bit ones."""
         off = self._ws_ptr - self.workspace.data_ptr()
-        n, B, ms = Q3_CTAS, self.B, lay.mail_stride
-        shape = {"h": (n, B, ms, 1), "hmid": (n, B, ms, 1), "act": (n, B, ms, lay.act_words),
-                 "attn": (n, B, NKV, lay.attn_words), "qkv": (n, lay.qkv_words)}[name]
-        o = off + getattr(lay, "off_" + name)
-        count = 1
-        for d in shape:
-            count *= d
-        return self.workspace[o:o + count * 16].view(torch.int16).view(*shape, 8)
-
-    def _ranges(self, width: int):
-        n = self._layout().n_ctas
-        return [(width * p // n, width * (p + 1) // n) for p in range(n)]
+        up = lambda n: (n + 255) // 256 * 256
+        o = off + up(64 * 4)
+        for nm, n in self._FLAGGED:
+            nb = self.B * (n // 2) * 8
+            if nm == name:
+                if nm in self._WIDE:
+                    words = n // self._WIDE[nm]
+                    return self.workspace[o:o + self.B * words * 16].view(torch.int64).view(self.B, words, 2)
+                return self.workspace[o:o + nb].view(torch.int64).view(self.B, n // 2)
+            o += up(nb)
+        raise KeyError(name)
 
     def read_buf(self, name: str) -> torch.Tensor:
-        """bf16 ``[B, n]`` content of the vector ``name`` (h, qkv, attn, hmid, act) as the last phase mailed it."""
-        lay, m = self._layout(), self._mail(name)
-        out = torch.zeros(self.B, self._WIDTH[name], dtype=torch.int16, device=self.dev)
-        if name in ("h", "hmid", "act"):
-            box = m[0]                                             # CTA 0's mailbox: every CTA received the same words
-            for p, (lo, hi) in enumerate(self._ranges(self._WIDTH[name])):
-                out[:, lo:hi] = box[:, p, :, :7].reshape(self.B, -1)[:, :hi - lo]
-        elif name == "attn":
-            nc, wpo = lay.merge_ctas, lay.attn_words_per_owner
-            dpc = HD // nc
-            for g in range(NKV):
-                for j in range(nc):
-                    vals = m[0][:, g, j * wpo:(j + 1) * wpo, :7].reshape(self.B, -1)[:, :2 * dpc]
-                    out[:, (2 * g) * HD + j * dpc:(2 * g) * HD + (j + 1) * dpc] = vals[:, :dpc]
-                    out[:, (2 * g + 1) * HD + j * dpc:(2 * g + 1) * HD + (j + 1) * dpc] = vals[:, dpc:]
-        else:                                                      # qkv: the first split of every (sequence, kv head)
-            for b in range(self.B):
-                for g in range(NKV):
-                    box = m[(b * NKV + g) * lay.n_splits][:, :4].reshape(4, HD)
-                    out[b, (2 * g) * HD:(2 * g + 2) * HD] = box[:2].reshape(-1)
-                    out[b, DQ + g * HD:DQ + (g + 1) * HD] = box[2]
-                    out[b, DQ + NKV * HD + g * HD:DQ + NKV * HD + (g + 1) * HD] = box[3]
-        return out.view(torch.bfloat16)
+        """bf16 ``[B, n]`` payload of the flagged buffer ``name`` (h, qkv, attn, hmid, act)."""
+        w = self._flagged_words(name)
+        if name in self._WIDE:
+            lo, hi = w[..., 0], w[..., 1]
+            vals = [lo & 0xFFFF, (lo >> 16) & 0xFFFF, (lo >> 32) & 0xFFFF, (lo >> 48) & 0xFFFF, hi & 0xFFFF, (hi >> 16) & 0xFFFF]
+            pair = torch.stack(vals[:self._WIDE[name]], -1)
+        else:
+            pair = torch.stack([w & 0xFFFF, (w >> 16) & 0xFFFF], -1)
+        return pair.to(torch.int32).to(torch.int16).view(torch.bfloat16).reshape(self.B, -1)
 
     def write_buf(self, name: str, values: torch.Tensor, layer: int) -> None:
-        """Plant ``values`` ([B, n] or [n]) as vector ``name`` in every mailbox that receives it, with the tag of (step 0, ``layer``)."""
-        lay, m = self._layout(), self._mail(name)
-        v = values.to(torch.bfloat16).reshape(self.B, -1).to(self.dev).view(torch.int16)
-        tag = layer + 1
-        m[..., 7] = tag
-        if name in ("h", "hmid", "act"):
-            k = m.shape[3]
-            for p, (lo, hi) in enumerate(self._ranges(self._WIDTH[name])):
-                w = torch.zeros(self.B, 7 * k, dtype=torch.int16, device=self.dev)
-                w[:, :hi - lo] = v[:, lo:hi]
-                m[:, :, p, :, :7] = w.view(1, self.B, k, 7)
-        elif name == "attn":
-            nc, wpo = lay.merge_ctas, lay.attn_words_per_owner
-            dpc = HD // nc
-            for g in range(NKV):
-                for j in range(nc):
-                    w = torch.zeros(self.B, 7 * wpo, dtype=torch.int16, device=self.dev)
-                    w[:, :dpc] = v[:, (2 * g) * HD + j * dpc:(2 * g) * HD + (j + 1) * dpc]
-                    w[:, dpc:2 * dpc] = v[:, (2 * g + 1) * HD + j * dpc:(2 * g + 1) * HD + (j + 1) * dpc]
-                    m[:, :, g, j * wpo:(j + 1) * wpo, :7] = w.view(1, self.B, wpo, 7)
+        """Plant ``values`` ([B, n] or [n]) in flagged buffer ``name`` with the tag of (step 0, ``layer``)."""
+        per = self._WIDE.get(name, 2)
+        v = values.to(torch.bfloat16).reshape(self.B, -1, per).to(self.dev).view(torch.int16).to(torch.int64) & 0xFFFF
+        tag = (layer + 1) << 32
+        if name in self._WIDE:
+            lo = v[..., 0] | (v[..., 1] << 16) | (v[..., 2] << 32) | (v[..., 3] << 48)
+            hi = (v[..., 4] | (v[..., 5] << 16) if per == 6 else torch.zeros_like(lo)) | tag
+            self._flagged_words(name).copy_(torch.stack([lo, hi], -1))
         else:
-            m[..., 4:7] = 0
-            for b in range(self.B):
-                for g in range(NKV):
-                    box = torch.stack([v[b, (2 * g) * HD:(2 * g + 1) * HD], v[b, (2 * g + 1) * HD:(2 * g + 2) * HD],
-                                       v[b, DQ + g * HD:DQ + (g + 1) * HD], v[b, DQ + NKV * HD + g * HD:DQ + NKV * HD + (g + 1) * HD]])
-                    c0 = (b * NKV + g) * lay.n_splits
-                    m[c0:c0 + lay.n_splits, :, :4] = box.reshape(1, 4 * HD // 4, 4)
+            self._flagged_words(name).copy_(v[..., 0] | (v[..., 1] << 16) | tag)
 
     @torch.no_grad()
     def generate(self, prompt_host: torch.Tensor, n_steps: int) -> torch.Tensor:

@@ -130,7 +130,10 @@ class Engine:
         T, B = sum(seqlens), len(seqlens)
         assert T <= self.M and B <= self.Bmax and min(seqlens) > 0
         pos, seq, slot, seqs, last, _ = self._tasks(seqlens)
-        self.tokens[:T].copy_(torch.tensor([t for s in input_ids for t in s], dtype=torch.int32), non_blocking=True)
+        flat = torch.tensor([t for s in input_ids for t in s], dtype=torch.int32)
+        if int(flat.min()) < 0 or int(flat.max()) >= self.embed.shape[0]:
+            raise ValueError(f"token id outside [0, {self.embed.shape[0]})")      # the gather kernel would clamp it silently
+        self.tokens[:T].copy_(flat, non_blocking=True)
         self.pos[:T].copy_(pos, non_blocking=True)
         self.seq[:T].copy_(seq, non_blocking=True)
         self.slot[:T].copy_(slot, non_blocking=True)

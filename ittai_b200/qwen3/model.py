@@ -33,19 +33,26 @@ class Qwen3Embedder:
             raise RuntimeError("no tokenizer loaded: pass lists of token ids")
         return [self.tok(t, truncation=True, max_length=max_length)["input_ids"] for t in texts]
 
+    def _batches(self, lengths):
+        """Cuts the sequences, in order, into runs that fit one forward: at most ``max_seqs`` sequences and ``max_tokens``
+        tokens each (the batching rule of the reference's ``embed``, ``model.py:79-90``).  Yields (first, count)."""
+        first, tokens = 0, 0
+        for i, n in enumerate(lengths):
+            if n > self.max_tokens:
+                raise ValueError(f"sequence {i} has {n} tokens, more than max_tokens={self.max_tokens}")
+            if i - first == self.max_seqs or tokens + n > self.max_tokens:
+                yield first, i - first
+                first, tokens = i, 0
+            tokens += n
+        if len(lengths) > first:
+            yield first, len(lengths) - first
+
     @torch.no_grad()
     def embed(self, texts, max_length=2048):
-        """Greedy packing under ``max_tokens`` / ``max_seqs`` exactly as the reference batches (``model.py:79-90``)."""
+        """fp32 ``[N, 1024]`` embeddings; every batch's result is cloned out of the engine's persistent buffer."""
         ids = self._ids(texts, max_length)
-        out, k = [], 0
-        while k < len(ids):
-            n, tot = 0, 0
-            while k + n < len(ids) and n < self.max_seqs and tot + len(ids[k + n]) <= self.max_tokens:
-                tot += len(ids[k + n]); n += 1
-            assert n > 0, "sequence longer than max_tokens"
-            out.append(self.engine.forward(ids[k: k + n]).clone())
-            k += n
-        return torch.cat(out)
+        parts = [self.engine.forward(ids[a:a + n]).clone() for a, n in self._batches([len(s) for s in ids])]
+        return torch.cat(parts) if parts else torch.zeros(0, 1024)
 
     @torch.no_grad()
     def validate(self, ids, threshold=0.999):

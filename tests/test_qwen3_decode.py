@@ -17,6 +17,7 @@ from oracle import qwen3_ref as ref
 
 gpu = pytest.mark.gpu
 TIE_GAP = 0.0625      # two bf16 logits of magnitude 2..4 closer than this are within 2 ulp
+RMS_SLACK = 1.05      # the rms over the 151-column sample of a 151 936-column row is itself an estimate
 
 
 def _load(golden_dir, name):
@@ -156,6 +157,8 @@ def test_bad_token_reports_status(tiny_dec):
     d.next_id.fill_(10 ** 6)
     with pytest.raises(IttaiError, match="out of range"):
         d.decode(1)
+    # the aborted launch left the device positions alone, and the host mirror follows them
+    assert d.lengths == d.pos.tolist() == [0]
     d.reset()
     d.next_id.fill_(3)
     d.decode(1)            # the context is still usable
@@ -203,6 +206,7 @@ def test_full_model_config1(full_hf, golden_dir):
     strided = logits[:, ::1009]
     gs = g["strided_logits"].float()
     worst_abs = (strided - gs).abs().max().item()
+    rms = (strided - gs).pow(2).mean().sqrt().item()
     worst_cos = F.cosine_similarity(strided, gs, dim=-1).min().item()
     top = torch.gather(logits, 1, g["top_indices"].long())
     top_abs = (top - g["top_values"].float()).abs().max().item()
@@ -210,7 +214,7 @@ def test_full_model_config1(full_hf, golden_dir):
     agree = sum(int(a == b) for a, b in zip(picks, g["ids"].tolist()))
     gaps = (g["top_values"][:, 0].float() - g["top_values"][:, 1].float())
     bad = [s for s in range(64) if picks[s] != int(g["ids"][s]) and gaps[s] > TIE_GAP]
-    report = dict(teacher_forced_argmax_agree=agree, strided_max_abs=worst_abs, strided_min_cos=worst_cos,
+    report = dict(teacher_forced_argmax_agree=agree, strided_max_abs=worst_abs, strided_rms=rms, strided_min_cos=worst_cos,
                   top8_max_abs=top_abs, norm_rel=norm_rel)
     # free-running
     out = d.generate(g["prompt"], 64)[0].tolist()
@@ -218,13 +222,26 @@ def test_full_model_config1(full_hf, golden_dir):
     while same < 64 and out[same] == int(g["ids"][same]):
         same += 1
     report.update(free_running_prefix_equal=same, first_flip_gap=float(gaps[same]) if same < 64 else None)
+    # The noise floor of the comparison, from the fixture: how far the oracle's own variants (bf16 with the eager attention
+    # backend, fp32) are from the pinned run on the same weights and ids.  The kernel has to be no further from the pinned
+    # run than they are.  The strict north-star figures (max-abs 3e-2, 64 of 64 ids) are printed beside them: the variants
+    # themselves miss those.
+    floor = g["variant_distance"]
+    lim_abs = max(v["full_max_abs"] for v in floor.values())        # any sample of the columns stays below the full maximum
+    lim_rms = max(v["strided_rms"] for v in floor.values())
+    lim_cos = min(v["strided_min_cos"] for v in floor.values())
+    lim_agree = min(v["argmax_agree"] for v in floor.values())
+    report.update(floor=dict(max_abs=lim_abs, strided_rms=lim_rms, strided_min_cos=lim_cos, argmax_agree=lim_agree,
+                             free_running_prefix_equal={k: v["free_running_prefix_equal"] for k, v in floor.items()}),
+                  strict=dict(max_abs_le_3e_2=worst_abs <= 3e-2 and top_abs <= 3e-2, ids_64_of_64=same == 64))
     report_dir = os.environ.get("ITTAI_REPORT_DIR")
     if report_dir and os.path.isdir(report_dir):
         json.dump(report, open(os.path.join(report_dir, "parity_config1.json"), "w"), indent=1)
     print(report)
-    # the eager model's own backends differ by 0.051 max-abs on this config; the gate is 3e-2 + that floor
     assert worst_cos >= 0.9995 and norm_rel <= 5e-3
-    assert worst_abs <= 0.09 and top_abs <= 0.09
+    assert worst_abs <= lim_abs and top_abs <= lim_abs, f"max-abs {worst_abs:.4f} / {top_abs:.4f} beyond the oracle variants' {lim_abs:.4f}"
+    assert rms <= RMS_SLACK * lim_rms, f"rms {rms:.5f} beyond the oracle variants' {lim_rms:.5f}"
+    assert agree >= lim_agree, f"teacher-forced argmax agrees on {agree} steps, the oracle's variants on {lim_agree}"
     assert not bad, f"argmax differs at steps {bad} where the oracle's top-2 gap exceeds {TIE_GAP}"
     assert same == 64 or gaps[same] <= TIE_GAP, f"free-running ids diverge at step {same} with top-2 gap {gaps[same]}"
 

@@ -39,3 +39,18 @@ def test_rope_table_matches_eager_rotary(tiny_hf):
     assert torch.equal(t[:, :64], cos[0, :, :64]) and torch.equal(t[:, 64:], sin[0, :, :64])
     c, s = ref.rope_table(96, dims)
     assert torch.equal(t[:, :64].float(), c) and torch.equal(t[:, 64:].float(), s)
+
+
+def test_embedder_batches_respect_both_limits():
+    """The batching rule of ``Qwen3Embedder.embed``: runs of consecutive sequences under max_seqs and max_tokens."""
+    from ittai_b200.qwen3.model import Qwen3Embedder
+    import pytest
+    e = Qwen3Embedder.__new__(Qwen3Embedder)
+    e.max_seqs, e.max_tokens = 3, 10
+    lens = [4, 4, 4, 1, 1, 1, 1, 10, 9, 1]
+    runs = list(e._batches(lens))
+    assert runs == [(0, 2), (2, 3), (5, 2), (7, 1), (8, 2)]
+    assert sum(n for _, n in runs) == len(lens) and all(sum(lens[a:a + n]) <= 10 and n <= 3 for a, n in runs)
+    assert list(e._batches([])) == []
+    with pytest.raises(ValueError):
+        list(e._batches([3, 11]))
