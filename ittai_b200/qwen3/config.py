@@ -26,6 +26,23 @@ def decode_bytes_per_token(kv_len: int, n_layers: int = L, vocab: int = VOCAB) -
     kv_row = n_layers * 2 * NKV * HD * 2
     return weights + kv_row * kv_len + kv_row + 2 * D
 
-# names the reference also exports (reference ``src/ittai/qwen3/config.py:8-14``); the op ids double as phase ids here
+# The op table of the prefill task list, under the reference's names (reference ``src/ittai/qwen3/config.py:8-20``):
+# op ids, dependency-flag slots, words per task record, rows per GEMM block / attention query block, and for every GEMM
+# its width N, depth K, the slot it waits on, the slot it arrives on (``dl`` layers further), the norm statistics it
+# consumes / produces and its epilogue kind.
 OP_QKV, OP_OPROJ, OP_GU, OP_DOWN, OP_EMB, OP_ATTN, OP_FINAL = range(7)
-BM, QB = 128, 64          # rows per GEMM tile / per attention query block
+NGEMM = 4
+SLOT_X, SLOT_QKV, SLOT_ATTN, SLOT_XMID, SLOT_H, SLOT_SEQ = range(6)
+NSLOT = 5
+LN1, LN2 = 0, 1
+TW = 8
+BM, QB = 128, 64
+SPEC = {
+    OP_QKV: {"N": DQKV, "K": D, "dep": SLOT_X, "out": SLOT_QKV, "dl": 0, "s_in": LN1, "s_out": None, "kind": "qkv"},
+    OP_OPROJ: {"N": D, "K": DQ, "dep": SLOT_ATTN, "out": SLOT_XMID, "dl": 0, "s_in": None, "s_out": LN2, "kind": "res"},
+    OP_GU: {"N": DGU, "K": D, "dep": SLOT_XMID, "out": SLOT_H, "dl": 0, "s_in": LN2, "s_out": None, "kind": "gu"},
+    OP_DOWN: {"N": D, "K": FF, "dep": SLOT_H, "out": SLOT_X, "dl": 1, "s_in": None, "s_out": LN1, "kind": "res"},
+}
+# The reference searches these tile / stage grids per GPU (``config.py:22-27``); there is one sm_100a kernel set here, so
+# the table only names it.  Kept because callers import the name.
+CONFIGS = {"sm100": [{"tile_m": 256, "tile_n": 256, "stages": 5, "cta_pair": True}]}

@@ -17,22 +17,21 @@ import torch
 from .. import _C, ops
 from .config import BM, D, DQ, DQKV, EPS, FF, HD, NH, NKV, QB
 from .decoder import _strip, pack_weights, rope_table
+from .tasks import build_tasks
 
 
 def rope_perm(n_heads):
-    """Row permutation that makes half-split RoPE pairs adjacent (reference ``src/ittai/qwen3/engine.py:13-14``).
+    """Row order that puts the two halves of every RoPE pair side by side: within each 128-row head, rows
+    0, 64, 1, 65, ... (reference ``src/ittai/qwen3/engine.py:13-14``).
 
     Kept for callers that import it; this build stores Q/K rows in the eager order and rotates (i, i + 64) directly."""
-    return np.concatenate([[hh * HD + i, hh * HD + i + HD // 2] for hh in range(n_heads) for i in range(HD // 2)])
+    within = np.stack([np.arange(HD // 2), np.arange(HD // 2) + HD // 2], axis=1).reshape(-1)
+    return (np.arange(n_heads)[:, None] * HD + within[None, :]).reshape(-1)
 
 
-def build_tasks(seqlens, *unused):
-    """Host description of one packed forward: per-token positions, sequence ids and cache rows, and the per-sequence
-    (first row, rows, first key row, key rows) records the attention kernel walks.
-
-    The reference's ``build_tasks`` (``src/ittai/qwen3/engine.py:17-84``) emits a flat task list with dependency flags
-    for its single persistent kernel; here every phase is its own launch inside one CUDA graph, so the "task list" is
-    just the packing metadata.  Extra positional arguments of the reference's signature are accepted and ignored.
+def packing(seqlens):
+    """Host description of one packed forward for the kernels: per-token positions, sequence ids and cache rows, and the
+    per-sequence (first row, rows, first key row, key rows) records the attention kernel walks.
     Returns (pos, seq, slot, seqs, T) as int32 numpy arrays."""
     seqlens = [int(x) for x in seqlens]
     cu = np.concatenate([[0], np.cumsum(seqlens)]).astype(np.int64)
@@ -112,7 +111,7 @@ class Engine:
         """Packing metadata, cached per tuple of lengths like the reference's task lists (``engine.py:144-151``)."""
         key = tuple(seqlens)
         if key not in self._meta:
-            pos, seq, slot, seqs, T = build_tasks(seqlens)
+            pos, seq, slot, seqs, T = packing(seqlens)
             dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
             self._meta[key] = (dev(pos), dev(seq), dev(slot), dev(seqs), dev(seqs[:, 0] + seqs[:, 1] - 1), T)
         return self._meta[key]
@@ -162,3 +161,10 @@ class Engine:
 
     def check(self) -> None:
         ops.check_status(self.core.status)
+
+    def task_list(self, seqlens, group_m=8):
+        """The forward over ``seqlens`` as the reference's device queue would see it: ``(tasks, expect, T)`` of
+        ``build_tasks`` for this engine's geometry (256-column GEMM tiles, one arrival per tile).  The launches this
+        engine records into its CUDA graph realise the same dependencies by stream order, phase after phase; the list
+        is what a single persistent kernel would walk instead."""
+        return build_tasks(seqlens, self.M // BM, self.Bmax, self.L + 1, (DQKV // 256, D // 256, 2 * FF // 256, D // 256), 1, 128, group_m)

@@ -14,6 +14,24 @@ import torch
 from .. import _C, ops
 
 
+def fold_ln(W, b, g, beta, dtype=torch.bfloat16):
+    """LayerNorm folded into the Linear that follows it, under the reference's name and return order
+    (``src/ittai/siglip/kernel.py:523-525``): ``(W' = W * gain in `dtype`, row sums of the rounded W' in fp32,
+    b' = b + W beta in fp32)``."""
+    wp, bias, sums = ops.fold_layernorm(W, b, g, beta)
+    return wp.to(dtype), sums, bias
+
+
+def gemm_tasks(op, l, nm, nn, group_m):
+    """``(op, layer, row block, column tile)`` of one GEMM in queue order: row blocks in groups of ``group_m``, and inside a
+    group the column tile outermost, so that neighbouring tasks share a weight tile (reference ``kernel.py:528-529``)."""
+    order = []
+    for first in range(0, nm, group_m):
+        rows = range(first, min(first + group_m, nm))
+        order.extend((op, l, i, j) for j in range(nn) for i in rows)
+    return order
+
+
 def _vision_model(m):
     return m.vision_model if hasattr(m, "vision_model") else m
 

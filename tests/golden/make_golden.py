@@ -99,7 +99,43 @@ def siglip():
     print("siglip", out32.pooler_output[0, :4])
 
 
+TASK_CASES = {          # name -> (seqlens, MB_alloc, Bmax, n_tiles, spt, kv block, group_m)
+    "single_short": ([37], 1, 1, (32, 8, 48, 8), 1, 64, 8),
+    "ragged": ([300, 5, 129, 1, 64], 4, 8, (32, 8, 48, 8), 1, 64, 8),
+    "straddling_sm90": ([100, 100, 100, 100, 100], 8, 8, (16, 4, 24, 4), 2, 128, 16),
+    "one_block_each": ([128, 128, 128], 3, 4, (32, 8, 48, 8), 1, 64, 2),
+    "long": ([1000, 1048], 16, 2, (16, 4, 24, 4), 2, 128, 8),
+}
+
+
+def qwen3_tasks():
+    """Task lists of the reference's own ``build_tasks`` for a handful of packings.
+
+    The reference's engine module cannot be imported here (its kernels need a newer CuTe DSL than this image has), but
+    ``build_tasks`` is plain numpy: the function's source is taken out of ``src/ittai/qwen3/engine.py`` with ``ast`` and
+    executed against the reference's own ``config.py``.  Stored: every case's T, the SHA-256 of its task and expect arrays,
+    and the arrays themselves for the smaller cases."""
+    import ast
+    import hashlib
+    import numpy as np
+    root = os.environ.get("ITTAI_REFERENCE", "/root/reference")
+    ns = {"np": np}
+    exec(compile(open(os.path.join(root, "src/ittai/qwen3/config.py")).read(), "config.py", "exec"), ns)
+    src = open(os.path.join(root, "src/ittai/qwen3/engine.py")).read()
+    fn = [n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == "build_tasks"][0]
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), "engine.py", "exec"), ns)
+    out = {}
+    for name, (lens, mb, bmax, tiles, spt, kvb, gm) in TASK_CASES.items():
+        tasks, expect, T = ns["build_tasks"](lens, mb, bmax, ns["L"] + 1, tiles, spt, kvb, gm)
+        out[name + "__T"] = np.int64(T)
+        out[name + "__sha"] = np.frombuffer(hashlib.sha256(tasks.astype(np.int32).tobytes() + expect.astype(np.int32).tobytes()).digest(), dtype=np.uint8)
+        if len(tasks) < 20000:
+            out[name + "__tasks"], out[name + "__expect"] = tasks.astype(np.int32), expect.astype(np.int32)
+        print(name, tasks.shape, expect.shape, T)
+    np.savez_compressed(os.path.join(HERE, "qwen3_tasks.npz"), **out)
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["qwen3_tiny", "qwen3_full", "siglip"]
+    which = sys.argv[1:] or ["qwen3_tiny", "qwen3_full", "siglip", "qwen3_tasks"]
     for w in which:
         globals()[w]()

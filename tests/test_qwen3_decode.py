@@ -247,10 +247,12 @@ def test_full_model_config1(full_hf, golden_dir):
 
 
 @gpu
-def test_long_context_against_eager_on_device(full_hf):
+def test_long_context_against_eager_on_device(full_hf, golden_dir):
     """BASELINE config 2 shape: 4096-id prompt (seed 1), capacity 8192, then teacher-forced steps; the checker is the
-    eager model run on the same GPU."""
+    eager model run on the same GPU.  The max-abs gate is the distance between the eager model's own variants recorded
+    in the config-1 fixture."""
     from ittai_b200.qwen3 import Qwen3Decoder
+    lim_abs = max(v["full_max_abs"] for v in _load(golden_dir, "qwen3_full_c1.pt")["variant_distance"].values())
     ids = hf.prompt_ids(4096, seed=1)
     m = full_hf.to("cuda")
     try:
@@ -270,8 +272,8 @@ def test_long_context_against_eager_on_device(full_hf):
     wl = want_logits.float()
     cos = F.cosine_similarity(logits, wl, dim=-1).min().item()
     err = (logits - wl).abs().max().item()
-    print(dict(cos=cos, max_abs=err, picks=picks, want=want_ids.tolist()))
-    assert cos >= 0.9995 and err <= 0.09
+    print(dict(cos=cos, max_abs=err, floor=lim_abs, picks=picks, want=want_ids.tolist()))
+    assert cos >= 0.9995 and err <= lim_abs
     assert d.pos.tolist() == [4096 + 7]
     kc = d.kcache[hf.FULL.n_layers - 1, 0, :, :4096 + 7].float().cpu()
     assert F.cosine_similarity(kc.flatten(), k_last[:, :4096 + 7].flatten(), dim=0) >= 0.999

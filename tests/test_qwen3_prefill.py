@@ -9,9 +9,10 @@ from oracle import qwen3_ref as ref
 gpu = pytest.mark.gpu
 
 
-def test_build_tasks_metadata():
-    from ittai_b200.qwen3 import build_tasks, rope_perm
-    pos, seq, slot, seqs, T = build_tasks([3, 1, 4])
+def test_packing_metadata():
+    from ittai_b200.qwen3 import rope_perm
+    from ittai_b200.qwen3.engine import packing
+    pos, seq, slot, seqs, T = packing([3, 1, 4])
     assert T == 8 and pos.tolist() == [0, 1, 2, 0, 0, 1, 2, 3] and slot.tolist() == list(range(8)) and not seq.any()
     assert seqs.tolist() == [[0, 3, 0, 3], [3, 1, 3, 1], [4, 4, 4, 4]]
     p = rope_perm(2)
