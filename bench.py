@@ -107,9 +107,18 @@ class ClockSampler:
 
 
 SIGLIP_BATCH = 64
-# dram__bytes_read.sum + dram__bytes_write.sum of q3_decode_kernel<1> per decoded token at cache length 4096, from the ncu
-# capture of an 8-token launch summarised under profiles/ (traffic grows with tokens, so it is scaled by the step's 256)
-NCU_DRAM_BYTES_PER_TOKEN = (13.296941e9 + 20.676864e6) / 8
+
+
+def ncu_traffic_per_token():
+    """DRAM bytes (read + write) of the decode kernel per decoded token from the last ncu capture, or None.  The figures
+    sit in a small JSON beside the capture's summary, with the commit they were measured at: traffic grows with the
+    tokens of a launch, so the bench scales the per-token figure by its own 256."""
+    path = os.path.join(ROOT, "profiles", "qwen3_decode_kernel_b1_ctx4096.traffic.json")
+    try:
+        t = json.load(open(path))
+        return (t["dram_bytes_read"] + t["dram_bytes_write"]) / t["tokens_per_launch"], t.get("measured_at_commit")
+    except (OSError, KeyError, ValueError):
+        return None, None
 
 
 def siglip_leg(dev, rank, barrier, iters: int = 20):
@@ -140,8 +149,74 @@ def siglip_leg(dev, rank, barrier, iters: int = 20):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(); eng.forward(inp); b.record(); torch.cuda.synchronize()
         singles.append(a.elapsed_time(b))
+    # end to end: pixels from pinned host memory, embeddings back to pinned host memory, both inside the timed region
+    host_px = px.cpu().pin_memory()
+    dev_px = torch.empty_like(px)
+    host_out = torch.empty(SIGLIP_BATCH, eng.D, dtype=torch.bfloat16).pin_memory()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(iters):
+        dev_px.copy_(host_px, non_blocking=True)
+        host_out.copy_(eng.forward({"pixel_values": dev_px}), non_blocking=True)
+    f1.record()
+    barrier()
+    eng.check()
     return {"ms": e0.elapsed_time(e1), "iters": iters, "median_single_ms": sorted(singles)[iters // 2], "images": iters * SIGLIP_BATCH, "flops_reference_formula": iters * eng.flops("reference"),
-            "launches_per_forward": 2 + 12 * 5 + 6}
+            "launches_per_forward": 2 + 12 * 5 + 6, "e2e_ms": f0.elapsed_time(f1), "h2d_bytes": host_px.numel() * 4, "d2h_bytes": host_out.numel() * 2}
+
+
+def config4_leg(sd, dev, barrier):
+    """BASELINE config 4 on one GPU: eight 2048-token prompts (seed 4) prefilled on the tensor cores, then batch-8 greedy
+    decode with the caches at length 2048 and at 8192 - 32 (filled with N(0,1) rows up to there: a decode step's cost
+    depends on the cache length, not its contents).  Prefill FLOPs by the reference's formula (benchmarks/qwen3.py:35),
+    decode bytes as weights + 8 caches."""
+    from ittai_b200.qwen3 import Qwen3Decoder, decode_bytes_per_token
+    from ittai_b200.qwen3.config import D, DGU, DQ, DQKV, FF, L
+    B, T, STEPS = 8, 2048, 32
+    dec = Qwen3Decoder(sd, max_batch=B, kv_capacity=CAP, device=dev)
+    g = torch.Generator().manual_seed(4)
+    prompts = torch.randint(0, dec.V, (B, T), generator=g, dtype=torch.int32)
+    out = {}
+    times = []
+    for it in range(4):
+        dec.reset()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        dec.prefill_cache(prompts)
+        b.record()
+        barrier()
+        times.append(a.elapsed_time(b))
+    ms = sorted(times[1:])[1]
+    flops = L * (2 * B * T * D * (DQKV + DQ + DGU + FF) + 2 * B * T * T * DQ)
+    out["prefill"] = {"tokens": B * T, "ms": ms, "tok_per_s": B * T / (ms / 1e3), "tflops_reference_formula": flops / (ms / 1e3) / 1e12}
+    first = torch.randint(0, dec.V, (B,), generator=g, dtype=torch.int32).to(dev)
+    weights = decode_bytes_per_token(0)
+    kv_row = decode_bytes_per_token(1) - weights
+    for ctx in (T, CAP - STEPS):
+        if ctx > T:
+            dec.kcache[:, :, :, T:ctx].normal_()
+            dec.vcache[:, :, :, T:ctx].normal_()
+        times = []
+        for it in range(4):
+            dec.rewind(ctx)
+            dec.next_id.copy_(first)
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dec.decode(STEPS, check=False)
+            b.record()
+            barrier()
+            times.append(a.elapsed_time(b))
+        dec.check_status()
+        ms = sorted(times[1:])[1]
+        bytes_step = weights + B * kv_row * (ctx + (STEPS - 1) / 2)
+        out[f"decode_ctx{ctx}"] = {"batch": B, "steps": STEPS, "us_per_step": ms * 1e3 / STEPS, "tok_per_s": B * STEPS / (ms / 1e3),
+                                   "bytes_per_step": bytes_step, "GBs": bytes_step * STEPS / (ms / 1e3) / 1e9}
+    del dec
+    torch.cuda.empty_cache()
+    return out
 
 
 def cpu_reference(steps: int, warmup: int):
@@ -175,6 +250,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
     ap.add_argument("--no-siglip", action="store_true", help="skip the SigLIP images/s leg")
+    ap.add_argument("--no-config4", action="store_true", help="skip the 2048-token prefill + batch-8 decode leg (1 GPU only)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -203,8 +279,7 @@ def main():
     first = dec.prefill(prompt).clone()          # outside the timed region: cache resident in HBM
 
     def rewind():
-        dec.pos.fill_(PROMPT)
-        dec.lengths = [PROMPT]
+        dec.rewind(PROMPT)
         dec.next_id.copy_(first)
 
     def barrier():
@@ -213,9 +288,10 @@ def main():
         torch.cuda.synchronize(dev)
 
     launches = 0
+    ids_seen = []
     for _ in range(warmup):
         rewind()
-        dec.decode(DECODE)
+        ids_seen.append(dec.decode(DECODE).clone())
     # ---- device-resident timing ------------------------------------------------------------------------
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
@@ -225,12 +301,15 @@ def main():
         for k in range(args.steps):
             rewind()
             ev[k][0].record()
-            dec.decode(DECODE, check=False)
+            ids_seen.append(dec.decode(DECODE, check=False))
             ev[k][1].record()
             launches += 1
         t1.record()
         barrier()
     dec.check_status()
+    # every timed step decodes the same 256 tokens from the same state: the ids have to repeat exactly
+    if not all(torch.equal(ids_seen[0], x) for x in ids_seen[1:]):
+        raise SystemExit("decode steps that start from the same state returned different ids")
     total_ms = t0.elapsed_time(t1)
     kern_ms = [a.elapsed_time(b) for a, b in ev]
     # per-token times of one more run (device globaltimer stamps)
@@ -244,8 +323,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for k in range(args.steps):
-        dec.pos.fill_(PROMPT)
-        dec.lengths = [PROMPT]
+        dec.rewind(PROMPT)
         dec.next_id.copy_(host_in, non_blocking=True)
         out = dec.decode(DECODE, check=False)
         host_out.copy_(out, non_blocking=True)
@@ -255,9 +333,14 @@ def main():
     dec.check_status()
     e2e_ms = e0.elapsed_time(e1)
 
+    c4 = None
+    if world == 1 and not args.no_config4:
+        del dec
+        torch.cuda.empty_cache()
+        c4 = config4_leg(synthetic_state_dict(seed=rank, device=dev), dev, barrier)
     sig = siglip_leg(dev, rank, barrier) if not args.no_siglip else None
-    (total_ms, e2e_ms, sig_ms), toks = replicas.aggregate([total_ms, e2e_ms, sig["ms"] if sig else 0.0],
-                                                          units=args.steps * DECODE, device=dev)
+    (total_ms, e2e_ms, sig_ms, sig_e2e_ms), toks = replicas.aggregate(
+        [total_ms, e2e_ms, sig["ms"] if sig else 0.0, sig["e2e_ms"] if sig else 0.0], units=args.steps * DECODE, device=dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -268,6 +351,7 @@ def main():
     mean_bytes = sum(decode_bytes_per_token(PROMPT + i) for i in range(DECODE)) / DECODE
     kern_ms_avg = sum(kern_ms) / len(kern_ms)
     achieved = mean_bytes * DECODE / (kern_ms_avg / 1e3) / 1e9
+    ncu_tok, ncu_commit = ncu_traffic_per_token()
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -278,8 +362,9 @@ def main():
         "us_per_token": {"median": float(per_tok_us.median()), "p99": float(per_tok_us.quantile(0.99)),
                          "mean_kernel": kern_ms_avg * 1e3 / DECODE},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_TOKEN * DECODE / 1e9,
-                     "traffic_unit": "GB per launch (ncu dram read+write of an 8-token launch, scaled by tokens)", "peak_kind": peak_kind,
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": ncu_tok * DECODE / 1e9 if ncu_tok else None,
+                     "traffic_unit": f"GB per launch (ncu dram read+write of an 8-token launch at commit {ncu_commit}, scaled by tokens)",
+                     "peak_kind": peak_kind,
                      "frac_of_nominal_8TBs": achieved / 8000.0, "bytes_per_token": mean_bytes},
         "e2e": {"value": toks / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * DECODE},
         "gpu_launches": launches,
@@ -297,10 +382,25 @@ def main():
                                        "single_forward": {"ms": sig["median_single_ms"], "frac": sig["flops_reference_formula"] / sig["iters"] / (sig["median_single_ms"] / 1e3) / 1e12 / peaks["bf16_tflops"],
                                                           "timing": "median of 20 forwards timed one by one, the reference benchmark's protocol"},
                                        "flops": "reference benchmark formula: B*L*(2*S*D*(4D+2F) + 4*S*S*D)"},
-                          "gpu_launches_per_forward": sig["launches_per_forward"]}
+                          "gpu_launches_per_forward": sig["launches_per_forward"],
+                          "e2e": {"value": world * sig["images"] / (sig_e2e_ms / 1e3), "unit": "img/s", "h2d_bytes_per_step": sig["h2d_bytes"],
+                                  "d2h_bytes_per_step": sig["d2h_bytes"], "step": "one batch of 64 images: pixels from pinned host memory, embeddings back"}}
+    if c4:
+        tf = c4["prefill"]["tflops_reference_formula"]
+        c4["prefill"]["roofline"] = {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind}
+        for k, v in c4.items():
+            if k.startswith("decode"):
+                v["roofline"] = {"bound": "hbm", "achieved": v["GBs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": v["GBs"] / peaks["hbm_gbs"],
+                                 "frac_of_nominal_8TBs": v["GBs"] / 8000.0, "peak_kind": peak_kind}
+        line["config4"] = dict(c4, workload="qwen3-0.6b random-init bf16: eight 2048-token prompts prefilled, then batch-8 greedy decode at cache length 2048 and 8160")
     if not args.no_cpu_baseline and world == 1:
-        r, sample = cpu_reference(8, 2)
+        r, sample = cpu_reference(16, 2)
         line["cpu_baseline"] = {"value": r["tok_s"], "unit": UNIT, "cores": r["threads"], "kind": "reference", "sample": sample}
+        if sig:
+            from oracle import siglip_hf
+            c = siglip_hf.time_cpu(SIGLIP_BATCH, iters=2)
+            line["siglip"]["cpu_baseline"] = {"value": c["img_s"], "unit": "img/s", "cores": c["threads"], "kind": "reference",
+                                              "sample": f"2 eager bf16 forwards of one batch of {SIGLIP_BATCH} images on host cores after 1 warm-up"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -42,8 +42,7 @@ def main():
     first = torch.randint(0, dec.V, (a.batch,), generator=g, dtype=torch.int32).cuda()
 
     def rewind():
-        dec.pos.fill_(a.ctx)
-        dec.lengths = [a.ctx] * a.batch
+        dec.rewind(a.ctx)
         dec.next_id.copy_(first)
 
     times = []

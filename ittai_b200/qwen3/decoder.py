@@ -143,6 +143,21 @@ class Qwen3Decoder:
         self.lengths = [0] * self.B
         self._unchecked = 0
 
+    def rewind(self, length: int) -> None:
+        """Set every sequence's cache length to ``length``: rows from there on stay in memory but are no longer attended
+        and will be overwritten (benchmarks replay the same decode steps from one prefilled state)."""
+        if not 0 <= length <= self.cap:
+            raise ValueError(f"length {length} outside 0..{self.cap}")
+        self.pos.fill_(length)
+        self.lengths = [length] * self.B
+        self._unchecked = 0
+
+    def prefill_cache(self, ids) -> None:
+        """Append prompts ``ids`` ([B, n] ints) to the caches with the tensor-core prefill only: no logits, no first id
+        (``prefill`` adds the decode step that yields them)."""
+        ids = torch.as_tensor(ids, dtype=torch.int32)
+        self._prefill_dense(ids[None] if ids.dim() == 1 else ids)
+
     def _launch(self, n_steps, forced=None, timed=False, check=True):
         if max(self.lengths) + self._unchecked + n_steps > self.cap:
             raise ValueError(f"KV capacity {self.cap} exceeded: {max(self.lengths) + self._unchecked} cached + {n_steps} steps")

@@ -32,6 +32,24 @@ def gemm_tasks(op, l, nm, nn, group_m):
     return order
 
 
+def resize_positions(grid: torch.Tensor, shapes, max_len: int) -> torch.Tensor:
+    """Position rows of variable-resolution (NaFlex) images: the learned ``[side, side, D]`` grid resized to every image's
+    ``(height, width)`` patch grid (bilinear, antialiased, in fp32), flattened row-major and padded to ``max_len`` rows with
+    the image's first row, as the eager embedding module does and the reference's ``_prepare`` restates
+    (``src/ittai/siglip/kernel.py:638-649``).  ``grid``: fp32 ``[side, side, D]``; returns fp32 ``[B, max_len, D]``."""
+    g = grid.permute(2, 0, 1)[None].float()
+    shapes = [tuple(int(v) for v in hw) for hw in shapes]
+    out = torch.empty(len(shapes), max_len, grid.shape[-1], dtype=torch.float32, device=grid.device)
+    for hw in set(shapes):
+        if hw[0] < 1 or hw[1] < 1 or hw[0] * hw[1] > max_len:
+            raise ValueError(f"patch grid {hw} does not fit {max_len} positions")
+        rows = torch.nn.functional.interpolate(g, size=hw, mode="bilinear", align_corners=False, antialias=True)[0].flatten(1).t()
+        idx = [k for k, v in enumerate(shapes) if v == hw]
+        out[idx, :len(rows)] = rows
+        out[idx, len(rows):] = rows[0]
+    return out
+
+
 def _vision_model(m):
     return m.vision_model if hasattr(m, "vision_model") else m
 
@@ -45,11 +63,12 @@ class Engine:
     def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True, fold_ln=True):
         vm = _vision_model(vm)
         cfg, emb = vm.config, vm.embeddings
-        if not isinstance(emb.patch_embedding, torch.nn.Conv2d):
-            raise NotImplementedError("variable-resolution (NaFlex) patch embedding is not built; fixed-resolution Conv2d towers only")
+        # Conv2d patch embedding: fixed resolution.  Linear: SigLIP2 NaFlex, whose inputs arrive as patch rows with a
+        # validity mask and a per-image patch grid (reference ``:574-578, 638-649``).
+        self.conv = isinstance(emb.patch_embedding, torch.nn.Conv2d)
         self.vm, self.B = vm, B
         self.D, self.F, self.H, self.L = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_hidden_layers
-        self.p, self.eps, self.img = cfg.patch_size, cfg.layer_norm_eps, cfg.image_size
+        self.p, self.eps, self.img = cfg.patch_size, cfg.layer_norm_eps, getattr(cfg, "image_size", 0)
         self.hd = self.D // self.H
         self.S0 = emb.num_patches
         if self.hd != 64 or self.D % 128 or self.F % 128 or (3 * self.p * self.p) % 64:
@@ -62,7 +81,12 @@ class Engine:
         f32 = lambda t: t.detach().to(dev, torch.float32).contiguous()
         self.wpe, self.bpe = bf(emb.patch_embedding.weight.reshape(D, -1)), f32(emb.patch_embedding.bias)
         # position table repeated per image: the patch-embedding GEMM adds it as its residual (reference :569-571)
-        self.pos = bf(emb.position_embedding.weight).repeat(B, 1)
+        if self.conv:
+            self.pos = bf(emb.position_embedding.weight).repeat(B, 1)
+        else:
+            side = int(round(S ** 0.5))
+            self.pos_grid = f32(emb.position_embedding.weight).reshape(side, side, D)
+            self.pos = torch.zeros(M, D, dtype=torch.bfloat16, device=dev)
         self.layers = []
         for lyr in vm.encoder.layers:
             a, m = lyr.self_attn, lyr.mlp
@@ -95,7 +119,7 @@ class Engine:
         self.hln = (f32(h.layernorm.weight), f32(h.layernorm.bias))
         self.hw1, self.hb1, self.hw2, self.hb2 = bf(h.mlp.fc1.weight), f32(h.mlp.fc1.bias), bf(h.mlp.fc2.weight), f32(h.mlp.fc2.bias)
         z = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)
-        self.pixels = torch.empty(B, 3, self.img, self.img, dtype=torch.float32, device=dev)
+        self.pixels = torch.empty(B, 3, self.img, self.img, dtype=torch.float32, device=dev) if self.conv else None
         self.patches, self.x, self.y = z(M, 3 * self.p * self.p), z(M, D), z(M, D)
         self.qkv, self.attn, self.h = z(M, 3 * D), z(M, D), z(M, self.F)
         self.kv, self.pool_a, self.pool_r, self.pool_y, self.pool_h = z(M, 2 * D), z(B, D), z(B, D), z(B, D), z(B, self.F)
@@ -112,9 +136,13 @@ class Engine:
     def _body(self):
         D, S, B, H, hd, eps = self.D, self.S0, self.B, self.H, self.hd, self.eps
         L, st = _C.lib(), self.status
-        _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p,
-                                       ops._stream(self.pixels)))
+        if self.conv:
+            _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p,
+                                           ops._stream(self.pixels)))
         fold = self.fold_ln
+        # with variable-resolution inputs an image's keys are its first key_len rows (the records in `seqs` say how many)
+        # and may number 256: more than the tensor-memory kernel's 224, so those towers run the register-tile kernel
+        kv_max = S if self.conv else 0
         ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m if fold else None)
         for w in self.layers:
             if fold:
@@ -124,7 +152,8 @@ class Engine:
                 ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
             ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
                           causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
-                          o_strides=(D, hd), max_kv_len=S, q_rows_total=self.M, kv_rows_total=self.M, status=st)
+                          o_strides=(D, hd), max_kv_len=kv_max, q_rows_total=self.M if self.conv else 0,
+                          kv_rows_total=self.M if self.conv else 0, status=st if self.conv else None)
             ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x, stats_out=self.stats_a if fold else None)
             if fold:
                 ops.gemm(self.x, w["fc1_f"][0], st, bias=w["fc1_f"][1], epi=_C.EPI_GELU, out=self.h, row_stats=self.stats_a, col_sums=w["fc1_f"][2],
@@ -149,12 +178,28 @@ class Engine:
 
     @torch.no_grad()
     def forward(self, inp):
-        """``inp["pixel_values"]``: ``[B, 3, H, W]`` on any device; copied into the engine's buffer, then one graph replay."""
-        if "spatial_shapes" in inp:
-            raise NotImplementedError("variable-resolution (NaFlex) inputs are not built")
+        """``inp["pixel_values"]``: ``[B, 3, H, W]`` on any device; copied into the engine's buffer, then one graph replay.
+        A NaFlex tower takes ``pixel_values`` ``[B, S, 3 p p]`` (patch rows), ``pixel_attention_mask`` ``[B, S]`` (valid rows
+        first) and ``spatial_shapes`` ``[B, 2]``, like the reference's engine (``:638-649``)."""
         px = inp["pixel_values"]
-        assert tuple(px.shape) == tuple(self.pixels.shape), f"expected {tuple(self.pixels.shape)}, got {tuple(px.shape)}"
-        self.pixels.copy_(px, non_blocking=True)
+        if self.conv:
+            if "spatial_shapes" in inp:
+                raise ValueError("this tower has a fixed-resolution patch embedding; it takes [B, 3, H, W] pixels only")
+            assert tuple(px.shape) == tuple(self.pixels.shape), f"expected {tuple(self.pixels.shape)}, got {tuple(px.shape)}"
+            self.pixels.copy_(px, non_blocking=True)
+        else:
+            S = self.S0
+            assert tuple(px.shape) == (self.B, S, self.patches.shape[1]), f"expected {(self.B, S, self.patches.shape[1])}, got {tuple(px.shape)}"
+            mask, shapes = inp["pixel_attention_mask"], inp["spatial_shapes"]
+            key_len = mask.to(torch.int64).sum(1).cpu()
+            area = torch.as_tensor(shapes).to(torch.int64).cpu().prod(1)
+            if not torch.equal(key_len, area) or int(key_len.min()) < 1:
+                raise ValueError("pixel_attention_mask must mark exactly height * width leading rows of every image")
+            self.patches.copy_(px.reshape(self.M, -1), non_blocking=True)
+            self.pos.copy_(resize_positions(self.pos_grid, torch.as_tensor(shapes).tolist(), S).reshape(self.M, -1))
+            kl = key_len.to(torch.int32).to(self.dev, non_blocking=True)
+            self.seqs[:, 3].copy_(kl)
+            self.pool_seqs[:, 3].copy_(kl)
         if self.graph is None:
             self.status.zero_()
             s = torch.cuda.Stream()
@@ -193,7 +238,7 @@ class Siglip2Embedder:
     (``None`` without a checkpoint), ``.vm``, ``.engine``; ``.embed(pixel_values)`` batches and pads like the reference's
     ``embed`` (``:715-723``: the last batch repeats its final image)."""
 
-    def __init__(self, model_id="google/siglip2-base-patch16-224", batch_size=64, device="cuda"):
+    def __init__(self, model_id="google/siglip2-base-patch16-naflex", batch_size=64, device="cuda"):
         self.processor = None
         if isinstance(model_id, str):
             from transformers import AutoImageProcessor, AutoModel
@@ -205,11 +250,19 @@ class Siglip2Embedder:
 
     @torch.no_grad()
     def embed(self, images):
-        """``images``: fp32 ``[N, 3, H, W]`` pixel values, or PIL images when a processor is loaded."""
-        px = images if torch.is_tensor(images) else self.processor(images=images, return_tensors="pt")["pixel_values"]
+        """``images``: fp32 ``[N, 3, H, W]`` pixel values, a dict of processor outputs (NaFlex: ``pixel_values``,
+        ``pixel_attention_mask``, ``spatial_shapes``), or PIL images when a processor is loaded."""
+        if torch.is_tensor(images):
+            inp = {"pixel_values": images}
+        elif isinstance(images, dict):
+            inp = dict(images)
+        else:
+            inp = dict(self.processor(images=images, return_tensors="pt"))
+        total = len(inp["pixel_values"])
         out = []
-        for k in range(0, len(px), self.B):
-            n = min(self.B, len(px) - k)
-            batch = torch.cat([px[k:k + n], px[k + n - 1:k + n].expand(self.B - n, *px.shape[1:])])
-            out.append(self.engine.forward({"pixel_values": batch})[:n].clone())
+        for k in range(0, total, self.B):
+            n = min(self.B, total - k)
+            # a short last batch is filled up with copies of its final image (reference ``:720-723``)
+            fill = lambda t: torch.cat([t[k:k + n], t[k + n - 1:k + n].expand(self.B - n, *t.shape[1:])])
+            out.append(self.engine.forward({name: fill(t) for name, t in inp.items()})[:n].clone())
         return torch.cat(out)

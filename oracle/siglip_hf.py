@@ -43,3 +43,28 @@ def time_cpu(batch: int, iters: int = 3, threads: int | None = None):
         m(pixel_values=px)
     dt = (time.perf_counter() - t0) / iters
     return dict(img_s=batch / dt, ms=dt * 1e3, threads=threads, batch=batch)
+
+
+def build_hf_naflex(seed: int = 2, dtype=torch.bfloat16, device="cpu", n_layers: int = 12, num_patches: int = 256):
+    """Random-init ``Siglip2VisionModel`` at the base geometry: the variable-resolution (NaFlex) tower the reference's
+    wrapper loads by default (``src/ittai/siglip/kernel.py:672``): Linear patch embedding over 16 x 16 x 3 patch rows, a
+    16 x 16 learned position grid resized per image, key masks in every attention."""
+    from transformers import Siglip2VisionConfig, Siglip2VisionModel
+
+    cfg = Siglip2VisionConfig(hidden_size=768, intermediate_size=3072, num_hidden_layers=n_layers, num_attention_heads=12,
+                              num_patches=num_patches, patch_size=16, hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6)
+    torch.manual_seed(seed)
+    model = Siglip2VisionModel(cfg).to(dtype).eval()
+    return model.to(device) if device != "cpu" else model
+
+
+def naflex_inputs(shapes, num_patches: int = 256, seed: int = 3):
+    """Patch rows of images with the given (height, width) patch grids: N(0, 1) values for the valid rows, zeros after."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    B = len(shapes)
+    px = torch.zeros(B, num_patches, 3 * 16 * 16)
+    mask = torch.zeros(B, num_patches, dtype=torch.int64)
+    for b, (h, w) in enumerate(shapes):
+        px[b, :h * w] = torch.randn(h * w, 3 * 16 * 16, generator=g)
+        mask[b, :h * w] = 1
+    return {"pixel_values": px, "pixel_attention_mask": mask, "spatial_shapes": torch.tensor(shapes, dtype=torch.int64)}
