@@ -99,10 +99,9 @@ def test_naflex_engine_against_eager_on_device():
     vm = hf.build_hf_naflex(seed=2, device="cuda")
     inp = hf.naflex_inputs(NAFLEX_SHAPES, seed=3)
     with torch.no_grad():
-        want = vm(pixel_values=inp["pixel_values"].cuda().to(torch.bfloat16), attention_mask=inp["pixel_attention_mask"].cuda(),
+        want = vm(pixel_values=inp["pixel_values"].cuda().to(torch.bfloat16), pixel_attention_mask=inp["pixel_attention_mask"].cuda(),
                   spatial_shapes=inp["spatial_shapes"].cuda()).pooler_output.float().cpu()
-        want32 = hf.build_hf_naflex(seed=2, dtype=torch.float32)(pixel_values=inp["pixel_values"], attention_mask=inp["pixel_attention_mask"],
-                                                                 spatial_shapes=inp["spatial_shapes"]).pooler_output
+        want32 = hf.build_hf_naflex(seed=2, dtype=torch.float32)(**inp).pooler_output
     emb = Siglip2Embedder(vm, batch_size=len(NAFLEX_SHAPES))
     out = emb.embed(inp).float().cpu()
     emb.engine.check()
@@ -112,7 +111,7 @@ def test_naflex_engine_against_eager_on_device():
     # other shapes through the same engine (the graph is replayed; only the records and the position rows change)
     inp2 = hf.naflex_inputs(NAFLEX_SHAPES[::-1], seed=5)
     with torch.no_grad():
-        want2 = vm(pixel_values=inp2["pixel_values"].cuda().to(torch.bfloat16), attention_mask=inp2["pixel_attention_mask"].cuda(),
+        want2 = vm(pixel_values=inp2["pixel_values"].cuda().to(torch.bfloat16), pixel_attention_mask=inp2["pixel_attention_mask"].cuda(),
                    spatial_shapes=inp2["spatial_shapes"].cuda()).pooler_output.float().cpu()
     out2 = emb.embed(inp2).float().cpu()
     assert F.cosine_similarity(out2, want2, dim=-1).min() >= 0.9995
