@@ -21,18 +21,7 @@ sys.path.insert(0, ROOT)
 
 from bench import measured_peaks, synthetic_state_dict  # noqa: E402
 from ittai_b200.qwen3 import D, DGU, DQ, DQKV, FF, Qwen3Embedder  # noqa: E402
-
-
-def median_ms(fn, iters=20):
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    ts = []
-    for _ in range(iters):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); fn(); e.record(); torch.cuda.synchronize()
-        ts.append(s.elapsed_time(e))
-    return sorted(ts)[iters // 2]
+from benchmarks._timing import median_ms  # noqa: E402
 
 
 def main():

@@ -3,7 +3,9 @@
 tower (``:33``).  The reference's inputs (a hub checkpoint and one COCO image) are not available offline, so the tower
 is the ViT-B/16-224 configuration with seeded random weights and the pixels are N(0, 1) (seed 3).
 
-  python benchmarks/siglip.py [batch=64] [--ours-only]
+  python benchmarks/siglip.py [batch=64] [--ours-only] [--per-op]
+
+``--per-op`` prints the timings of one encoder layer's kernels instead (each repeated inside one CUDA graph).
 """
 import json
 import os
@@ -17,22 +19,41 @@ sys.path.insert(0, ROOT)
 from bench import measured_peaks  # noqa: E402
 from ittai_b200.siglip.kernel import Siglip2Embedder  # noqa: E402
 from oracle import siglip_hf as hf  # noqa: E402  (the eager tower is the comparison column, as in the reference script)
+from benchmarks._timing import graph_us, median_ms as ms  # noqa: E402
 
 
-def ms(fn, iters=20):
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    ts = []
-    for _ in range(iters):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); fn(); e.record(); torch.cuda.synchronize()
-        ts.append(s.elapsed_time(e))
-    return sorted(ts)[iters // 2]
+def per_op(B: int) -> None:
+    """Timings of one encoder layer's kernels at batch B, each repeated inside one CUDA graph."""
+    from ittai_b200 import ops
+    S, D, H = 196, 768, 12
+    M = B * S
+    st = ops.new_status("cuda")
+    x = torch.randn(M, D, device="cuda").bfloat16()
+    y = torch.empty_like(x)
+    gw, gb = torch.randn(D, device="cuda"), torch.randn(D, device="cuda")
+    print("layernorm  %.1f us" % graph_us(lambda: ops.layernorm_rows(x, gw, gb, 1e-6, out=y)))
+    qkv = torch.randn(M, 3 * D, device="cuda").bfloat16()
+    o = torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+    seqs = torch.tensor([[b * S, S, b * S, S] for b in range(B)], dtype=torch.int32, device="cuda")
+    print("attention  %.1f us" % graph_us(lambda: ops.attention(
+        qkv, qkv[:, D:], qkv[:, 2 * D:], o, seqs, n_heads=H, group=1, head_dim=64, causal=False, max_q_len=S, q_strides=(3 * D, 64),
+        k_strides=(3 * D, 64, 0), v_strides=(3 * D, 64, 0), o_strides=(D, 64), max_kv_len=S, q_rows_total=M, kv_rows_total=M, status=st)))
+    for n, k, epi, res in ((2304, 768, 0, False), (768, 768, 0, True), (3072, 768, 1, False), (768, 3072, 0, True)):
+        a = torch.randn(M, k, device="cuda").bfloat16()
+        w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+        bias = torch.randn(n, device="cuda")
+        r = torch.randn(M, n, device="cuda").bfloat16() if res else None
+        out = torch.empty(M, n, device="cuda", dtype=torch.bfloat16)
+        t = graph_us(lambda: ops.gemm(a, w, st, bias=bias, residual=r, epi=epi, out=out), 20)
+        print("gemm N=%d K=%d epi=%d res=%d  %.1f us  %.0f TF" % (n, k, epi, res, t, 2.0 * M * n * k / t / 1e6))
+    ops.check_status(st)
 
 
 def main():
     B = int(sys.argv[1]) if len(sys.argv) > 1 and sys.argv[1].isdigit() else 64
+    if "--per-op" in sys.argv:
+        per_op(B)
+        return
     vm = hf.build_hf(seed=2, device="cuda")
     emb = Siglip2Embedder(vm, batch_size=B)
     px = hf.pixels(B, seed=3).cuda()

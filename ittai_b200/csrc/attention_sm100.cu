@@ -40,15 +40,7 @@ struct AttnTcArgs {
     int group;
     float scale_log2;
     uint32_t* status;
-#ifdef ITTAI_ATTN_PROFILE
-    long long* clk;   // [CTAs][16] SM cycle stamps of the first softmax thread
-#endif
 };
-#ifdef ITTAI_ATTN_PROFILE
-#define ATTN_STAMP(i) do { if (threadIdx.x == 32) a.clk[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (i)] = clock64(); } while (0)
-#else
-#define ATTN_STAMP(i) do {} while (0)
-#endif
 
 __device__ __forceinline__ void mbar_arrive_cta(void* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -94,7 +86,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_keys = max(16, (kv_len + 15) & ~15);       // score columns / keys the MMAs cover
 
-    ATTN_STAMP(0);
     if (threadIdx.x == 0) {
         mbar_init(bar_load, 1); mbar_init(bar_s, 1); mbar_init(bar_mx, 256); mbar_init(bar_p, 256); mbar_init(bar_o, 1);
         mbar_init(bar_v, 1);
@@ -114,7 +105,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_after();
     pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
-    ATTN_STAMP(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -145,10 +135,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int q4 = warp & 3;                             // TMEM lane quarter this warp may touch
         const int r = q4 * 32 + lane;                        // query row inside the tile
         const bool live = mt * 128 + q4 * 32 < q_len;        // a warp whose 32 rows are all padding skips the arithmetic
-        ATTN_STAMP(2);
         bool ok = mbar_wait_abortable(bar_s, 0, abort_flag);
         if (!ok) break;
-        ATTN_STAMP(3);
         tc_fence_after();
         const uint32_t t_row = tmem_base + ((uint32_t)(q4 * 32) << 16);
         const int c_lo = hf * kTcHalf, c_hi = min(c_lo + kTcHalf, n_keys);
@@ -187,7 +175,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = mbar_wait_abortable(bar_mx, 0, abort_flag) && mbar_wait_abortable(bar_v, 0, abort_flag);
         if (!ok) break;
         mx = fmaxf(mx, xmax[(hf ^ 1) * 128 + r]);
-        ATTN_STAMP(4);
         // keys between the sequence's end and the MMA's K extent belong to a neighbour: zero those V rows so that
         // 0 * V stays 0 whatever they hold
         {
@@ -230,11 +217,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         fence_proxy_async();                     // the zeroed V rows were ordinary stores; the MMA reads them through the async proxy
         tc_fence_before();
         mbar_arrive_cta(bar_p);
-        ATTN_STAMP(5);
         // ---- epilogue: this warp's 32 output columns, O / rowsum -> bf16 -> staging tile -> 64-byte row pieces
         ok = mbar_wait_abortable(bar_o, 0, abort_flag);      // O follows everyone's arrival on bar_p, which follows their sums
         if (!ok) break;
-        ATTN_STAMP(6);
         tc_fence_after();
         const float l = (l0 + l1) + xsum[(hf ^ 1) * 128 + r];
         const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -261,7 +246,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     *reinterpret_cast<uint4*>(a.o + (long long)(sinfo.x + row) * a.o_row + (long long)head * a.o_head + 32 * hf + 8 * sub) = val;
             }
         }
-        ATTN_STAMP(7);
     } while (false);
     tc_fence_before();
     __syncthreads();
@@ -309,9 +293,6 @@ int attn_tc_launch(const IttaiAttention* p, cudaStream_t st) {
     a.group = p->group;
     a.scale_log2 = 1.4426950408889634f / 8.0f;
     a.status = p->status;
-#ifdef ITTAI_ATTN_PROFILE
-    a.clk = nullptr;
-#endif
     const cudaError_t e = launch_pdl(attn_tc_kernel, dim3(p->n_heads, (p->max_q_len + 127) / 128, p->n_seqs), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a);
     return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_tc_kernel");
 }

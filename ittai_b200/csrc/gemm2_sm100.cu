@@ -232,20 +232,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             constexpr uint32_t idesc = umma_idesc_bf16(PM, PN);
             int it = 0, local = 0;
             bool ok = true;
-            GEMM_PROF(long long t_start = clock64(); long long w_full = 0; long long w_acc = 0;)
             for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
                 const int buf = local & 1, round = local >> 1;
-                GEMM_PROF(long long t0 = clock64();)
                 ok = (round == 0 || mbar_wait_bounded(&acc_empty[buf], (round - 1) & 1, kSpin2)) && !*abort_flag;
-                GEMM_PROF(w_acc += clock64() - t0;)
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * PN);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % kStages2, use = it / kStages2;
-                    GEMM_PROF(long long t1 = clock64();)
                     ok = mbar_wait_bounded(&full[s], use & 1, kSpin2) && !*abort_flag;
-                    GEMM_PROF(w_full += clock64() - t1;)
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t da = umma_desc_sw128(sa + s * kHalfA), db = umma_desc_sw128(sb + s * kHalfB);
@@ -258,7 +253,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 umma_commit_pair(&acc_full[buf]);              // both CTAs' epilogues may read their rows
             }
             if (!ok) *abort_flag = 1;
-            GEMM_PROF(g.clk[blockIdx.x * 8 + 0] = clock64() - t_start; g.clk[blockIdx.x * 8 + 1] = w_full; g.clk[blockIdx.x * 8 + 2] = w_acc;)
         }
     } else {
         // ---- epilogue: warp w may touch TMEM lanes 32*(w%4)..+31 = 32 rows of this CTA's half tile; the two warps that
@@ -286,7 +280,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (has_res && lane == 0) { prefetch_res(0); prefetch_res(1); }
         uint32_t cc = 0;
         int local = 0;
-        GEMM_PROF(long long e_busy = 0; long long e_wait = 0;)
         for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
             const int buf = local & 1, round = local >> 1;
             const int tile_m = TILE_M(tile), tile_n = TILE_N(tile);
@@ -317,7 +310,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 *reinterpret_cast<uint4*>(sbias + 4 * lane) = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(col0 < ITTAI_Q3_DQ ? g.rope.qn : g.rope.kn) + 8 * lane);
             __syncwarp();
             bool ok = true;
-            GEMM_PROF(long long t0 = clock64();)
             {
                 uint32_t spins = 0;
                 while (!mbar_try_wait(&acc_full[buf], round & 1)) {
@@ -325,7 +317,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 }
             }
             if (!ok) { *abort_flag = 1; break; }
-            GEMM_PROF(long long t1 = clock64(); e_wait += t1 - t0;)
             tc_fence_after();
             if (g.epi == ITTAI_EPI_QKROPE) {
                 epilogue_qkrope(g, &tm_out, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + kEpiCols * cq), so,
@@ -401,10 +392,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[buf], 0));
-            GEMM_PROF(e_busy += clock64() - t1;)
         }
         if (lane == 0) tma_store_wait_all();                          // shared memory stays valid until the stores are done
-        GEMM_PROF(if (threadIdx.x == 64) { g.clk[blockIdx.x * 8 + 3] = e_busy; g.clk[blockIdx.x * 8 + 4] = e_wait; })
     }
     tc_fence_before();
     __syncthreads();

@@ -21,15 +21,7 @@ struct GemmArgs {
     int stats_parts;         // > 0: row_stats holds [M][parts][2] partial sums over K instead of (mean, rstd)
     float stats_eps;
     IttaiQkRope rope;        // ITTAI_EPI_QKROPE only
-#ifdef ITTAI_GEMM_PROFILE
-    long long* clk;          // [CTAs][8]: total, MMA waiting for loads, MMA waiting for a free accumulator, epilogue busy, epilogue waiting
-#endif
 };
-#ifdef ITTAI_GEMM_PROFILE
-#define GEMM_PROF(x) x
-#else
-#define GEMM_PROF(x)
-#endif
 
 // GELU-tanh as the reference writes it (src/ittai/siglip/kernel.py:289-291); the hardware tanh approximation is good
 // to about 2^-11, well inside the bf16 rounding of the result.

@@ -92,21 +92,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t idesc = umma_idesc_bf16(GM, TN);
             int it = 0, local = 0;
             bool ok = true;
-            GEMM_PROF(long long t_start = clock64(); long long w_full = 0; long long w_acc = 0;)
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
                 const int buf = local & 1, round = local >> 1;
                 // the epilogue must have drained this accumulator (passes at once on its first use)
-                GEMM_PROF(long long t0 = clock64();)
                 ok = (round == 0 || mbar_wait_bounded(&acc_empty[buf], (round - 1) & 1, kGemmSpin)) && !*abort_flag;
-                GEMM_PROF(w_acc += clock64() - t0;)
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * TN);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES, use = it / STAGES;
-                    GEMM_PROF(long long t1 = clock64();)
                     ok = mbar_wait_bounded(&full[s], use & 1, kGemmSpin) && !*abort_flag;
-                    GEMM_PROF(w_full += clock64() - t1;)
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t da = umma_desc_sw128(sa + s * kStageBytesA), db = umma_desc_sw128(sb + s * GemmCfg<TN, STAGES>::kStageBytesB);
@@ -119,19 +114,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 umma_commit(&acc_full[buf]);               // accumulator complete
             }
             if (!ok) *abort_flag = 1;
-            GEMM_PROF(g.clk[blockIdx.x * 8 + 0] = clock64() - t_start; g.clk[blockIdx.x * 8 + 1] = w_full; g.clk[blockIdx.x * 8 + 2] = w_acc;)
         }
     } else {
         // ---- epilogue: warp w may touch TMEM lanes 32*(w%4)..+31 = 32 rows of the tile; the two warps that share a lane
         //      quarter split the 256 columns, so every scheduler has two epilogue warps to interleave
         const int q = warp & 3, col_half = (warp - 2) >> 2;
         int local = 0;
-        GEMM_PROF(long long e_busy = 0; long long e_wait = 0;)
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             const int buf = local & 1, round = local >> 1;
             const int tile_m = tile / tiles_n, tile_n = tile % tiles_n;
             bool ok = true;
-            GEMM_PROF(long long t0 = clock64();)
             {   // bounded wait that also gives up when another role aborted
                 uint32_t spins = 0;
                 while (!mbar_try_wait(&acc_full[buf], round & 1)) {
@@ -139,7 +131,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
             if (!ok) { *abort_flag = 1; break; }
-            GEMM_PROF(long long t1 = clock64(); e_wait += t1 - t0;)
             tc_fence_after();
             const int row = tile_m * GM + q * 32 + lane;
 #pragma unroll 1
@@ -152,9 +143,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            GEMM_PROF(e_busy += clock64() - t1;)
         }
-        GEMM_PROF(if (threadIdx.x == 64) { g.clk[blockIdx.x * 8 + 3] = e_busy; g.clk[blockIdx.x * 8 + 4] = e_wait; })
     }
     tc_fence_before();
     __syncthreads();
@@ -237,10 +226,6 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.stats_parts = a->stats_parts;
     g.stats_eps = a->stats_eps;
     if (a->epi == ITTAI_EPI_QKROPE) g.rope = *a->qk_rope; else g.rope = IttaiQkRope{};
-#ifdef ITTAI_GEMM_PROFILE
-    extern long long* g_gemm_clk;
-    g.clk = g_gemm_clk;
-#endif
     if (pair) return gemm2_bf16_launch(tm_a, tm_b, g, st);
     const int tiles = ((a->m + GM - 1) / GM) * (a->n / 64);
     cudaError_t e = launch_pdl(gemm_bf16_kernel<64, 8>, dim3(tiles < n_sms ? tiles : n_sms), dim3(kGemmThreads), GemmCfg<64, 8>::kSmem, st, 1, tm_a, tm_b, g);

@@ -4,5 +4,6 @@ from .config import *  # noqa: F401,F403
 from .decoder import Qwen3Decoder, pack_weights, rope_table
 from .engine import Engine, PrefillCore, build_tasks, rope_perm
 from .model import Qwen3Embedder
+from .serving import DecodeServer, Request
 
-__all__ = ["Qwen3Embedder", "Qwen3Decoder"]
+__all__ = ["Qwen3Embedder", "Qwen3Decoder", "DecodeServer"]

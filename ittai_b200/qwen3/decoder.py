@@ -196,6 +196,56 @@ class Qwen3Decoder:
         out, _ = self._launch(forced.shape[0], forced=forced)
         return out[-1]
 
+    def prefill_slots(self, prompts: dict) -> None:
+        """Append token ids to the caches of SOME sequences of the batch, each with its own length: ``prompts`` maps a
+        sequence index to a 1-D id list.  The other sequences' caches and positions stay as they are.  Tensor-core
+        prefill, tokens of all named sequences packed into one activation matrix (the varlen packing of the reference's
+        engine, ``src/ittai/qwen3/engine.py:20,149-150``); no logits are produced."""
+        from .engine import PrefillCore
+        if self._unchecked:
+            self.check_status()
+        todo = {int(b): torch.as_tensor(t, dtype=torch.int32).reshape(-1) for b, t in prompts.items() if len(t) > 0}
+        if not todo:
+            return
+        for b, t in todo.items():
+            if not 0 <= b < self.B:
+                raise ValueError(f"sequence {b} outside 0..{self.B - 1}")
+            if int(t.min()) < 0 or int(t.max()) >= self.V:
+                raise ValueError(f"token id outside [0, {self.V})")
+            if self.lengths[b] + len(t) > self.cap:
+                raise ValueError(f"KV capacity {self.cap} exceeded: {self.lengths[b]} cached + {len(t)} prompt tokens")
+        total = sum(len(t) for t in todo.values())
+        if self._core is None or self._core.M < total:
+            self._core = PrefillCore(self.w, self.L, max(total, 256), self.dev)
+        i32 = lambda x: torch.as_tensor(x, dtype=torch.int32).to(self.dev, non_blocking=True)
+        tokens, pos, seq, seqs, row = [], [], [], [], 0
+        for b in range(self.B):                       # one record per sequence of the batch: the record index names the cache
+            n = len(todo[b]) if b in todo else 0
+            seqs.append([row, n, 0, self.lengths[b] + n])
+            if n:
+                tokens.append(todo[b])
+                pos.append(torch.arange(self.lengths[b], self.lengths[b] + n, dtype=torch.int32))
+                seq.append(torch.full((n,), b, dtype=torch.int32))
+                row += n
+        pos_d = i32(torch.cat(pos))
+        self._core.status.zero_()
+        self._core.run(total, i32(torch.cat(tokens)), pos_d, i32(torch.cat(seq)), pos_d, i32(seqs), max(len(t) for t in todo.values()),
+                       self.rope, lambda l: (self.kcache[l], self.vcache[l]), self.cap, (HD, self.cap * HD, NKV * self.cap * HD))
+        for b, t in todo.items():
+            self.lengths[b] += len(t)
+        self.pos.copy_(i32(self.lengths))
+        from .. import ops
+        ops.check_status(self._core.status)
+
+    def set_length(self, b: int, length: int) -> None:
+        """Set ONE sequence's cache length (0 frees the slot for a new request)."""
+        if not 0 <= length <= self.cap:
+            raise ValueError(f"length {length} outside 0..{self.cap}")
+        if self._unchecked:
+            self.check_status()
+        self.lengths[b] = length
+        self.pos[b] = length
+
     def _prefill_dense(self, ids: torch.Tensor) -> None:
         """Append ``ids`` ([B, n]) to every sequence's cache with the dense prefill kernels."""
         from .engine import PrefillCore

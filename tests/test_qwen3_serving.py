@@ -1,0 +1,81 @@
+"""The host request loop: scheduling on a stand-in decoder (CPU) and, on the GPU, every request's tokens against an
+independent batch-1 run of the same prompt."""
+import pytest
+import torch
+
+from ittai_b200.qwen3.serving import DecodeServer
+from oracle import qwen3_hf as hf
+
+gpu = pytest.mark.gpu
+
+
+class FakeDecoder:
+    """Four slots; the "model" continues a sequence with last token + 1.  Records what the loop asks of it."""
+
+    def __init__(self, B=4, cap=64):
+        self.B, self.cap = B, cap
+        self.next_id = torch.zeros(B, dtype=torch.int32)
+        self.lengths = [0] * B
+        self.prefills = []
+
+    def reset(self):
+        self.lengths = [0] * self.B
+
+    def set_length(self, b, n):
+        self.lengths[b] = n
+
+    def prefill_slots(self, prompts):
+        self.prefills.append({b: list(t) for b, t in prompts.items()})
+        for b, t in prompts.items():
+            self.lengths[b] += len(t)
+
+    def decode(self, n):
+        out = torch.stack([self.next_id + k + 1 for k in range(n)], 1)
+        self.next_id = out[:, -1].clone()
+        self.lengths = [x + n for x in self.lengths]
+        return out
+
+
+def test_requests_flow_through_free_slots_in_order():
+    d = FakeDecoder()
+    s = DecodeServer(d, chunk=4)
+    rids = [s.submit([10 * i, 10 * i + 1, 10 * i + 2], max_new_tokens=3 + 2 * i) for i in range(6)]
+    first = s.step()                                  # requests 0..3 admitted; 0 (3 tokens) finishes inside the first chunk
+    assert first == [rids[0]] and d.prefills[0] == {b: [10 * b, 10 * b + 1] for b in range(4)}
+    out = s.run()
+    assert sorted(out) == rids
+    for i in rids:
+        assert out[i] == [10 * i + 3 + k for k in range(3 + 2 * i)], (i, out[i])
+    # request 4 took the slot request 0 freed, with only its own prompt prefilled
+    assert d.prefills[1] == {0: [40, 41]}
+
+
+def test_stop_id_and_capacity_checks():
+    d = FakeDecoder(B=2, cap=32)
+    s = DecodeServer(d, chunk=8)
+    a = s.submit([5], max_new_tokens=20, stop_id=9)
+    b = s.submit([100, 101], max_new_tokens=2)
+    out = s.run()
+    assert out[a] == [6, 7, 8, 9] and out[b] == [102, 103]
+    with pytest.raises(ValueError):
+        s.submit(list(range(30)), max_new_tokens=10)
+    with pytest.raises(ValueError):
+        s.submit([], max_new_tokens=1)
+    assert not s.busy and s.step() == []
+
+
+@gpu
+def test_served_requests_match_independent_runs(tiny_hf):
+    from ittai_b200.qwen3 import Qwen3Decoder
+    model, dims = tiny_hf
+    lens = [40, 7, 150, 33, 90, 12, 64]
+    budgets = [9, 20, 5, 14, 3, 17, 8]
+    prompts = [hf.prompt_ids(n, seed=70 + i, vocab=dims.vocab).tolist() for i, n in enumerate(lens)]
+    d4 = Qwen3Decoder(model, max_batch=4, kv_capacity=256)
+    srv = DecodeServer(d4, chunk=4)
+    rids = [srv.submit(p, m) for p, m in zip(prompts, budgets)]
+    out = srv.run()
+    d1 = Qwen3Decoder(model, max_batch=1, kv_capacity=256)
+    for rid, p, m in zip(rids, prompts, budgets):
+        want = d1.generate(torch.tensor(p), m)[0].tolist()
+        assert out[rid] == want, f"request {rid} (prompt {len(p)}, {m} tokens): {out[rid]} vs {want}"
