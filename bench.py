@@ -251,6 +251,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-core baseline leg")
     ap.add_argument("--no-siglip", action="store_true", help="skip the SigLIP images/s leg")
     ap.add_argument("--no-config4", action="store_true", help="skip the 2048-token prefill + batch-8 decode leg (1 GPU only)")
+    ap.add_argument("--siglip-iters", type=int, default=20, help="timed SigLIP forwards per measurement (fewer for a profiler's launch list)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -338,7 +339,7 @@ def main():
         del dec
         torch.cuda.empty_cache()
         c4 = config4_leg(synthetic_state_dict(seed=rank, device=dev), dev, barrier)
-    sig = siglip_leg(dev, rank, barrier) if not args.no_siglip else None
+    sig = siglip_leg(dev, rank, barrier, iters=max(args.siglip_iters, 1)) if not args.no_siglip else None
     (total_ms, e2e_ms, sig_ms, sig_e2e_ms), toks = replicas.aggregate(
         [total_ms, e2e_ms, sig["ms"] if sig else 0.0, sig["e2e_ms"] if sig else 0.0], units=args.steps * DECODE, device=dev)
     if rank != 0:
