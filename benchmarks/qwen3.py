@@ -2,7 +2,7 @@
 Counterpart of the reference's ``benchmarks/qwen3.py`` with its shapes (B=64, S=512 by default), its FLOP formula
 (``:34``) and its timing protocol (3 warm-ups, median of 20 CUDA-event timings, ``:16-25``).
 
-  python benchmarks/qwen3.py [B] [S] [--ragged] [--layers 28] [--eager]
+  python benchmarks/qwen3.py [B] [S] [--ragged] [--layers 28] [--eager [--compile [MODE]]]
 
 There is no checkpoint or tokenizer offline: the weights are the seeded random-init state dict of ``bench.py`` and the
 ids are uniform random (``--ragged`` draws lengths uniformly from [S/4, S], the varlen case the reference packs).
@@ -31,6 +31,8 @@ def main():
     ap.add_argument("--ragged", action="store_true")
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--compile", nargs="?", const="max-autotune", default=None, metavar="MODE",
+                    help="with --eager: also time the eager module through torch.compile (default mode max-autotune, as the reference does)")
     a = ap.parse_args()
     g = torch.Generator().manual_seed(4)
     lens = torch.randint(max(1, a.S // 4), a.S + 1, (a.B,), generator=g).tolist() if a.ragged else [a.S] * a.B
@@ -65,11 +67,20 @@ def main():
             pad[i, S_max - len(s):] = torch.tensor(s, device="cuda")
             mask[i, S_max - len(s):] = 1
         with torch.inference_mode():
-            te = median_ms(lambda: body(input_ids=pad, attention_mask=mask), iters=5)
+            te = median_ms(lambda: body(input_ids=pad, attention_mask=mask), repeats=5)
             ref = F.normalize(body(input_ids=pad, attention_mask=mask).last_hidden_state[:, -1].float(), dim=-1)
         res["eager_ms"] = te
         res["min_cos_vs_eager"] = F.cosine_similarity(out.float(), ref, dim=-1).min().item()
         print(f"hf eager (sdpa)  {te:8.2f} ms  {flops / te / 1e9:6.1f} TFLOPS")
+        if a.compile:
+            # the reference's second comparison column (benchmarks/qwen3.py:13,30): the same module through torch.compile
+            body_c = torch.compile(body, mode=a.compile)
+            with torch.inference_mode():
+                tc = median_ms(lambda: body_c(input_ids=pad, attention_mask=mask), repeats=5)
+                ref_c = F.normalize(body_c(input_ids=pad, attention_mask=mask).last_hidden_state[:, -1].float(), dim=-1)
+            res["compile_ms"], res["compile_mode"] = tc, a.compile
+            res["min_cos_vs_compile"] = F.cosine_similarity(out.float(), ref_c, dim=-1).min().item()
+            print(f"hf {a.compile:13s} {tc:8.2f} ms  {flops / tc / 1e9:6.1f} TFLOPS  ittai_b200 is {tc / t:.2f}x vs compile")
     print(f"ittai_b200       {t:8.2f} ms  {flops / t / 1e9:6.1f} TFLOPS  {T / t:.0f}k tok/s")
     print(json.dumps(res))
 

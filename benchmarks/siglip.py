@@ -3,7 +3,7 @@
 tower (``:33``).  The reference's inputs (a hub checkpoint and one COCO image) are not available offline, so the tower
 is the ViT-B/16-224 configuration with seeded random weights and the pixels are N(0, 1) (seed 3).
 
-  python benchmarks/siglip.py [batch=64] [--ours-only] [--per-op]
+  python benchmarks/siglip.py [batch=64] [--ours-only] [--compile] [--per-op]
 
 ``--per-op`` prints the timings of one encoder layer's kernels instead (each repeated inside one CUDA graph).
 """
@@ -62,16 +62,22 @@ def main():
     with torch.inference_mode():
         t_eager = float("nan") if "--ours-only" in sys.argv else ms(lambda: vm(**kw))
         ref = vm(**kw).pooler_output.float()
+    t_comp = float("nan")
+    if "--compile" in sys.argv:
+        # the reference's second comparison column (benchmarks/siglip.py:13,30): the eager tower through torch.compile
+        vm_c = torch.compile(vm, mode="max-autotune")
+        with torch.inference_mode():
+            t_comp = ms(lambda: vm_c(**kw))
     t_mega = ms(lambda: emb.engine.forward(inp))
     emb.engine.check()
     cos = torch.nn.functional.cosine_similarity(emb.engine.forward(inp).float(), ref, dim=-1).min().item()
     flops, full = emb.engine.flops("reference"), emb.engine.flops("full")
     peaks, kind = measured_peaks()
-    for n, t in (("hf eager", t_eager), ("ittai_b200", t_mega)):
+    for n, t in (("hf eager", t_eager), ("hf max-autotune", t_comp), ("ittai_b200", t_mega)):
         print(f"{n:16s} {t:8.3f} ms  {flops / t / 1e9:7.1f} TFLOPS  {t_eager / t:.2f}x vs eager")
     print(json.dumps({"batch": B, "ms": t_mega, "img_per_s": B / t_mega * 1e3, "tflops_reference_formula": flops / t_mega / 1e9,
                       "tflops_full_count": full / t_mega / 1e9, "frac_of_" + kind + "_bf16_peak": flops / t_mega / 1e9 / peaks["bf16_tflops"],
-                      "frac_of_nominal_2250": flops / t_mega / 1e9 / 2250.0, "min_cos_vs_eager": cos, "eager_ms": t_eager}))
+                      "frac_of_nominal_2250": flops / t_mega / 1e9 / 2250.0, "min_cos_vs_eager": cos, "eager_ms": t_eager, "compile_ms": t_comp}))
 
 
 if __name__ == "__main__":

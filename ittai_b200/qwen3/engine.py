@@ -48,8 +48,9 @@ class PrefillCore:
     the reference's Engine owns its buffers: ``src/ittai/qwen3/engine.py:123-134``); weights and the key/value store are
     borrowed."""
 
-    def __init__(self, w: dict, n_layers: int, max_tokens: int, device):
+    def __init__(self, w: dict, n_layers: int, max_tokens: int, device, fused_rope: bool = True):
         self.w, self.L, self.M, self.dev = w, n_layers, max_tokens, device
+        self.fused_rope = fused_rope       # QK-norm + RoPE + cache scatter inside the QKV GEMM's epilogue (needs > 128 rows)
         z = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=device)
         self.h, self.xn, self.qkv, self.attn, self.act = z(max_tokens, D), z(max_tokens, D), z(max_tokens, DQKV), z(max_tokens, DQ), z(max_tokens, FF)
         self.status = ops.new_status(device)
@@ -64,7 +65,7 @@ class PrefillCore:
         for l in range(self.L):
             kc, vc = kv_layer(l)
             ops.rmsnorm_rows(h, w["ln1"][l], EPS, out=xn)
-            if T > 128:
+            if T > 128 and self.fused_rope:
                 # QK-norm + RoPE + cache scatter inside the QKV GEMM's epilogue (the reference's qkv epilogue, base.py:84-109)
                 ops.gemm(xn, w["wqkv"][l], st, out=qkv, epi=_C.EPI_QKROPE,
                          qk_rope=dict(qn=w["qn"][l], kn=w["kn"][l], rope=rope, pos=pos, seq=seq, slot=slot, kcache=kc, vcache=vc, kv_cap=kv_cap, eps=EPS))
@@ -90,7 +91,7 @@ class Engine:
 
     @torch.no_grad()
     def __init__(self, sd, max_tokens, max_seqs, arch=None, tile_n=None, stages=None, kv_block=None, group_m=None, warps=8,
-                 device="cuda", graph=True):
+                 device="cuda", graph=True, fused_rope=True):
         sd = _strip(sd if isinstance(sd, dict) else sd.state_dict())
         self.dev = torch.device(device)
         self.M, self.Bmax = (max_tokens + BM - 1) // BM * BM, max_seqs
@@ -98,7 +99,7 @@ class Engine:
         self.w = pack_weights(sd, self.L, self.dev)
         self.embed, self.fin_w = self.w["embed"], self.w["fin_w"]
         self.rope = rope_table(self.M, self.dev)
-        self.core = PrefillCore(self.w, self.L, self.M, self.dev)
+        self.core = PrefillCore(self.w, self.L, self.M, self.dev, fused_rope=fused_rope)
         z = lambda *s, dt: torch.zeros(*s, dtype=dt, device=self.dev)
         # one packed key/value store reused by every layer: the embedding pass keeps no cache
         self.kbuf, self.vbuf = z(1, NKV, self.M, HD, dt=torch.bfloat16), z(1, NKV, self.M, HD, dt=torch.bfloat16)

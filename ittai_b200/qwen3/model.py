@@ -14,7 +14,9 @@ from .engine import Engine
 
 
 class Qwen3Embedder:
-    def __init__(self, model_id="Qwen/Qwen3-Embedding-0.6B", max_tokens=8192, max_seqs=256, device="cuda"):
+    CANDIDATES = ({"fused_rope": True}, {"fused_rope": False})
+
+    def __init__(self, model_id="Qwen/Qwen3-Embedding-0.6B", max_tokens=8192, max_seqs=256, device="cuda", tune=None):
         self.tok = None
         if isinstance(model_id, str):
             from transformers import AutoModel, AutoTokenizer
@@ -24,7 +26,41 @@ class Qwen3Embedder:
             self.model = model_id
         self.sd = self.model if isinstance(self.model, dict) else self.model.state_dict()
         self.max_tokens, self.max_seqs, self.device, self.model_id = max_tokens, max_seqs, device, model_id
-        self.engine = Engine(self.sd, max_tokens, max_seqs, device=device)
+        # a hub id is tuned like the reference tunes (model.py:25); an in-memory module only on request
+        tune = isinstance(model_id, str) if tune is None else tune
+        self.engine = Engine(self.sd, max_tokens, max_seqs, device=device, **(self._tune() if tune else {}))
+
+    def _tune(self, path=None) -> dict:
+        """Fastest engine configuration that agrees with the eager module (minimum cosine above 0.999), remembered per
+        GPU, model and size in the tuning cache: the reference's ``_tune`` (``model.py:50-77``) over this build's switches.
+        The probe batch is 32 sequences of seeded random ids of mixed lengths (no tokenizer is needed)."""
+        from .. import tuning
+        if isinstance(self.model, dict):
+            raise RuntimeError("tuning validates against the eager module: pass the module, not a state dict")
+        g = torch.Generator().manual_seed(11)
+        vocab = self.sd[[k for k in self.sd if k.endswith("embed_tokens.weight")][0]].shape[0]
+        lens = [min(self.max_tokens // 32, n) for n in (24, 9, 240, 3)] * 8
+        ids = [torch.randint(0, vocab, (max(n, 1),), generator=g).tolist() for n in lens]
+        dev = next(self.model.parameters()).device
+        body = self.model.model if hasattr(self.model, "lm_head") else self.model
+        with torch.no_grad():
+            ref = torch.stack([F.normalize(body(input_ids=torch.tensor([s], device=dev)).last_hidden_state[0, -1].float(), dim=-1) for s in ids])
+
+        def time_ms(engine, iters=10):
+            for _ in range(3):
+                engine.forward(ids)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                engine.forward(ids)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / iters
+
+        name = self.model_id if isinstance(self.model_id, str) else type(self.model).__name__
+        key = f"{torch.cuda.get_device_name()}|{name}|{self.max_tokens}"
+        return tuning.choose(key, self.CANDIDATES, lambda c: Engine(self.sd, self.max_tokens, self.max_seqs, device=self.device, **c),
+                             lambda e: F.cosine_similarity(e.forward(ids).float().to(ref.device), ref, dim=-1).min().item(), time_ms, path=path)
 
     def _ids(self, texts, max_length):
         if len(texts) and not isinstance(texts[0], str):

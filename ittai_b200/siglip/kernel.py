@@ -238,15 +238,55 @@ class Siglip2Embedder:
     (``None`` without a checkpoint), ``.vm``, ``.engine``; ``.embed(pixel_values)`` batches and pads like the reference's
     ``embed`` (``:715-723``: the last batch repeats its final image)."""
 
-    def __init__(self, model_id="google/siglip2-base-patch16-naflex", batch_size=64, device="cuda"):
+    CANDIDATES = ({"fold_ln": True}, {"fold_ln": False})
+
+    def __init__(self, model_id="google/siglip2-base-patch16-naflex", batch_size=64, device="cuda", tune=None):
         self.processor = None
+        name = model_id if isinstance(model_id, str) else type(model_id).__name__
+        tune = isinstance(model_id, str) if tune is None else tune
         if isinstance(model_id, str):
             from transformers import AutoImageProcessor, AutoModel
             self.processor = AutoImageProcessor.from_pretrained(model_id)
             model_id = AutoModel.from_pretrained(model_id, dtype=torch.bfloat16)
         self.vm = _vision_model(model_id).to(device, torch.bfloat16).eval()
         self.B, self.device = batch_size, device
-        self.engine = Engine(self.vm, batch_size)
+        self.engine = Engine(self.vm, batch_size, **(self._tune(name) if tune else {}))
+
+    def _probe_inputs(self) -> dict:
+        """Seeded random inputs of the tower's own input kind, as the reference's ``_tune`` draws them (``:695-700``)."""
+        cfg, B = self.vm.config, self.B
+        g = torch.Generator().manual_seed(13)
+        if isinstance(self.vm.embeddings.patch_embedding, torch.nn.Conv2d):
+            return {"pixel_values": torch.randn(B, 3, cfg.image_size, cfg.image_size, generator=g)}
+        S = cfg.num_patches
+        side = int(S ** 0.5)
+        return {"pixel_values": torch.randn(B, S, 3 * cfg.patch_size ** 2, generator=g), "pixel_attention_mask": torch.ones(B, S, dtype=torch.long),
+                "spatial_shapes": torch.tensor([[side, side]] * B)}
+
+    def _tune(self, name: str, path=None) -> dict:
+        """Fastest engine configuration whose pooled embeddings agree with the eager tower (minimum cosine above 0.999),
+        remembered per GPU, model and batch size: the reference's ``_tune`` (``:690-713``) over this build's switches."""
+        from .. import tuning
+        inp = self._probe_inputs()
+        with torch.no_grad():
+            kw = {k: v.to(self.device) for k, v in inp.items()}
+            kw["pixel_values"] = kw["pixel_values"].to(torch.bfloat16)
+            ref = self.vm(**kw).pooler_output.float()
+
+        def time_ms(engine, iters=10):
+            for _ in range(3):
+                engine.forward(inp)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                engine.forward(inp)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / iters
+
+        key = f"{torch.cuda.get_device_name()}|{name}|{self.B}"
+        return tuning.choose(key, self.CANDIDATES, lambda c: Engine(self.vm, self.B, **c),
+                             lambda e: torch.nn.functional.cosine_similarity(e.forward(inp).float(), ref, dim=-1).min().item(), time_ms, path=path)
 
     @torch.no_grad()
     def embed(self, images):
