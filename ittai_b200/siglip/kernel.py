@@ -54,10 +54,25 @@ def _vision_model(m):
     return m.vision_model if hasattr(m, "vision_model") else m
 
 
+def fits_fast_path(cfg) -> bool:
+    """Whether a tower's widths are the ones the fused path is written for: head_dim 64, model and MLP width multiples of
+    128 (256 for the two-SM GEMM's tile comes with them for ViT-B), patch rows a multiple of 64 values."""
+    D, H, Fm, p = cfg.hidden_size, cfg.num_attention_heads, cfg.intermediate_size, cfg.patch_size
+    return D % H == 0 and D // H == 64 and D % 256 == 0 and Fm % 256 == 0 and (3 * p * p) % 64 == 0
+
+
 class Engine:
     """``Engine(vm, B)``: fixed batch ``B``; ``forward({"pixel_values": fp32 [B,3,H,W]})`` returns bf16 ``[B, D]`` pooled
     embeddings (a persistent buffer, like the reference's ``self.embeds``).  The reference's tuning arguments
     (``tile_n, stages, warps, fold_k, group_m, kv_block``) are accepted and ignored: there is one sm_100a kernel."""
+
+    def __new__(cls, vm, B, *args, **kw):
+        """ViT-B-like geometries (head_dim 64, widths in multiples of 128) get this class; anything else (so400m: width
+        1152, head_dim 72, MLP 4304, patch 14) the same kernels on zero-padded weights (``padded.PaddedEngine``)."""
+        if cls is Engine and not fits_fast_path(_vision_model(vm).config):
+            from .padded import PaddedEngine
+            return PaddedEngine(vm, B, graph=kw.get("graph", True))
+        return super().__new__(cls)
 
     @torch.no_grad()
     def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True, fold_ln=True):

@@ -119,3 +119,50 @@ def test_naflex_engine_against_eager_on_device():
         bad = dict(inp)
         bad["pixel_attention_mask"] = torch.ones_like(inp["pixel_attention_mask"])
         emb.embed(bad)
+
+
+# ---- so400m geometry (width 1152, 16 heads of 72, MLP 4304, patch 14): the kernels on zero-padded weights -----------------
+def _so400m(naflex: bool, n_layers: int = 2, device="cpu", dtype=torch.bfloat16, seed: int = 5):
+    from transformers import Siglip2VisionConfig, Siglip2VisionModel, SiglipVisionConfig, SiglipVisionModel
+    kw = dict(hidden_size=1152, intermediate_size=4304, num_hidden_layers=n_layers, num_attention_heads=16,
+              hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6)
+    torch.manual_seed(seed)
+    m = (Siglip2VisionModel(Siglip2VisionConfig(num_patches=256, patch_size=16, **kw)) if naflex else
+         SiglipVisionModel(SiglipVisionConfig(image_size=384, patch_size=14, **kw)))
+    return m.to(dtype).eval().to(device)
+
+
+def test_geometry_dispatch():
+    from ittai_b200.siglip.kernel import fits_fast_path
+    assert fits_fast_path(hf.build_hf(n_layers=1).config)
+    assert not fits_fast_path(_so400m(False, n_layers=1).config) and not fits_fast_path(_so400m(True, n_layers=1).config)
+
+
+@gpu
+@pytest.mark.parametrize("naflex", [False, True])
+def test_so400m_geometry_against_eager(naflex):
+    """The benchmark default of the reference (`siglip2-so400m-patch14-384`, benchmarks/siglip.py:7) at two layers, and the
+    same widths as a NaFlex tower: pooled embeddings against the eager tower on the same GPU (bf16) and on the CPU (fp32)."""
+    from ittai_b200.siglip.kernel import Siglip2Embedder
+    from ittai_b200.siglip.padded import PaddedEngine
+    vm = _so400m(naflex, device="cuda")
+    if naflex:
+        inp = hf.naflex_inputs([(16, 16), (9, 21), (3, 5)], seed=8)
+        kw = dict(pixel_values=inp["pixel_values"].cuda().to(torch.bfloat16), pixel_attention_mask=inp["pixel_attention_mask"].cuda(),
+                  spatial_shapes=inp["spatial_shapes"].cuda())
+        B = 3
+    else:
+        B = 2
+        inp = {"pixel_values": torch.randn(B, 3, 384, 384, generator=torch.Generator().manual_seed(8))}
+        kw = dict(pixel_values=inp["pixel_values"].cuda().to(torch.bfloat16))
+    with torch.no_grad():
+        want = vm(**kw).pooler_output.float().cpu()
+        want32 = _so400m(naflex, dtype=torch.float32)(**inp).pooler_output
+    emb = Siglip2Embedder(vm, batch_size=B)
+    assert isinstance(emb.engine, PaddedEngine) and emb.engine.hdp == 128 and emb.engine.Dp == 1280 and emb.engine.Fp == 4352
+    out = emb.embed(inp if naflex else inp["pixel_values"]).float().cpu()
+    emb.engine.check()
+    cos, cos32 = F.cosine_similarity(out, want, dim=-1), F.cosine_similarity(out, want32, dim=-1)
+    print("so400m", "naflex" if naflex else "patch14-384", "min cos vs bf16 eager", cos.min().item(), "vs fp32 eager", cos32.min().item())
+    assert out.shape == (B, 1152) and cos.min() >= 0.9995 and cos32.min() >= 0.9995
+    assert torch.equal(emb.embed(inp if naflex else inp["pixel_values"]).float().cpu(), out)       # graph replay
