@@ -123,11 +123,14 @@ __device__ __forceinline__ bool head_runs(const Cta& c, int step) { return step 
 // Slice addresses are linear in the layer index, so everything but one small division per step is hoisted.
 //
 // Cache tiles and the row appended one step earlier: the K/V tiles of (step s, layer l) contain the row that some CTA
-// appended at (step s - 1, layer l).  That store (and the fences behind it) comes before the appending CTA publishes its
-// split's partial, and the attention output of (s - 1, l) needs every partial; so the tiles are held back until this
-// CTA's compute threads have received that whole output and said so in `kv_epoch`.  The hold costs nothing (the condition
-// was met a whole token ago, except with a single layer), and it replaces an ordering that used to rest on the ring being
-// smaller than what a CTA streams between the two points.
+// appended at (step s - 1, layer l).  The appending thread stores the row and fences (gpu scope, then the proxy fence for
+// the TMA unit) before its CTA publishes its split's partial, and the attention output of (s - 1, l) needs every partial;
+// so the tiles are held back until this CTA's compute threads have received that whole output and said so in `kv_epoch`.
+// The hold costs nothing (the condition was met a whole token ago, except with a single layer), and it replaces an
+// ordering that used to rest on the ring being smaller than what a CTA streams between the two points.  The observing
+// side carries no gpu-scope fence of its own: the bulk copy reads L2, where the fenced row already is when any word
+// that depends on it can be seen, and a fence.acq_rel.gpu on this side was measured at 7 us per token of a 256-token
+// run in a warp of its own, 10-13 us in a compute thread, 210 us in the feeding lane with its copies in flight.
 __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t limit = c.w.limit;
@@ -755,15 +758,9 @@ __device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uin
     const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
     if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what, p1 > p0 ? &W : nullptr)) return false;
     c.t_ready = clock64();
-    if (what == ITTAI_PH_OPROJ && c.tid == kThreads - 1) {
-        // The whole attention output of (step, layer) is here, so every cache row appended up to (step, layer) is in
-        // place: the feeding lane may fetch the tiles of (step + 1, layer).  The fence makes what this CTA's threads
-        // observed before the barrier above an acquire of the appending CTAs' fenced stores (13 us per token of a
-        // 256-token run on a B200; the same fence pair executed by the feeding lane itself, with its bulk copies in
-        // flight, cost 210 us).
-        asm volatile("fence.acq_rel.gpu;" ::: "memory");
-        st_release_cta(&c.st.sh->kv_epoch, epoch);
-    }
+    // The whole attention output of (step, layer) is here, so every cache row appended up to (step, layer) is in place:
+    // the feeding lane may fetch the tiles of (step + 1, layer).
+    if (epoch != 0u && c.tid == 0) st_release_cta(&c.st.sh->kv_epoch, epoch);
     if (p1 == p0) return all_ok(ok);
     if constexpr (NB > 1) {
         // several sequences: tiles of up to 16 rows x 256 columns on the tensor cores, one column block per warp

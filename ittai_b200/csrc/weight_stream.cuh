@@ -33,7 +33,7 @@ struct StreamShared {
     uint32_t consumed;                     // entries released so far (compute thread 0; release / acquire accesses)
     volatile uint32_t stop;                // compute threads are leaving early: issue nothing more
     uint32_t kv_epoch;                     // 1 + index (step * layers + layer) of the last attention output this CTA's compute
-                                           // threads have received whole (release / acquire accesses)
+                                           // threads have received whole (compute thread 0; release / acquire accesses)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
