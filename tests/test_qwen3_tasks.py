@@ -62,3 +62,35 @@ def test_layer_order_guard_for_the_shared_qkv_buffer():
     assert (blk1[6], blk1[7]) == (base + 4 * bmax + 1, 2)      # rows 128..255: sequences 1 and 2
     assert (blk2[6], blk2[7]) == (base + 4 * bmax + 2, 1)
     assert (tasks[(tasks[:, 0] == cfg.OP_QKV) & (tasks[:, 1] == 0)][:, 6] == -1).all()
+
+
+# ---- properties over random packings ---------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+
+@settings(max_examples=12, deadline=None)
+@given(lens=st.lists(st.integers(min_value=1, max_value=300), min_size=1, max_size=5), spt=st.sampled_from([1, 2]),
+       group_m=st.sampled_from([1, 2, 8]), seed=st.integers(min_value=0, max_value=1000))
+def test_random_packings_are_consistent(lens, spt, group_m, seed):
+    """For any packing (sequences of length 1, sequences that straddle row blocks, a single block): the announced arrivals
+    equal the arrivals the tasks make, every dependency index is a flag that exists, attention items cover every query
+    row exactly once per kv head, and a handful of persistent CTAs get through the list."""
+    T = sum(lens)
+    mb = -(-T // cfg.BM) + 1
+    bmax = len(lens) + 1
+    tiles = (4, 2, 6, 2)
+    tasks, expect, T2 = build_tasks(lens, mb, bmax, cfg.L + 1, tiles, spt, 64, group_m)
+    assert T2 == T
+    n_flags = len(expect)
+    for d, c in ((tasks[:, 4], tasks[:, 5]), (tasks[:, 6], tasks[:, 7])):
+        live = d >= 0
+        assert (d[live] + c[live] <= n_flags).all() and (c[live] >= 1).all()
+    # layer 0's attention items: each sequence's query blocks, all 8 kv heads
+    a0 = tasks[(tasks[:, 0] == cfg.OP_ATTN) & (tasks[:, 1] == 0)]
+    assert len(a0) == cfg.NKV * sum(-(-n // cfg.QB) for n in lens)
+    for s, n in enumerate(lens):
+        blocks = sorted(a0[a0[:, 2] == s * cfg.NKV][:, 3].tolist())
+        assert blocks == list(range(-(-n // cfg.QB)))
+    arr = lambda t: arrivals_of(t, cfg.L + 1, mb, bmax, spt, lens)
+    arrived = simulate(tasks, expect, 5, np.random.default_rng(seed), arr)
+    assert np.array_equal(arrived, expect)
