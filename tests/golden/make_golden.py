@@ -1,6 +1,7 @@
 """Write the golden fixtures in this directory from the Hugging Face eager modules.
 
-Run from the repository root:  python tests/golden/make_golden.py [qwen3_tiny|qwen3_full|siglip ...]
+Run from the repository root:  python tests/golden/make_golden.py [qwen3_tiny|qwen3_full|siglip|qwen3_tasks ...]
+(``qwen3_tasks`` needs ITTAI_REFERENCE=<checkout of the reference>; the others need only ``transformers``.)
 
 The reference ships no fixtures; these are outputs of the ``transformers`` modules it validates
 against (reference ``src/ittai/qwen3/model.py:32-37``, ``src/ittai/siglip/kernel.py:701-702``),
@@ -118,7 +119,9 @@ def qwen3_tasks():
     import ast
     import hashlib
     import numpy as np
-    root = os.environ.get("ITTAI_REFERENCE", "/root/reference")
+    root = os.environ.get("ITTAI_REFERENCE")
+    if not root or not os.path.isdir(os.path.join(root, "src", "ittai")):
+        raise SystemExit("set ITTAI_REFERENCE to a checkout of the reference (the directory that holds src/ittai)")
     ns = {"np": np}
     exec(compile(open(os.path.join(root, "src/ittai/qwen3/config.py")).read(), "config.py", "exec"), ns)
     src = open(os.path.join(root, "src/ittai/qwen3/engine.py")).read()
