@@ -228,15 +228,22 @@ def cpu_reference(steps: int, warmup: int):
     return r, sample
 
 
+REF_TOKENS_PER_STEP = 16      # the reference arm's step: a bounded sample of the 256-token step (about 0.7 s of host work)
+
+
 def run_reference(args, rank):
+    """The reference's eager path on the host cores.  One step here is REF_TOKENS_PER_STEP decoded tokens at cache length
+    4096 (a bounded sample of the GPU arm's 256-token step); `value` is tokens per second, `ms_per_step` the measured time
+    of one sampled step, so steps x ms_per_step is the time the run really took."""
     if rank != 0:
         return
-    n = max(8, min(32, args.steps * 8))
+    n = max(args.steps, 1) * REF_TOKENS_PER_STEP
     r, sample = cpu_reference(n, args.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": r["tok_s"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_tok"] * DECODE, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_tok"] * REF_TOKENS_PER_STEP, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"qwen3-0.6b random-init bf16, batch 1, cache length {PROMPT}, greedy decode on host cores"},
+            "config": {"workload": f"qwen3-0.6b random-init bf16, batch 1, cache length {PROMPT}, greedy decode on host cores; one step = "
+                                   f"{REF_TOKENS_PER_STEP} tokens (bounded sample of the {DECODE}-token step)"},
             "cpu_baseline": {"value": r["tok_s"], "unit": UNIT, "cores": r["threads"], "kind": "reference", "sample": sample},
             "e2e": {"value": r["tok_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
