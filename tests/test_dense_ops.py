@@ -40,7 +40,7 @@ def test_attention_dense_packed_qkv(B, S):
 
 
 @gpu
-@pytest.mark.parametrize("lens", [[196] * 5, [224, 65, 130, 200], [128, 129], [70]])
+@pytest.mark.parametrize("lens", [[196] * 5, [224, 65, 130, 200], [128, 129], [70], [112, 113, 100, 97], [208, 81, 127]])
 def test_attention_tensor_memory_kernel(lens):
     """The tcgen05 kernel (row totals + status words given): ragged sequences packed in one q | k | v matrix, with rows
     past the last sequence left as NaN-free garbage.  Same reference and tolerance as the register-tile kernels."""
@@ -61,6 +61,41 @@ def test_attention_tensor_memory_kernel(lens):
         want = F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(n, D)
         _check(out[s:s + n], want, f"tensor-memory attention rows {s}..{s + n}")
     assert not out[T:].any(), "rows past the last sequence were written"
+
+
+@gpu
+@pytest.mark.parametrize("kind", ["ramp", "step"])
+@pytest.mark.parametrize("n", [196, 224, 120])
+def test_attention_tensor_memory_kernel_rising_scores(n, kind):
+    """Scores that grow along the keys by far more than a row's softmax reference may lag behind: the one-pass softmax
+    has to raise its reference and rescale the probabilities it has already written, in both halves of the keys, and the
+    halves end with references hundreds of log2 units apart.  Head 0, "ramp": key j is (j / 4) x the query direction
+    (+1.08 log2 units per key); "step": keys 0..39 are zero and the rest 50 x the query direction (+216 log2 units inside
+    one chunk, so the stale reference makes 2^x overflow before it is raised).  Head 1: the same keys in reverse order
+    (the first chunk already holds the maximum); the other heads are random."""
+    from ittai_b200 import ops
+    H, hd, D = 12, 64, 768
+    qkv = _rand(n, 3 * D, seed=9)
+    u = torch.nn.functional.normalize(torch.randn(hd, generator=torch.Generator().manual_seed(3)), dim=0).cuda()
+    ramp = torch.arange(n, device="cuda", dtype=torch.float32)
+    mag = ramp / 4 if kind == "ramp" else (ramp >= 40).float() * 50
+    qkv[:, 0:hd] = (u * 24.0).to(torch.bfloat16)                                   # q of head 0: |q| = 24 for every row
+    qkv[:, D:D + hd] = (mag[:, None] * u).to(torch.bfloat16)                       # k of head 0
+    qkv[:, hd:2 * hd] = (u * 24.0).to(torch.bfloat16)
+    qkv[:, D + hd:D + 2 * hd] = (mag.flip(0)[:, None] * u).to(torch.bfloat16)
+    out = torch.zeros(n, D, dtype=torch.bfloat16, device="cuda")
+    seqs = torch.tensor([[0, n, 0, n]], dtype=torch.int32, device="cuda")
+    st = ops.new_status(qkv.device)
+    ops.attention(qkv, qkv[:, D:], qkv[:, 2 * D:], out, seqs, n_heads=H, group=1, head_dim=hd, causal=False, max_q_len=n,
+                  q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0), o_strides=(D, hd),
+                  max_kv_len=n, q_rows_total=n, kv_rows_total=n, status=st)
+    ops.check_status(st)
+    q, k, v = (qkv[:, i * D:(i + 1) * D].float().view(n, H, hd).transpose(0, 1) for i in range(3))
+    sc = q[0] @ k[0].T / 8
+    assert float((sc.amax(1) - sc[:, :16].amax(1)).min()) * 1.4427 > 64, "the case no longer forces a raise of the reference"
+    want = F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(n, D)
+    assert torch.isfinite(out.float()).all()
+    _check(out, want, f"rising scores ({kind}), {n} keys")
 
 
 @gpu
