@@ -857,11 +857,14 @@ __device__ bool phase_gu(Cta& c, int l) {
             const bf16* wu = W + (size_t)(4 * (un - u0)) * D;
             float a0[NB], a1[NB];
             if constexpr (NB == 1) {
-                const bf16* wp[4] = {wu, wu + D, wu + 2 * D, wu + 3 * D};
-                float acc[4][NB];
-                dot_rows_k1024<false, NB, 4>(c, wp, xr, acc);
+                // two rows at a time: four rows' worth of weights in flight (64 registers) next to the 32 of xr spills
+                const bf16* wa[2] = {wu, wu + D};
+                const bf16* wb[2] = {wu + 2 * D, wu + 3 * D};
+                float acc[2][NB], acd[2][NB];
+                dot_rows_k1024<false, NB, 2>(c, wa, xr, acc);
+                dot_rows_k1024<false, NB, 2>(c, wb, xr, acd);
                 a0[0] = swiglu(acc[0][0], acc[1][0]);
-                a1[0] = swiglu(acc[2][0], acc[3][0]);
+                a1[0] = swiglu(acd[0][0], acd[1][0]);
             } else {
 #pragma unroll
                 for (int hsel = 0; hsel < 2; ++hsel) {
