@@ -255,7 +255,7 @@ class Siglip2Embedder:
 
     CANDIDATES = ({"fold_ln": True}, {"fold_ln": False})
 
-    def __init__(self, model_id="google/siglip2-base-patch16-naflex", batch_size=64, device="cuda", tune=None):
+    def __init__(self, model_id="google/siglip2-base-patch16-naflex", batch_size=64, device="cuda", tune=None, engine=None):
         self.processor = None
         name = model_id if isinstance(model_id, str) else type(model_id).__name__
         tune = isinstance(model_id, str) if tune is None else tune
@@ -265,7 +265,8 @@ class Siglip2Embedder:
             model_id = AutoModel.from_pretrained(model_id, dtype=torch.bfloat16)
         self.vm = _vision_model(model_id).to(device, torch.bfloat16).eval()
         self.B, self.device = batch_size, device
-        self.engine = Engine(self.vm, batch_size, **(self._tune(name) if tune else {}))
+        # `engine`: an Engine already built for this module and batch size (skips a second graph capture)
+        self.engine = engine if engine is not None else Engine(self.vm, batch_size, **(self._tune(name) if tune else {}))
 
     def _probe_inputs(self) -> dict:
         """Seeded random inputs of the tower's own input kind, as the reference's ``_tune`` draws them (``:695-700``)."""
@@ -304,9 +305,63 @@ class Siglip2Embedder:
                              lambda e: torch.nn.functional.cosine_similarity(e.forward(inp).float(), ref, dim=-1).min().item(), time_ms, path=path)
 
     @torch.no_grad()
+    def embed_batches(self, batches, to_host=False):
+        """Embeddings of an iterable of input dicts (or fp32 pixel tensors) of exactly ``batch_size`` images each, one device
+        tensor ``[B, D]`` per batch.  Pixel values that live in host memory are staged through two device buffers on a copy
+        stream of their own: batch k + 1 crosses PCIe while batch k is in the encoder (pinned host tensors make the copy
+        asynchronous for the host as well).  Inputs already on the device go straight to the engine.  ``to_host=True``
+        returns pinned host tensors instead, each copied back right behind its batch (synchronise before reading them)."""
+        dev = torch.device(self.device)
+        main = torch.cuda.current_stream(dev)
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(dev)
+            self._staged = [None, None]                    # per slot: device copy of the pixel values
+            self._free = [torch.cuda.Event(), torch.cuda.Event()]      # slot read by the engine: may be overwritten
+            for e in self._free:
+                e.record(main)
+
+        def stage(inp, slot):
+            inp = {"pixel_values": inp} if torch.is_tensor(inp) else dict(inp)
+            px = inp["pixel_values"]
+            if px.device.type == "cuda":
+                return inp, None
+            buf = self._staged[slot]
+            if buf is None or buf.shape != px.shape or buf.dtype != px.dtype:
+                buf = self._staged[slot] = torch.empty(px.shape, dtype=px.dtype, device=dev)
+            ready = torch.cuda.Event()
+            with torch.cuda.stream(self._copy_stream):
+                self._copy_stream.wait_event(self._free[slot])
+                buf.copy_(px, non_blocking=True)
+                ready.record(self._copy_stream)
+            inp["pixel_values"] = buf                      # the small NaFlex tensors (mask, shapes) stay where they are
+            return inp, ready
+
+        out, it, k = [], iter(batches), 0
+        nxt = next(it, None)
+        staged = stage(nxt, 0) if nxt is not None else None
+        while staged is not None:
+            cur, ready = staged
+            nxt = next(it, None)
+            staged = stage(nxt, (k + 1) & 1) if nxt is not None else None      # issued before this batch's forward
+            if ready is not None:
+                main.wait_event(ready)
+            emb = self.engine.forward(cur)
+            if to_host:
+                host = torch.empty(emb.shape, dtype=emb.dtype).pin_memory()
+                host.copy_(emb, non_blocking=True)
+                out.append(host)
+            else:
+                out.append(emb.clone())
+            if ready is not None:
+                self._free[k & 1].record(main)
+            k += 1
+        return out
+
+    @torch.no_grad()
     def embed(self, images):
         """``images``: fp32 ``[N, 3, H, W]`` pixel values, a dict of processor outputs (NaFlex: ``pixel_values``,
-        ``pixel_attention_mask``, ``spatial_shapes``), or PIL images when a processor is loaded."""
+        ``pixel_attention_mask``, ``spatial_shapes``), or PIL images when a processor is loaded.  Host inputs are fed
+        through ``embed_batches``: the copy of a batch overlaps the encoder pass of the one before."""
         if torch.is_tensor(images):
             inp = {"pixel_values": images}
         elif isinstance(images, dict):
@@ -314,10 +369,12 @@ class Siglip2Embedder:
         else:
             inp = dict(self.processor(images=images, return_tensors="pt"))
         total = len(inp["pixel_values"])
-        out = []
-        for k in range(0, total, self.B):
-            n = min(self.B, total - k)
-            # a short last batch is filled up with copies of its final image (reference ``:720-723``)
-            fill = lambda t: torch.cat([t[k:k + n], t[k + n - 1:k + n].expand(self.B - n, *t.shape[1:])])
-            out.append(self.engine.forward({name: fill(t) for name, t in inp.items()})[:n].clone())
-        return torch.cat(out)
+        counts = [min(self.B, total - k) for k in range(0, total, self.B)]
+
+        def batches():
+            for k, n in zip(range(0, total, self.B), counts):
+                # a short last batch is filled up with copies of its final image (reference ``:720-723``)
+                fill = lambda t: t[k:k + n] if n == self.B else torch.cat([t[k:k + n], t[k + n - 1:k + n].expand(self.B - n, *t.shape[1:])])
+                yield {name: fill(t) for name, t in inp.items()}
+
+        return torch.cat([e[:n] for e, n in zip(self.embed_batches(batches()), counts)])

@@ -166,3 +166,21 @@ def test_so400m_geometry_against_eager(naflex):
     print("so400m", "naflex" if naflex else "patch14-384", "min cos vs bf16 eager", cos.min().item(), "vs fp32 eager", cos32.min().item())
     assert out.shape == (B, 1152) and cos.min() >= 0.9995 and cos32.min() >= 0.9995
     assert torch.equal(emb.embed(inp if naflex else inp["pixel_values"]).float().cpu(), out)       # graph replay
+
+
+@gpu
+def test_embed_from_host_memory_overlaps_copies_and_matches_device_inputs():
+    """``embed`` on pixels in (pinned) host memory stages batch k + 1 on a copy stream while batch k is in the encoder; the
+    embeddings equal those of the same pixels handed over on the device, batch by batch, short last batch included."""
+    from ittai_b200.siglip.kernel import Siglip2Embedder
+    vm = hf.build_hf(seed=2, device="cuda")
+    emb = Siglip2Embedder(vm, batch_size=8)
+    px = hf.pixels(8 * 3 + 5, seed=11)
+    on_device = emb.embed(px.cuda())
+    from_host = emb.embed(px.pin_memory())
+    from_pageable = emb.embed(px.clone())
+    assert on_device.shape == (29, 768)
+    assert torch.equal(on_device, from_host) and torch.equal(on_device, from_pageable)
+    hosts = emb.embed_batches([px[:8].pin_memory(), px[8:16].pin_memory()], to_host=True)
+    torch.cuda.synchronize()
+    assert all(h.is_pinned() for h in hosts) and torch.equal(torch.cat(hosts).cuda(), on_device[:16])
