@@ -343,12 +343,13 @@ def main():
     dec.check_status()
     e2e_ms = e0.elapsed_time(e1)
 
+    # the two headline legs first, the config-4 leg (which frees the batch-1 decoder) last
+    sig = siglip_leg(dev, rank, barrier, iters=max(args.siglip_iters, 1)) if not args.no_siglip else None
     c4 = None
     if world == 1 and not args.no_config4:
         del dec
         torch.cuda.empty_cache()
         c4 = config4_leg(synthetic_state_dict(seed=rank, device=dev), dev, barrier)
-    sig = siglip_leg(dev, rank, barrier, iters=max(args.siglip_iters, 1)) if not args.no_siglip else None
     (total_ms, e2e_ms, sig_ms, sig_e2e_ms), toks = replicas.aggregate(
         [total_ms, e2e_ms, sig["ms"] if sig else 0.0, sig["e2e_ms"] if sig else 0.0], units=args.steps * DECODE, device=dev)
     if rank != 0:
