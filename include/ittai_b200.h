@@ -232,6 +232,17 @@ typedef struct IttaiGemm {
  * (src/ittai/qwen3/sm80.py:175-272, src/ittai/qwen3/sm90.py:256-316, src/ittai/siglip/kernel.py:197-333). */
 int ittai_gemm_bf16_launch(const IttaiGemm* g, void* stream);
 
+/* A chain of 1 to 4 GEMMs in ONE persistent launch: gemms[i + 1].a must be gemms[i].out (k = the previous n), every GEMM
+ * has the same M > 128, epilogues ITTAI_EPI_NONE / ITTAI_EPI_GELU with bias, residual (also in place), a folded LayerNorm
+ * and stats_out as in ittai_gemm_bf16_launch; the results are bit-identical to the same GEMMs launched one by one.  The tiles
+ * of all GEMMs form one task list dealt round-robin to the resident clusters; a tile of GEMM i + 1 waits on a counter per
+ * 128-row block that the tiles of GEMM i bump when their stores are complete, so the next GEMM starts on a row block as
+ * soon as that block exists instead of after the slowest tile of the whole GEMM.  `flags`: n * 2 * ceil(M / 256) device
+ * words that are ZERO at launch (the caller clears them, e.g. once per forward for all its chains).  This is the
+ * reference's device task queue with per-row-block dependency counters (src/ittai/siglip/kernel.py:197-333,
+ * src/ittai/qwen3/engine.py:17-84) restricted to runs of consecutive GEMMs. */
+int ittai_gemm_chain_launch(const IttaiGemm* gemms, int32_t n, uint32_t* flags, void* stream);
+
 /* ---- softmax attention for the prefill and SigLIP paths ------------------------------------------------- */
 
 /* Flash-style attention over `n_seqs` independent sequences.  Row r of sequence s lives at

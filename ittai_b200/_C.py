@@ -22,7 +22,7 @@ EXPORTS = (
     "ittai_version", "ittai_last_error", "ittai_device_check", "ittai_decode_status",
     "ittai_qwen3_decode_workspace_bytes", "ittai_qwen3_decode_launch", "ittai_qwen3_phase_launch",
     "ittai_qwen3_decode_launch_static",
-    "ittai_gemm_bf16_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows", "ittai_row_stats",
+    "ittai_gemm_bf16_launch", "ittai_gemm_chain_launch", "ittai_attention_launch", "ittai_rmsnorm_rows", "ittai_layernorm_rows", "ittai_row_stats",
     "ittai_qwen3_qk_rope_scatter", "ittai_siglip_im2col", "ittai_embed_rows", "ittai_qwen3_final_pool",
 )
 EPI_NONE, EPI_GELU, EPI_SWIGLU, EPI_QKROPE = range(4)
@@ -99,6 +99,7 @@ def lib() -> C.CDLL:
     L.ittai_qwen3_phase_launch.argtypes = [C.POINTER(Qwen3Decode), C.c_int, C.c_int, C.c_void_p]
     L.ittai_qwen3_decode_launch_static.argtypes = [C.POINTER(Qwen3Decode), C.c_void_p]
     L.ittai_gemm_bf16_launch.argtypes = [C.POINTER(Gemm), C.c_void_p]
+    L.ittai_gemm_chain_launch.argtypes = [C.POINTER(Gemm), C.c_int32, C.c_void_p, C.c_void_p]
     L.ittai_attention_launch.argtypes = [C.POINTER(Attention), C.c_void_p]
     vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
     L.ittai_rmsnorm_rows.argtypes = [vp, i32, vp, vp, i32, i32, f32, vp]

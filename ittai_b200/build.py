@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libittai_b200.so")
-SOURCES = ["api.cu", "qwen3_decode.cu", "gemm_sm100.cu", "gemm2_sm100.cu", "attention.cu", "attention_sm100.cu", "attention_fa_sm100.cu", "rowwise.cu"]
+SOURCES = ["api.cu", "qwen3_decode.cu", "gemm_sm100.cu", "gemm2_sm100.cu", "gemm2_chain_sm100.cu", "attention.cu", "attention_sm100.cu", "attention_fa_sm100.cu", "rowwise.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]
 

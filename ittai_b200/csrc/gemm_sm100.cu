@@ -165,7 +165,8 @@ int cuda_fail(cudaError_t e, const char* what);
 
 int gemm2_bf16_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmArgs& g, cudaStream_t st);   // gemm2_sm100.cu
 
-int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
+// Checks one IttaiGemm and turns it into kernel arguments and the operand tensor maps (`pair`: the two-SM kernel's W box).
+int gemm_args_from_abi(const IttaiGemm* a, GemmArgs* gp, CUtensorMap* tm_a, CUtensorMap* tm_b, bool pair) {
     if (!a || !a->a || !a->w || !a->out || !a->status) { set_error("null pointer in IttaiGemm"); return ITTAI_E_ARG; }
     if (a->m < 1 || a->n < GN || a->n % GN != 0 || a->k < GK || a->k % GK != 0) {
         set_error("gemm shape M=%d N=%d K=%d: N must be a multiple of %d and K of %d", a->m, a->n, a->k, GN, GK);
@@ -195,24 +196,11 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
         set_error("gemm operands must be 16-byte aligned with leading dimensions that are multiples of 8");
         return ITTAI_E_ARG;
     }
-    // more than one 128-row tile: the two-SM kernel (each CTA of a pair loads 128 rows of A and 128 rows of W per stage)
-    const bool pair = a->m > GM;
-    CUtensorMap tm_a, tm_b;
-    int rc = make_tmap_bf16(&tm_a, a->a, a->m, a->k, ld_a, GM);
+    int rc = make_tmap_bf16(tm_a, a->a, a->m, a->k, ld_a, GM);
     if (rc != ITTAI_OK) return rc;
-    rc = make_tmap_bf16(&tm_b, a->w, a->n, a->k, ld_w, pair ? GN / 2 : 64);
+    rc = make_tmap_bf16(tm_b, a->w, a->n, a->k, ld_w, pair ? GN / 2 : 64);
     if (rc != ITTAI_OK) return rc;
-    static thread_local int attr_dev = -1, n_sms = 0;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (attr_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<64, 8>::kSmem);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
-        e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
-        attr_dev = dev;
-    }
-    GemmArgs g;
+    GemmArgs& g = *gp;
     g.M = a->m; g.N = a->n; g.K = a->k; g.epi = a->epi;
     g.bias = reinterpret_cast<const float*>(a->bias);
     g.residual = reinterpret_cast<const bf16*>(a->residual);
@@ -226,6 +214,26 @@ int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
     g.stats_parts = a->stats_parts;
     g.stats_eps = a->stats_eps;
     if (a->epi == ITTAI_EPI_QKROPE) g.rope = *a->qk_rope; else g.rope = IttaiQkRope{};
+    return ITTAI_OK;
+}
+
+int gemm_bf16_launch(const IttaiGemm* a, cudaStream_t st) {
+    // more than one 128-row tile: the two-SM kernel (each CTA of a pair loads 128 rows of A and 128 rows of W per stage)
+    const bool pair = a != nullptr && a->m > GM;
+    CUtensorMap tm_a, tm_b;
+    GemmArgs g;
+    const int rc = gemm_args_from_abi(a, &g, &tm_a, &tm_b, pair);
+    if (rc != ITTAI_OK) return rc;
+    static thread_local int attr_dev = -1, n_sms = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmCfg<64, 8>::kSmem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemm)");
+        e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(sm count)");
+        attr_dev = dev;
+    }
     if (pair) return gemm2_bf16_launch(tm_a, tm_b, g, st);
     const int tiles = ((a->m + GM - 1) / GM) * (a->n / 64);
     cudaError_t e = launch_pdl(gemm_bf16_kernel<64, 8>, dim3(tiles < n_sms ? tiles : n_sms), dim3(kGemmThreads), GemmCfg<64, 8>::kSmem, st, 1, tm_a, tm_b, g);

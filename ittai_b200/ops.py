@@ -21,11 +21,13 @@ def _stream(t: torch.Tensor):
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Tensor | None = None,
-         residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None,
-         row_stats: torch.Tensor | None = None, col_sums: torch.Tensor | None = None, stats_out: torch.Tensor | None = None,
-         stats_eps: float = 0.0, qk_rope: dict | None = None) -> torch.Tensor:
-    """``out = epilogue(a @ w.T)`` on the tcgen05 GEMM: a [M, K] and w [N, K] bf16 (last dim contiguous), bias fp32 [N],
+def gemm_desc(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Tensor | None = None,
+              residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None,
+              row_stats: torch.Tensor | None = None, col_sums: torch.Tensor | None = None, stats_out: torch.Tensor | None = None,
+              stats_eps: float = 0.0, qk_rope: dict | None = None):
+    """The ``IttaiGemm`` record of ``gemm(...)`` with the same arguments, and its output tensor: ``(record, out)``.
+
+    ``out = epilogue(a @ w.T)`` on the tcgen05 GEMM: a [M, K] and w [N, K] bf16 (last dim contiguous), bias fp32 [N],
     residual bf16 [M, N].  SwiGLU takes interleaved (gate, up) weight rows and returns [M, N/2].  ``row_stats`` (fp32
     [M, 2] from ``row_stats``) with ``col_sums`` (fp32 [N]) folds a LayerNorm over ``a`` into the GEMM: ``w`` is then the
     weight scaled by the LayerNorm gain along K and ``bias`` includes ``W @ beta`` (see ``fold_layernorm``).  ``stats_out``
@@ -67,8 +69,25 @@ def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Ten
         r.kcache_layer, r.vcache_layer = qk_rope["kcache"].data_ptr(), qk_rope["vcache"].data_ptr()
         r.kv_cap, r.eps = qk_rope["kv_cap"], qk_rope["eps"]
         g.qk_rope = C.pointer(r)
+        g._keep = r
+    return g, out
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, **kw) -> torch.Tensor:
+    """One GEMM launch; arguments as in ``gemm_desc``."""
+    g, out = gemm_desc(a, w, status, **kw)
     _C.check(_C.lib().ittai_gemm_bf16_launch(C.byref(g), _stream(a)))
     return out
+
+
+def gemm_chain(descs, flags: torch.Tensor) -> None:
+    """Up to four dependent GEMMs (``gemm_desc`` records; each reads its predecessor's output as ``a``) in one persistent
+    launch.  ``flags``: int32 / uint32 device words, ``len(descs) * 2 * ceil(M / 256)`` of them, zero at launch."""
+    n = len(descs)
+    arr = (_C.Gemm * n)(*descs)
+    m = descs[0].m
+    assert flags.dtype in (torch.int32, torch.uint32) and flags.is_contiguous() and flags.numel() >= n * 2 * ((m + 255) // 256)
+    _C.check(_C.lib().ittai_gemm_chain_launch(arr, n, flags.data_ptr(), _stream(flags)))
 
 
 def row_stats(x: torch.Tensor, eps: float, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -9,6 +9,8 @@ storage with fp32 accumulation, and the rounding points are the eager modules'.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from .. import _C, ops
@@ -75,7 +77,7 @@ class Engine:
         return super().__new__(cls)
 
     @torch.no_grad()
-    def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True, fold_ln=True):
+    def __init__(self, vm, B, tile_n=None, stages=None, warps=None, fold_k=None, group_m=None, kv_block=64, graph=True, fold_ln=True, chain=True):
         vm = _vision_model(vm)
         cfg, emb = vm.config, vm.embeddings
         # Conv2d patch embedding: fixed resolution.  Linear: SigLIP2 NaFlex, whose inputs arrive as patch rows with a
@@ -145,6 +147,11 @@ class Engine:
         # produces it: one buffer for the stream after attention, one for the stream after the MLP
         self.stats_a = torch.zeros(M, D // 128, 2, dtype=torch.float32, device=dev)
         self.stats_m = torch.zeros(M, D // 128, 2, dtype=torch.float32, device=dev)
+        # ``chain``: the GEMMs between two attention kernels (out-proj, fc1, fc2, the next layer's QKV) run as ONE
+        # persistent launch whose tiles wait on per-row-block counters, like the tasks of the reference's persistent kernel
+        # (reference ``:197-333``); needs the folded LayerNorms (no kernel of another kind between the GEMMs) and M > 128
+        self.chain = bool(chain) and self.fold_ln
+        self.chain_flags = torch.zeros(len(self.layers), 4 * 2 * ((M + 255) // 256), dtype=torch.int32, device=dev)
         self.status = ops.new_status(dev)
         self.graph = None if graph else False
 
@@ -159,16 +166,33 @@ class Engine:
         # and may number 256: more than the tensor-memory kernel's 224, so those towers run the register-tile kernel
         kv_max = S if self.conv else 0
         ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m if fold else None)
-        for w in self.layers:
+        def attention():
+            ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
+                          causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
+                          o_strides=(D, hd), max_kv_len=kv_max, q_rows_total=self.M if self.conv else 0,
+                          kv_rows_total=self.M if self.conv else 0, status=st if self.conv else None)
+
+        if self.chain:
+            self.chain_flags.zero_()
+            qkv = lambda w: ops.gemm_desc(self.x, w["qkv_f"][0], st, bias=w["qkv_f"][1], out=self.qkv, row_stats=self.stats_m,
+                                          col_sums=w["qkv_f"][2], stats_eps=eps)[0]
+            _C.check(L.ittai_gemm_bf16_launch(C.byref(qkv(self.layers[0])), ops._stream(self.x)))
+            for i, w in enumerate(self.layers):
+                attention()
+                descs = [ops.gemm_desc(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x, stats_out=self.stats_a)[0],
+                         ops.gemm_desc(self.x, w["fc1_f"][0], st, bias=w["fc1_f"][1], epi=_C.EPI_GELU, out=self.h, row_stats=self.stats_a,
+                                       col_sums=w["fc1_f"][2], stats_eps=eps)[0],
+                         ops.gemm_desc(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x, stats_out=self.stats_m)[0]]
+                if i + 1 < len(self.layers):
+                    descs.append(qkv(self.layers[i + 1]))
+                ops.gemm_chain(descs, self.chain_flags[i])
+        for w in (() if self.chain else self.layers):
             if fold:
                 ops.gemm(self.x, w["qkv_f"][0], st, bias=w["qkv_f"][1], out=self.qkv, row_stats=self.stats_m, col_sums=w["qkv_f"][2], stats_eps=eps)
             else:
                 ops.layernorm_rows(self.x, *w["ln1"], eps, out=self.y)
                 ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
-            ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
-                          causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
-                          o_strides=(D, hd), max_kv_len=kv_max, q_rows_total=self.M if self.conv else 0,
-                          kv_rows_total=self.M if self.conv else 0, status=st if self.conv else None)
+            attention()
             ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x, stats_out=self.stats_a if fold else None)
             if fold:
                 ops.gemm(self.x, w["fc1_f"][0], st, bias=w["fc1_f"][1], epi=_C.EPI_GELU, out=self.h, row_stats=self.stats_a, col_sums=w["fc1_f"][2],
@@ -253,7 +277,7 @@ class Siglip2Embedder:
     (``None`` without a checkpoint), ``.vm``, ``.engine``; ``.embed(pixel_values)`` batches and pads like the reference's
     ``embed`` (``:715-723``: the last batch repeats its final image)."""
 
-    CANDIDATES = ({"fold_ln": True}, {"fold_ln": False})
+    CANDIDATES = ({"fold_ln": True, "chain": True}, {"fold_ln": True, "chain": False}, {"fold_ln": False})
 
     def __init__(self, model_id="google/siglip2-base-patch16-naflex", batch_size=64, device="cuda", tune=None, engine=None):
         self.processor = None
