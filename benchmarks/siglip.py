@@ -46,6 +46,34 @@ def per_op(B: int) -> None:
         out = torch.empty(M, n, device="cuda", dtype=torch.bfloat16)
         t = graph_us(lambda: ops.gemm(a, w, st, bias=bias, residual=r, epi=epi, out=out), 20)
         print("gemm N=%d K=%d epi=%d res=%d  %.1f us  %.0f TF" % (n, k, epi, res, t, 2.0 * M * n * k / t / 1e6))
+    # the four GEMMs between two attention kernels as the encoder runs them (in-place residuals, folded LayerNorms, output
+    # statistics): one by one, and as one chained launch
+    F = 4 * D
+    attn, xx = (torch.randn(M, D, device="cuda").bfloat16() for _ in range(2))
+    h = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    ws = [(torch.randn(n, k, device="cuda") * 0.03).bfloat16() for n, k in ((D, D), (F, D), (D, F), (3 * D, D))]
+    bs = [torch.randn(n, device="cuda") * 0.1 for n in (D, F, D, 3 * D)]
+    cs1, csq = ws[1].float().sum(1), ws[3].float().sum(1)
+    sa, sm = (torch.zeros(M, D // 128, 2, device="cuda") for _ in range(2))
+    flags = torch.zeros(4 * 2 * ((M + 255) // 256), dtype=torch.int32, device="cuda")
+    layer = [dict(a=attn, w=ws[0], bias=bs[0], residual=xx, out=xx, stats_out=sa),
+             dict(a=xx, w=ws[1], bias=bs[1], epi=1, out=h, row_stats=sa, col_sums=cs1, stats_eps=1e-6),
+             dict(a=h, w=ws[2], bias=bs[2], residual=xx, out=xx, stats_out=sm),
+             dict(a=xx, w=ws[3], bias=bs[3], out=qkv, row_stats=sm, col_sums=csq, stats_eps=1e-6)]
+    descs = [ops.gemm_desc(d["a"], d["w"], st, **{k: v for k, v in d.items() if k not in ("a", "w")})[0] for d in layer]
+
+    def one_by_one():
+        for d in layer:
+            ops.gemm(d["a"], d["w"], st, **{k: v for k, v in d.items() if k not in ("a", "w")})
+
+    def chained():
+        flags.zero_()
+        ops.gemm_chain(descs, flags)
+
+    flop = 2.0 * M * (D * D + F * D + D * F + 3 * D * D)
+    for name, fn in (("four GEMMs one by one", one_by_one), ("four GEMMs chained   ", chained)):
+        t = graph_us(fn, 10)
+        print("%s  %.1f us  %.0f TF" % (name, t, flop / t / 1e6))
     ops.check_status(st)
 
 

@@ -150,8 +150,8 @@ class Engine:
         # ``chain``: the GEMMs between two attention kernels (out-proj, fc1, fc2, the next layer's QKV) run as ONE
         # persistent launch whose tiles wait on per-row-block counters, like the tasks of the reference's persistent kernel
         # (reference ``:197-333``); needs the folded LayerNorms (no kernel of another kind between the GEMMs) and M > 128
-        self.chain = bool(chain) and self.fold_ln
-        self.chain_flags = torch.zeros(len(self.layers), 4 * 2 * ((M + 255) // 256), dtype=torch.int32, device=dev)
+        self.chain = bool(chain) and self.fold_ln and M >= 1024      # a few row blocks only: nothing to overlap, one launch per GEMM is faster
+        self.chain_flags = torch.zeros(len(self.layers) + 1, 4 * 2 * ((M + 255) // 256), dtype=torch.int32, device=dev)
         self.status = ops.new_status(dev)
         self.graph = None if graph else False
 
@@ -165,7 +165,9 @@ class Engine:
         # with variable-resolution inputs an image's keys are its first key_len rows (the records in `seqs` say how many)
         # and may number 256: more than the tensor-memory kernel's 224, so those towers run the register-tile kernel
         kv_max = S if self.conv else 0
-        ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m if fold else None)
+        embed = dict(bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m if fold else None)
+        if not self.chain:
+            ops.gemm(self.patches, self.wpe, st, **embed)
         def attention():
             ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
                           causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
@@ -176,7 +178,9 @@ class Engine:
             self.chain_flags.zero_()
             qkv = lambda w: ops.gemm_desc(self.x, w["qkv_f"][0], st, bias=w["qkv_f"][1], out=self.qkv, row_stats=self.stats_m,
                                           col_sums=w["qkv_f"][2], stats_eps=eps)[0]
-            _C.check(L.ittai_gemm_bf16_launch(C.byref(qkv(self.layers[0])), ops._stream(self.x)))
+            # patch embedding + the first QKV projection; then per layer out-proj, fc1, fc2 and the next layer's QKV (after
+            # the last layer: the K/V projection of the pooling head)
+            ops.gemm_chain([ops.gemm_desc(self.patches, self.wpe, st, **embed)[0], qkv(self.layers[0])], self.chain_flags[len(self.layers)])
             for i, w in enumerate(self.layers):
                 attention()
                 descs = [ops.gemm_desc(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x, stats_out=self.stats_a)[0],
@@ -185,6 +189,9 @@ class Engine:
                          ops.gemm_desc(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x, stats_out=self.stats_m)[0]]
                 if i + 1 < len(self.layers):
                     descs.append(qkv(self.layers[i + 1]))
+                else:
+                    descs.append(ops.gemm_desc(self.x, self.kv_f[0], st, bias=self.kv_f[1], out=self.kv, row_stats=self.stats_m,
+                                               col_sums=self.kv_f[2], stats_eps=eps)[0])
                 ops.gemm_chain(descs, self.chain_flags[i])
         for w in (() if self.chain else self.layers):
             if fold:
@@ -202,7 +209,9 @@ class Engine:
                 ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)
             ops.gemm(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x, stats_out=self.stats_m if fold else None)
         # post-LayerNorm + MAP head: probe attends over the tokens, then LayerNorm + MLP with a residual
-        if fold:
+        if self.chain:
+            pass                                         # the last chain wrote self.kv
+        elif fold:
             ops.gemm(self.x, self.kv_f[0], st, bias=self.kv_f[1], out=self.kv, row_stats=self.stats_m, col_sums=self.kv_f[2], stats_eps=eps)
         else:
             ops.layernorm_rows(self.x, *self.post, eps, out=self.y)
