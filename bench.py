@@ -165,7 +165,7 @@ def siglip_leg(dev, rank, barrier, iters: int = 20):
     eng.check()
     assert len(host_out) == iters and bool(torch.isfinite(host_out[-1].float()).all())
     return {"ms": e0.elapsed_time(e1), "iters": iters, "median_single_ms": sorted(singles)[iters // 2], "images": iters * SIGLIP_BATCH, "flops_reference_formula": iters * eng.flops("reference"),
-            "launches_per_forward": 2 + 12 * 5 + 6, "e2e_ms": f0.elapsed_time(f1), "h2d_bytes": host_px.numel() * 4, "d2h_bytes": host_out[0].numel() * 2}
+            "launches_per_forward": eng.launches_per_forward(), "e2e_ms": f0.elapsed_time(f1), "h2d_bytes": host_px.numel() * 4, "d2h_bytes": host_out[0].numel() * 2}
 
 
 def config4_leg(sd, dev, barrier):

@@ -265,6 +265,12 @@ class Engine:
             self._body()
         return self.embeds
 
+    def launches_per_forward(self) -> int:
+        """Kernels in one forward (all inside one CUDA graph)."""
+        n_l = len(self.layers)
+        encoder = (n_l + 1) + n_l if self.chain else 1 + n_l * (5 if self.fold_ln else 7) + (1 if self.fold_ln else 2)
+        return (1 if self.conv else 0) + encoder + 5       # + pooling head: attention, projection, LayerNorm, two MLP GEMMs
+
     def check(self) -> None:
         """Synchronise and raise if any GEMM pipeline wait ran out since construction."""
         ops.check_status(self.status)
