@@ -211,4 +211,55 @@ __device__ __forceinline__ bool wait_word128(const Waiter& w, const void* p, uin
     }
 }
 
+
+// NB words, `stride` words apart, polled together: all loads of a sweep are in flight at once, so a thread that needs NB
+// words pays about one L2 round trip instead of NB of them.  (At NB = 1 this is wait_word.)
+template <int NB>
+__device__ __forceinline__ bool wait_words(const Waiter& w, const uint64_t* p, size_t stride, uint32_t tag, uint32_t (&payload)[NB], int what) {
+    if constexpr (NB == 1) {
+        return wait_word(w, p, tag, payload[0], what);
+    } else {
+        uint32_t spins = 0;
+        for (;;) {
+            uint64_t v[NB];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) v[b] = ld_flagged(p + (size_t)b * stride);
+            bool all = true;
+            uint32_t seen = tag;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                if ((uint32_t)(v[b] >> 32) != tag) { all = false; seen = (uint32_t)(v[b] >> 32); }
+                payload[b] = (uint32_t)v[b];
+            }
+            if (all) return true;
+            if (((++spins) & 1023u) == 0u && !keep_waiting(w.sync, w.status, w.limit, spins, what, seen, tag)) return false;
+        }
+    }
+}
+
+// The same for 128-bit words, `stride` 16-byte words apart: payloads a[b], b2[b], c[b].
+template <int NB>
+__device__ __forceinline__ bool wait_words128(const Waiter& w, const uint4* p, size_t stride, uint32_t tag, uint32_t (&a)[NB], uint32_t (&b2)[NB],
+                                              uint32_t (&c)[NB], int what) {
+    if constexpr (NB == 1) {
+        return wait_word128(w, p, tag, a[0], b2[0], c[0], what);
+    } else {
+        uint32_t spins = 0;
+        for (;;) {
+            uint64_t lo[NB], hi[NB];
+#pragma unroll
+            for (int b = 0; b < NB; ++b) ld_flagged128(p + (size_t)b * stride, lo[b], hi[b]);
+            bool all = true;
+            uint32_t seen = tag;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                if ((uint32_t)(hi[b] >> 32) != tag) { all = false; seen = (uint32_t)(hi[b] >> 32); }
+                a[b] = (uint32_t)lo[b]; b2[b] = (uint32_t)(lo[b] >> 32); c[b] = (uint32_t)hi[b];
+            }
+            if (all) return true;
+            if (((++spins) & 1023u) == 0u && !keep_waiting(w.sync, w.status, w.limit, spins, what, seen, tag)) return false;
+        }
+    }
+}
+
 }  // namespace ittai

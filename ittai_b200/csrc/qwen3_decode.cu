@@ -260,14 +260,15 @@ template <int NB, int K>
 __device__ __forceinline__ bool wait_rows_to_smem(Cta& c, const uint64_t* src, uint32_t tag, int what, const bf16** ring_entry = nullptr) {
     constexpr int V = K / kThreads;              // values per word
     static_assert(V == 4 || V == 6, "one 128-bit word per thread");
-    bool ok = true;
+    uint32_t u0[NB], u1[NB], u2[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) u0[b] = u1[b] = u2[b] = 0u;
+    bool ok = wait_words128<NB>(c.w, reinterpret_cast<const uint4*>(src) + c.tid, kThreads, tag, u0, u1, u2, what);
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
-        uint32_t u0 = 0, u1 = 0, u2 = 0;
-        ok = ok && wait_word128(c.w, reinterpret_cast<const uint4*>(src) + (size_t)b * kThreads + c.tid, tag, u0, u1, u2, what);
         uint32_t* dst = c.xs + b * (FF / 2) + c.tid * (V / 2);
-        dst[0] = u0; dst[1] = u1;
-        if constexpr (V == 6) dst[2] = u2;
+        dst[0] = u0[b]; dst[1] = u1[b];
+        if constexpr (V == 6) dst[2] = u2[b];
     }
     if (ring_entry != nullptr) {
         const unsigned char* ptr = stream_wait(c.st, c.st.consumed, c.w);
@@ -418,10 +419,11 @@ __device__ bool phase_qkv(Cta& c, int l) {
     const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.ln1) + (size_t)l * D + 2 * c.tid);
     uint32_t u[NB];
     bool ok = true;
+    if (l == 0) {
 #pragma unroll
-    for (int b = 0; b < NB; ++b) {
-        if (l == 0) u[b] = ldcg32(reinterpret_cast<const bf16*>(p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * c.tid);
-        else ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_QKV);
+        for (int b = 0; b < NB; ++b) u[b] = ldcg32(reinterpret_cast<const bf16*>(p.embed) + (size_t)c.hdr->tok_s[b] * D + 2 * c.tid);
+    } else {
+        ok = wait_words<NB>(c.w, c.ws.h + c.tid, D / 2, tag, u, ITTAI_PH_QKV);
     }
     int p0, p1;
     split_range(DQKV / 4, c.ncta, c.cta, p0, p1);    // 128-bit words: two row pairs (four outputs) each
@@ -840,9 +842,7 @@ __device__ bool phase_gu(Cta& c, int l) {
     const uint32_t tag = tag_of(c, c.step, l);
     const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.ln2) + (size_t)l * D + 2 * c.tid);
     uint32_t u[NB];
-    bool ok = true;
-#pragma unroll
-    for (int b = 0; b < NB; ++b) ok = ok && wait_word(c.w, c.ws.hmid + b * (D / 2) + c.tid, tag, u[b], ITTAI_PH_GU);
+    bool ok = wait_words<NB>(c.w, c.ws.hmid + c.tid, D / 2, tag, u, ITTAI_PH_GU);
     int u0, u1;
     split_range(FF / 6, c.ncta, c.cta, u0, u1);      // 128-bit words: three units of two activations = four weight rows each
     u0 *= 3; u1 *= 3;
@@ -923,10 +923,7 @@ __device__ bool phase_head(Cta& c) {
     const IttaiQwen3Decode& p = c.p;
     const uint32_t gw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const bf16*>(p.fin_w) + 2 * c.tid);
     uint32_t u[NB];
-    bool ok = true;
-#pragma unroll
-    for (int b = 0; b < NB; ++b)
-        ok = ok && wait_word(c.w, c.ws.h + b * (D / 2) + c.tid, tag_of(c, c.step, p.n_layers), u[b], ITTAI_PH_HEAD);
+    bool ok = wait_words<NB>(c.w, c.ws.h + c.tid, D / 2, tag_of(c, c.step, p.n_layers), u, ITTAI_PH_HEAD);
     if (!norm_pairs_to_smem<NB>(c, u, gw, ok)) return false;
     float xr[32];
     if constexpr (NB == 1) load_xreg(c.xs, c.lane, xr);
