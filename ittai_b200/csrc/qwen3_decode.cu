@@ -43,6 +43,7 @@ struct SmemHdr {
     float sub[kPartFloats * ITTAI_MAX_BATCH];    // partial dot products of the GEMV tiles: [task][16 rows][sequence]
     float candv[Q3_MAX_CTAS];                    // argmax candidates of every CTA
     int candi[Q3_MAX_CTAS];
+    long long t_ready;                           // cycle counter when the current phase had its inputs (in-kernel profile)
 };
 struct SmemAttn {
     float qs[2][HD];                             // rotated, pre-scaled queries of the two heads of a group
@@ -70,10 +71,14 @@ struct Cta {
     Waiter w;
     Stream st;
     int step;           // token index inside this launch
-    long long t_ready;  // cycle counter when the current phase had its inputs (in-kernel profile)
 };
 
 // Tag of the data a (step, layer) produces; layer n_layers names the stream entering the head.  Never zero.
+// In-kernel profile: thread 0 notes when the current phase had its inputs (in shared memory: a stamp kept in the context
+// would hold two registers across every phase, in a kernel that runs at its register limit).
+__device__ __forceinline__ void mark_ready(const Cta& c) {
+    if (c.p.phase_clk != nullptr && c.tid == 0) c.hdr->t_ready = clock64();
+}
 __device__ __forceinline__ uint32_t tag_of(const Cta& c, int step, int l) { return (uint32_t)(step * (c.p.n_layers + 1) + l + 1); }
 
 // CTA-uniform verdict on per-thread waits.
@@ -139,7 +144,9 @@ __device__ void stream_feed(const Cta& c, int k_begin, int k_end) {
     const uint32_t limit = c.w.limit;
     const int L = p.n_layers, PS = kStreamPhases * L + 1;
     int lo, hi;
-    // per-phase: base of this CTA's slice in layer 0, bytes between layers, bytes of the slice
+    // per-phase: base of this CTA's slice in layer 0, bytes between layers, bytes of the slice (tables indexed by the
+    // phase live in local memory: 12 loads per layer in this lane only; the same values as named scalars picked by a
+    // chain of selects were measured 12 us per token slower)
     const char* base[kStreamPhases];
     size_t stride[kStreamPhases];
     uint32_t nbytes[kStreamPhases];
@@ -239,7 +246,7 @@ __device__ __forceinline__ bool norm_pairs_to_smem(Cta& c, const uint32_t (&u)[N
         if (c.lane == 0) c.hdr->red[b * kWarps + c.warp] = v;
     }
     if (cta_or(!ok)) return false;
-    c.t_ready = clock64();
+    mark_ready(c);
 #pragma unroll
     for (int b = 0; b < NB; ++b) {
         float tot = 0.f;
@@ -558,7 +565,7 @@ __device__ bool phase_attn(Cta& c, int l) {
             }
         }
         if (!all_ok(ok)) return false;
-        c.t_ready = clock64();
+        mark_ready(c);
 
         // -- every half-warp runs its own online softmax over the positions it owns (position index = 2*warp + half
         //    modulo 32), with no CTA-wide barrier inside a tile; the 32 private (m, l, o) are merged once at the end.
@@ -693,7 +700,7 @@ __device__ bool phase_attn(Cta& c, int l) {
         }
         cta_sync();
     } else {
-        c.t_ready = clock64();
+        mark_ready(c);
     }
     // -- merge across splits: split s < nc of each (b, g) gathers, from every split of that head, the running max and
     //    sum and its own slice of the outputs
@@ -764,7 +771,7 @@ __device__ bool phase_proj_residual(Cta& c, int what, const uint64_t* x_src, uin
     }
     const bf16* W = nullptr;                                   // this CTA's rows [2*p0, 2*p1), contiguous in the ring
     if (!wait_rows_to_smem<NB, K>(c, x_src, x_tag, what, p1 > p0 ? &W : nullptr)) return false;
-    c.t_ready = clock64();
+    mark_ready(c);
     // The whole attention output of (step, layer) is here, so every cache row appended up to (step, layer) is in place:
     // the feeding lane may fetch the tiles of (step + 1, layer).
     if (epoch != 0u && c.tid == 0) st_release_cta(&c.st.sh->kv_epoch, epoch);
@@ -1105,7 +1112,7 @@ __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
           (int)(threadIdx.x & 31), (int)(threadIdx.x >> 5),                                                       \
           Waiter{wsp.sync, p.status, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit},                     \
           Stream{&reinterpret_cast<SmemHdr*>(smem)->stream, smem + q3_fixed_smem_bytes(nb), ring_bytes, 0u},      \
-          0, 0}
+          0}
 
 template <int NB>
 __global__ void __launch_bounds__(kBlock, 1) q3_decode_kernel(const __grid_constant__ IttaiQwen3Decode p,
@@ -1146,7 +1153,7 @@ __global__ void __launch_bounds__(kBlock, 1) q3_decode_kernel(const __grid_const
                 ok = run_phase<NB>(c, phase, l);
                 if (prof && ok) {
                     const size_t slot = ((size_t)step * (5 * p.n_layers + 1) + l * 5 + phase) * 2;
-                    p.phase_clk[slot] = (uint64_t)c.t_ready;
+                    p.phase_clk[slot] = (uint64_t)c.hdr->t_ready;
                     p.phase_clk[slot + 1] = (uint64_t)clock64();
                 }
             }
@@ -1155,7 +1162,7 @@ __global__ void __launch_bounds__(kBlock, 1) q3_decode_kernel(const __grid_const
             ok = phase_head<NB>(c);
             if (prof && ok) {
                 const size_t slot = ((size_t)step * (5 * p.n_layers + 1) + 5 * p.n_layers) * 2;
-                p.phase_clk[slot] = (uint64_t)c.t_ready;
+                p.phase_clk[slot] = (uint64_t)c.hdr->t_ready;
                 p.phase_clk[slot + 1] = (uint64_t)clock64();
             }
         }
