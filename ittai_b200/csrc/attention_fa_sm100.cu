@@ -44,7 +44,7 @@ __device__ __forceinline__ void fa_arrive(void* bar) {
 }
 __device__ __forceinline__ bool fa_wait(void* bar, uint32_t parity, volatile uint32_t* abort_flag) {
     uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_parked(bar, parity)) {
         if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kFaSpin)) { *abort_flag = 1; return false; }
     }
     return true;

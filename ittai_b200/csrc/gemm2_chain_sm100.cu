@@ -178,7 +178,7 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
             __syncwarp();
             {
                 uint32_t spins = 0;
-                while (!mbar_try_wait(&acc_full[buf], round & 1)) {
+                while (!mbar_try_wait_parked(&acc_full[buf], round & 1)) {
                     if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kSpin2)) { ok = false; break; }
                 }
             }
@@ -228,7 +228,7 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
                     // out = bf16(residual + bf16(module output)); this thread's row piece of the TMA-filled buffer
                     const uint32_t n = rcnt + ch, b = n & 1;
                     uint32_t spins = 0;
-                    while (!mbar_try_wait(&res_bar[b], (n >> 1) & 1)) {
+                    while (!mbar_try_wait_parked(&res_bar[b], (n >> 1) & 1)) {
                         if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kSpin2)) { ok = false; break; }
                     }
                     if (!ok) { *abort_flag = 1; break; }

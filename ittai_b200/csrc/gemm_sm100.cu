@@ -126,7 +126,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             bool ok = true;
             {   // bounded wait that also gives up when another role aborted
                 uint32_t spins = 0;
-                while (!mbar_try_wait(&acc_full[buf], round & 1)) {
+                while (!mbar_try_wait_parked(&acc_full[buf], round & 1)) {
                     if (((++spins) & 255u) == 0u && (*abort_flag || spins >= kGemmSpin)) { ok = false; break; }
                 }
             }

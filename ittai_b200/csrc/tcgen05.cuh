@@ -4,6 +4,10 @@
 #include "common.cuh"
 #include "weight_stream.cuh"   // smem_u32, mbar_init, mbar_expect_tx, mbar_try_wait, fence_mbar_init
 
+#ifndef ITTAI_PARK_NS
+#define ITTAI_PARK_NS 2000u
+#endif
+
 namespace ittai {
 
 // ---- TMA: 2-D tiled load global -> shared, completion counted in bytes on an mbarrier -----------------------
@@ -122,10 +126,23 @@ __device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// try_wait with a suspend-time hint (nanoseconds): the hardware parks the waiting warp until the phase completes or the
+// time runs out, instead of returning to a poll loop that spends issue slots and power.
+__device__ __forceinline__ bool mbar_try_wait_parked(void* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ITTAI_PARK_NS) : "memory");
+    return ok != 0;
+}
 // Bounded mbarrier wait: false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait_bounded(void* bar, uint32_t parity, uint32_t limit) {
     uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_parked(bar, parity)) {
         if (++spins >= limit) return false;
     }
     return true;
