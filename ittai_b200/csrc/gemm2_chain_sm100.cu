@@ -101,7 +101,8 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
                     const uint32_t want = (uint32_t)(kEpiWarps * (P.g[gi - 1].N / PN));
                     uint32_t spins = 0;
                     while (ld_acquire_gpu_u32(f) < want) {
-                        if (((++spins) & 63u) == 0u && (*abort_flag || spins >= kSpin2)) { *abort_flag = 1; break; }
+                        __nanosleep(100);                            // a poll is an L2 round trip: no need to keep several in flight
+                        if (((++spins) & 63u) == 0u && (*abort_flag || spins >= (kSpin2 >> 4))) { *abort_flag = 1; break; }
                     }
                     if (*abort_flag) break;
                     fence_proxy_async();                             // the loads below go through the async proxy
