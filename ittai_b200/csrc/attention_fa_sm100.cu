@@ -34,7 +34,8 @@ struct AttnFaArgs {
     bf16* o;
     long long o_row, o_head;
     int group, causal;
-    int k_seq_rows, k_head_rows;             // cache strides in rows of 128 elements
+    int k_seq_rows, k_head_rows;             // cache layout: strides in rows of 128 elements
+    int k_head_cols;                         // packed layout (heads side by side in a row, sequences by their row offsets): 128, else 0
     float scale_log2;
     uint32_t* status;
 };
@@ -88,6 +89,7 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     const int kv_row = blockIdx.z * a.k_seq_rows + kvh * a.k_head_rows + sinfo.z;   // first key row of this (sequence, kv head)
+    const int kc = kvh * a.k_head_cols;                                             // and its first column
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 128); mbar_init(bar_o, 1);
@@ -98,11 +100,11 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tma_load_2d(sm + kFaQ, &tm_q, head * 128, sinfo.x + r0, bar_q);
         tma_load_2d(sm + kFaQ + 16384, &tm_q, head * 128 + 64, sinfo.x + r0, bar_q);
         mbar_expect_tx(bar_k, 32768);
-        tma_load_2d(sm + kFaK, &tm_k, 0, kv_row, bar_k);
-        tma_load_2d(sm + kFaK + 16384, &tm_k, 64, kv_row, bar_k);
+        tma_load_2d(sm + kFaK, &tm_k, kc, kv_row, bar_k);
+        tma_load_2d(sm + kFaK + 16384, &tm_k, kc + 64, kv_row, bar_k);
         mbar_expect_tx(bar_v, 32768);
-        tma_load_2d(sm + kFaV, &tm_v, 0, kv_row, bar_v);
-        tma_load_2d(sm + kFaV + 16384, &tm_v, 64, kv_row, bar_v);
+        tma_load_2d(sm + kFaV, &tm_v, kc, kv_row, bar_v);
+        tma_load_2d(sm + kFaV + 16384, &tm_v, kc + 64, kv_row, bar_v);
     }
     if (warp == 0) { __syncwarp(); tmem_alloc(tmem_slot, kFaCols); }
     tc_fence_before();
@@ -131,16 +133,16 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     ok = fa_wait(bar_o, (j - 1) & 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(bar_v, 32768);
-                    tma_load_2d(sm + kFaV, &tm_v, 0, kv_row + j * kFaBlk, bar_v);
-                    tma_load_2d(sm + kFaV + 16384, &tm_v, 64, kv_row + j * kFaBlk, bar_v);
+                    tma_load_2d(sm + kFaV, &tm_v, kc, kv_row + j * kFaBlk, bar_v);
+                    tma_load_2d(sm + kFaV + 16384, &tm_v, kc + 64, kv_row + j * kFaBlk, bar_v);
                 }
                 ok = fa_wait(bar_s, ph, abort_flag);
                 if (!ok) break;
                 if (j + 1 < n_blk) {
                     // S is complete, so the K buffer is free: the next block's keys travel during this block's softmax
                     mbar_expect_tx(bar_k, 32768);
-                    tma_load_2d(sm + kFaK, &tm_k, 0, kv_row + (j + 1) * kFaBlk, bar_k);
-                    tma_load_2d(sm + kFaK + 16384, &tm_k, 64, kv_row + (j + 1) * kFaBlk, bar_k);
+                    tma_load_2d(sm + kFaK, &tm_k, kc, kv_row + (j + 1) * kFaBlk, bar_k);
+                    tma_load_2d(sm + kFaK + 16384, &tm_k, kc + 64, kv_row + (j + 1) * kFaBlk, bar_k);
                 }
                 ok = fa_wait(bar_p, ph, abort_flag) && fa_wait(bar_v, ph, abort_flag);
                 if (!ok) break;
@@ -306,9 +308,13 @@ int cuda_fail(cudaError_t e, const char* what);
 
 // Whether the key-loop kernel covers this call: head_dim 128, heads adjacent in the q rows, keys and values as dense rows
 // of 128 elements (the cache layout), identical strides for k and v, more than 64 query rows in some sequence.
+// Keys and values either in the cache layout (rows of 128 elements; heads and sequences whole numbers of rows apart) or
+// packed like the queries (the heads of a token side by side in one row, sequences told apart by their row offsets).
+static bool fa_packed_kv(const IttaiAttention* p) { return p->k_seq == 0 && p->v_seq == 0 && p->k_head == 128 && p->v_head == 128 && p->k_row == p->v_row && p->k_row > 128; }
 bool attn_fa_supported(const IttaiAttention* p) {
-    return p->head_dim == 128 && p->status != nullptr && p->max_q_len > 64 && p->q_head == 128 && p->k_row == 128 && p->v_row == 128 &&
-           p->k_head % 128 == 0 && p->k_seq % 128 == 0 && p->v_head == p->k_head && p->v_seq == p->k_seq && p->q_rows_total > 0 &&
+    const bool cache = p->k_row == 128 && p->v_row == 128 && p->k_head % 128 == 0 && p->k_seq % 128 == 0;
+    return p->head_dim == 128 && p->status != nullptr && p->max_q_len > 64 && p->q_head == 128 && (cache || fa_packed_kv(p)) &&
+           p->v_head == p->k_head && p->v_seq == p->k_seq && p->q_rows_total > 0 &&
            p->kv_rows_total > 0 && ((uintptr_t)p->q & 15) == 0 && ((uintptr_t)p->k & 15) == 0 && ((uintptr_t)p->v & 15) == 0 &&
            ((uintptr_t)p->o & 15) == 0 && p->o_row % 8 == 0 && p->o_head % 8 == 0;
 }
@@ -316,8 +322,10 @@ bool attn_fa_supported(const IttaiAttention* p) {
 int attn_fa_launch(const IttaiAttention* p, cudaStream_t st) {
     CUtensorMap tq, tk, tv;
     int rc = make_tmap_bf16(&tq, p->q, p->q_rows_total, (long long)p->n_heads * 128, p->q_row, 128);
-    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tk, p->k, p->kv_rows_total, 128, 128, 128);
-    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tv, p->v, p->kv_rows_total, 128, 128, 128);
+    const bool packed = fa_packed_kv(p);
+    const long long kv_cols = packed ? (long long)(p->n_heads / p->group) * 128 : 128, kv_ld = packed ? p->k_row : 128;
+    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tk, p->k, p->kv_rows_total, kv_cols, kv_ld, 128);
+    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tv, p->v, p->kv_rows_total, kv_cols, kv_ld, 128);
     if (rc != ITTAI_OK) return rc;
     static thread_local int attr_dev = -1;
     int dev = 0;
@@ -332,7 +340,8 @@ int attn_fa_launch(const IttaiAttention* p, cudaStream_t st) {
     a.o = reinterpret_cast<bf16*>(p->o);
     a.o_row = p->o_row; a.o_head = p->o_head;
     a.group = p->group; a.causal = p->causal;
-    a.k_seq_rows = (int)(p->k_seq / 128); a.k_head_rows = (int)(p->k_head / 128);
+    a.k_seq_rows = packed ? 0 : (int)(p->k_seq / 128); a.k_head_rows = packed ? 0 : (int)(p->k_head / 128);
+    a.k_head_cols = packed ? 128 : 0;
     a.scale_log2 = 1.4426950408889634f * 0.08838834764831845f;
     a.status = p->status;
     const cudaError_t e = launch_pdl(attn_fa_kernel, dim3(p->n_heads, (p->max_q_len + 127) / 128, p->n_seqs), dim3(kFaThreads), kFaSmem, st, 1, tq, tk, tv, a);

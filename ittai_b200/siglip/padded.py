@@ -119,8 +119,10 @@ class PaddedEngine:
         for w in self.layers:
             ops.layernorm_rows(self.x[:, :D], *w["ln1"], eps, out=self.y[:, :D])
             ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
+            # row totals + status words: the tcgen05 key-loop kernel (head_dim 128, keys and values packed like the queries)
             ops.attention(self.qkv, self.qkv[:, Hp:], self.qkv[:, 2 * Hp:], self.attn, self.seqs, max_q_len=S, q_strides=(3 * Hp, hdp),
-                          k_strides=(3 * Hp, hdp, 0), v_strides=(3 * Hp, hdp, 0), o_strides=(Hp, hdp), **att)
+                          k_strides=(3 * Hp, hdp, 0), v_strides=(3 * Hp, hdp, 0), o_strides=(Hp, hdp), max_kv_len=S,
+                          q_rows_total=self.M, kv_rows_total=self.M, status=st, **att)
             ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x)
             ops.layernorm_rows(self.x[:, :D], *w["ln2"], eps, out=self.y[:, :D])
             ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)

@@ -68,3 +68,16 @@ def naflex_inputs(shapes, num_patches: int = 256, seed: int = 3):
         px[b, :h * w] = torch.randn(h * w, 3 * 16 * 16, generator=g)
         mask[b, :h * w] = 1
     return {"pixel_values": px, "pixel_attention_mask": mask, "spatial_shapes": torch.tensor(shapes, dtype=torch.int64)}
+
+
+def build_hf_so400m(naflex: bool = False, n_layers: int = 27, device="cpu", dtype=torch.bfloat16, seed: int = 5):
+    """Random-init tower with the so400m widths (1152 wide, 16 heads of 72, MLP 4304): ``siglip2-so400m-patch14-384`` is
+    the reference benchmark's default model (reference ``benchmarks/siglip.py:7``); ``naflex`` gives the same widths as a
+    variable-resolution tower (patch 16, 256 patches)."""
+    from transformers import Siglip2VisionConfig, Siglip2VisionModel, SiglipVisionConfig, SiglipVisionModel
+    kw = dict(hidden_size=1152, intermediate_size=4304, num_hidden_layers=n_layers, num_attention_heads=16,
+              hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6)
+    torch.manual_seed(seed)
+    m = (Siglip2VisionModel(Siglip2VisionConfig(num_patches=256, patch_size=16, **kw)) if naflex else
+         SiglipVisionModel(SiglipVisionConfig(image_size=384, patch_size=14, **kw)))
+    return m.to(dtype).eval().to(device)

@@ -251,3 +251,28 @@ def test_im2col_embed_pool():
     x = rows[sel.long()].float()
     y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * gain.float()
     assert torch.allclose(pooled, F.normalize(y, dim=-1), atol=1e-5)
+
+
+@gpu
+@pytest.mark.parametrize("lens", [[729, 729], [256, 100, 300], [130]])
+def test_attention_key_loop_kernel_packed_keys(lens):
+    """The tcgen05 key-loop kernel with keys and values packed like the queries (one [T, 3 * H * 128] matrix, dense, no
+    cache): the layout of the zero-padded so400m tower."""
+    from ittai_b200 import ops
+    H, hd = 4, 128
+    D = H * hd
+    T = sum(lens)
+    qkv = _rand(T + 2, 3 * D, seed=13)
+    out = torch.zeros(T + 2, D, dtype=torch.bfloat16, device="cuda")
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    seqs = torch.tensor([[s, n, s, n] for s, n in zip(starts, lens)], dtype=torch.int32, device="cuda")
+    st = ops.new_status(qkv.device)
+    ops.attention(qkv, qkv[:, D:], qkv[:, 2 * D:], out, seqs, n_heads=H, group=1, head_dim=hd, causal=False, max_q_len=max(lens),
+                  q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0), o_strides=(D, hd), max_kv_len=max(lens),
+                  q_rows_total=T + 2, kv_rows_total=T + 2, status=st)
+    ops.check_status(st)
+    for s, n in zip(starts, lens):
+        q, k, v = (qkv[s:s + n, i * D:(i + 1) * D].float().view(n, H, hd).transpose(0, 1) for i in range(3))
+        want = F.scaled_dot_product_attention(q, k, v).transpose(0, 1).reshape(n, D)
+        _check(out[s:s + n], want, f"key-loop attention, packed keys, rows {s}..{s + n}")
+    assert not out[T:].any()

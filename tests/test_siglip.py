@@ -123,13 +123,7 @@ def test_naflex_engine_against_eager_on_device():
 
 # ---- so400m geometry (width 1152, 16 heads of 72, MLP 4304, patch 14): the kernels on zero-padded weights -----------------
 def _so400m(naflex: bool, n_layers: int = 2, device="cpu", dtype=torch.bfloat16, seed: int = 5):
-    from transformers import Siglip2VisionConfig, Siglip2VisionModel, SiglipVisionConfig, SiglipVisionModel
-    kw = dict(hidden_size=1152, intermediate_size=4304, num_hidden_layers=n_layers, num_attention_heads=16,
-              hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6)
-    torch.manual_seed(seed)
-    m = (Siglip2VisionModel(Siglip2VisionConfig(num_patches=256, patch_size=16, **kw)) if naflex else
-         SiglipVisionModel(SiglipVisionConfig(image_size=384, patch_size=14, **kw)))
-    return m.to(dtype).eval().to(device)
+    return hf.build_hf_so400m(naflex, n_layers=n_layers, device=device, dtype=dtype, seed=seed)
 
 
 def test_geometry_dispatch():
