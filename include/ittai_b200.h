@@ -225,6 +225,8 @@ typedef struct IttaiGemm {
                                arriving tile, src/ittai/siglip/kernel.py:335-364); plain stores, no atomics */
     int32_t stats_parts;
     float stats_eps;        /* LayerNorm epsilon, used when stats_parts > 0 */
+    int32_t stats_k;        /* stats_parts > 0: the number of columns of A the statistics are over, when A is zero-padded
+                               beyond its true width (the zero columns add nothing to the sums); 0 = k */
     const IttaiQkRope* qk_rope; /* host pointer, read during the call; required by ITTAI_EPI_QKROPE, NULL otherwise */
 } IttaiGemm;
 

@@ -212,7 +212,7 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
                     const float2* ps = reinterpret_cast<const float2*>(g.row_stats) + (size_t)(row0 + lane) * g.stats_parts;
                     float s1 = 0.f, s2 = 0.f;
                     for (int i = 0; i < g.stats_parts; ++i) { const float2 tt = ps[i]; s1 += tt.x; s2 += tt.y; }
-                    const float inv_k = 1.0f / (float)g.K;
+                    const float inv_k = 1.0f / (float)(g.stats_k > 0 ? g.stats_k : g.K);
                     mean = s1 * inv_k;
                     rstd = rsqrtf(fmaxf(s2 * inv_k - mean * mean, 0.f) + g.stats_eps);
                 }

@@ -232,7 +232,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         const float2* ps = reinterpret_cast<const float2*>(g.row_stats) + (size_t)(row0 + lane) * g.stats_parts;
                         float s1 = 0.f, s2 = 0.f;
                         for (int i = 0; i < g.stats_parts; ++i) { const float2 t = ps[i]; s1 += t.x; s2 += t.y; }
-                        const float inv_k = 1.0f / (float)g.K;
+                        const float inv_k = 1.0f / (float)(g.stats_k > 0 ? g.stats_k : g.K);
                         mean = s1 * inv_k;
                         rstd = rsqrtf(fmaxf(s2 * inv_k - mean * mean, 0.f) + g.stats_eps);
                     }

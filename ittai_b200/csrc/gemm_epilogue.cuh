@@ -20,6 +20,7 @@ struct GemmArgs {
     float* stats_out;        // [M][N/128][2] (sum, sum of squares) per 128-column slice of the output rows, or nullptr
     int stats_parts;         // > 0: row_stats holds [M][parts][2] partial sums over K instead of (mean, rstd)
     float stats_eps;
+    int stats_k;             // columns the folded LayerNorm's statistics are over (A may be zero-padded beyond them); 0 = K
     IttaiQkRope rope;        // ITTAI_EPI_QKROPE only
 };
 

@@ -188,6 +188,7 @@ int gemm_args_from_abi(const IttaiGemm* a, GemmArgs* gp, CUtensorMap* tm_a, CUte
     }
     if (a->stats_out != nullptr && (a->m <= GM || a->epi == ITTAI_EPI_SWIGLU)) { set_error("stats_out needs M > %d and no SwiGLU", GM); return ITTAI_E_ARG; }
     if (a->stats_parts < 0 || a->stats_parts > 64) { set_error("stats_parts %d out of range", a->stats_parts); return ITTAI_E_ARG; }
+    if (a->stats_k < 0 || a->stats_k > a->k) { set_error("stats_k %d: between 0 and K", a->stats_k); return ITTAI_E_ARG; }
     const int ld_a = a->ld_a ? a->ld_a : a->k, ld_w = a->ld_w ? a->ld_w : a->k;
     const int n_out = a->epi == ITTAI_EPI_SWIGLU ? a->n / 2 : a->n;
     const int ld_out = a->ld_out ? a->ld_out : n_out, ld_res = a->ld_res ? a->ld_res : a->n;
@@ -213,6 +214,7 @@ int gemm_args_from_abi(const IttaiGemm* a, GemmArgs* gp, CUtensorMap* tm_a, CUte
     g.stats_out = a->stats_out;
     g.stats_parts = a->stats_parts;
     g.stats_eps = a->stats_eps;
+    g.stats_k = a->stats_k;
     if (a->epi == ITTAI_EPI_QKROPE) g.rope = *a->qk_rope; else g.rope = IttaiQkRope{};
     return ITTAI_OK;
 }

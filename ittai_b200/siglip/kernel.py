@@ -73,7 +73,7 @@ class Engine:
         1152, head_dim 72, MLP 4304, patch 14) the same kernels on zero-padded weights (``padded.PaddedEngine``)."""
         if cls is Engine and not fits_fast_path(_vision_model(vm).config):
             from .padded import PaddedEngine
-            return PaddedEngine(vm, B, graph=kw.get("graph", True))
+            return PaddedEngine(vm, B, **{k: v for k, v in kw.items() if k in ("graph", "fold_ln", "chain")})
         return super().__new__(cls)
 
     @torch.no_grad()

@@ -12,6 +12,7 @@ as its own pass over the true width (the statistics must not see the padding).  
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 
 import torch
@@ -28,7 +29,7 @@ class PaddedEngine:
     """Same surface as ``Engine``: ``forward(inputs) -> bf16 [B, D]`` view of a persistent buffer, ``check()``, ``flops()``."""
 
     @torch.no_grad()
-    def __init__(self, vm, B, graph=True, **ignored):
+    def __init__(self, vm, B, graph=True, fold_ln=True, chain=True, **ignored):
         from .kernel import _vision_model
         vm = _vision_model(vm)
         cfg, emb = vm.config, vm.embeddings
@@ -89,6 +90,26 @@ class PaddedEngine:
         self.hln = (f(h.layernorm.weight).contiguous(), f(h.layernorm.bias).contiguous())
         self.hw1, self.hb1 = bf(pad2(h.mlp.fc1.weight, Fp, Dp)), F.pad(f(h.mlp.fc1.bias), (0, Fp - Fm)).contiguous()
         self.hw2, self.hb2 = bf(pad2(h.mlp.fc2.weight, Dp, Fp)), F.pad(f(h.mlp.fc2.bias), (0, Dp - D)).contiguous()
+        # LayerNorm folded into the GEMM that follows it (as in ``Engine``): W' = W * gain along K (zero in the padding
+        # columns), row sums of the rounded W', bias' = bias + W beta; the producing GEMM's epilogue writes the row sums
+        # and the consuming epilogue finishes mean and rstd over the TRUE width (``stats_k``).
+        self.fold_ln = bool(fold_ln) and M > 128
+        self.chain = bool(chain) and self.fold_ln and M >= 1024
+
+        def folded(w_bf16, bias, ln):
+            g, beta = (F.pad(t, (0, Dp - D)) for t in ln)
+            wf = w_bf16.float()
+            wp = (wf * g).to(torch.bfloat16).contiguous()
+            return wp, (bias + wf @ beta).contiguous(), wp.float().sum(1).contiguous()
+
+        if self.fold_ln:
+            for w in self.layers:
+                w["qkv_f"] = folded(w["wqkv"], w["bqkv"], w["ln1"])
+                w["fc1_f"] = folded(w["w1"], w["b1"], w["ln2"])
+            self.kv_f = folded(self.wkv, self.bkv, self.post)
+            self.stats_a = torch.zeros(M, Dp // 128, 2, dtype=torch.float32, device=dev)
+            self.stats_m = torch.zeros(M, Dp // 128, 2, dtype=torch.float32, device=dev)
+            self.chain_flags = torch.zeros(len(self.layers) + 1, 4 * 2 * ((M + 255) // 256), dtype=torch.int32, device=dev)
         z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
         self.pos = z(M, Dp)
         if self.conv:
@@ -114,22 +135,46 @@ class PaddedEngine:
             p = self.p
             rows = self.pixels.unfold(2, p, p).unfold(3, p, p).permute(0, 2, 3, 1, 4, 5).reshape(self.M, self.Kp0)
             self.patches[:, :self.Kp0].copy_(rows)
-        ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x)
         att = dict(n_heads=H, group=1, head_dim=hdp, causal=False)
-        for w in self.layers:
-            ops.layernorm_rows(self.x[:, :D], *w["ln1"], eps, out=self.y[:, :D])
-            ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
+
+        def attention():
             # row totals + status words: the tcgen05 key-loop kernel (head_dim 128, keys and values packed like the queries)
             ops.attention(self.qkv, self.qkv[:, Hp:], self.qkv[:, 2 * Hp:], self.attn, self.seqs, max_q_len=S, q_strides=(3 * Hp, hdp),
                           k_strides=(3 * Hp, hdp, 0), v_strides=(3 * Hp, hdp, 0), o_strides=(Hp, hdp), max_kv_len=S,
                           q_rows_total=self.M, kv_rows_total=self.M, status=st, **att)
-            ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x)
-            ops.layernorm_rows(self.x[:, :D], *w["ln2"], eps, out=self.y[:, :D])
-            ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)
-            ops.gemm(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x)
-        # post-LayerNorm + MAP head: the probe attends over the image's tokens, then LayerNorm + MLP with a residual
-        ops.layernorm_rows(self.x[:, :D], *self.post, eps, out=self.y[:, :D])
-        ops.gemm(self.y, self.wkv, st, bias=self.bkv, out=self.kv)
+
+        if self.fold_ln:
+            ln = dict(stats_eps=eps, stats_k=D)
+            embed = ops.gemm_desc(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m)[0]
+            qkv = lambda w: ops.gemm_desc(self.x, w["qkv_f"][0], st, bias=w["qkv_f"][1], out=self.qkv, row_stats=self.stats_m,
+                                          col_sums=w["qkv_f"][2], **ln)[0]
+            run = (lambda descs, flags: ops.gemm_chain(descs, flags)) if self.chain else \
+                  (lambda descs, flags: [_C.check(_C.lib().ittai_gemm_bf16_launch(C.byref(d), ops._stream(self.x))) for d in descs])
+            if self.chain:
+                self.chain_flags.zero_()
+            run([embed, qkv(self.layers[0])], self.chain_flags[len(self.layers)])
+            for i, w in enumerate(self.layers):
+                attention()
+                descs = [ops.gemm_desc(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x, stats_out=self.stats_a)[0],
+                         ops.gemm_desc(self.x, w["fc1_f"][0], st, bias=w["fc1_f"][1], epi=_C.EPI_GELU, out=self.h, row_stats=self.stats_a,
+                                       col_sums=w["fc1_f"][2], **ln)[0],
+                         ops.gemm_desc(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x, stats_out=self.stats_m)[0]]
+                descs.append(qkv(self.layers[i + 1]) if i + 1 < len(self.layers) else
+                             ops.gemm_desc(self.x, self.kv_f[0], st, bias=self.kv_f[1], out=self.kv, row_stats=self.stats_m, col_sums=self.kv_f[2], **ln)[0])
+                run(descs, self.chain_flags[i])
+        else:
+            ops.gemm(self.patches, self.wpe, st, bias=self.bpe, residual=self.pos, out=self.x)
+            for w in self.layers:
+                ops.layernorm_rows(self.x[:, :D], *w["ln1"], eps, out=self.y[:, :D])
+                ops.gemm(self.y, w["wqkv"], st, bias=w["bqkv"], out=self.qkv)
+                attention()
+                ops.gemm(self.attn, w["wo"], st, bias=w["bo"], residual=self.x, out=self.x)
+                ops.layernorm_rows(self.x[:, :D], *w["ln2"], eps, out=self.y[:, :D])
+                ops.gemm(self.y, w["w1"], st, bias=w["b1"], epi=_C.EPI_GELU, out=self.h)
+                ops.gemm(self.h, w["w2"], st, bias=w["b2"], residual=self.x, out=self.x)
+            # post-LayerNorm + MAP head: the probe attends over the image's tokens, then LayerNorm + MLP with a residual
+            ops.layernorm_rows(self.x[:, :D], *self.post, eps, out=self.y[:, :D])
+            ops.gemm(self.y, self.wkv, st, bias=self.bkv, out=self.kv)
         ops.attention(self.probe_q, self.kv, self.kv[:, Hp:], self.pool_a, self.pool_seqs, max_q_len=1, q_strides=(0, hdp),
                       k_strides=(2 * Hp, hdp, 0), v_strides=(2 * Hp, hdp, 0), o_strides=(Hp, hdp), **att)
         ops.gemm(self.pool_a, self.who, st, bias=self.bho, out=self.pool_r)
@@ -175,6 +220,12 @@ class PaddedEngine:
 
     def check(self) -> None:
         ops.check_status(self.status)
+
+    def launches_per_forward(self) -> int:
+        """Kernels in one forward (all inside one CUDA graph; the patch rows of a fixed-resolution tower come from torch ops)."""
+        n_l = len(self.layers)
+        encoder = (n_l + 1) + n_l if self.chain else 1 + n_l * (5 if self.fold_ln else 7) + (1 if self.fold_ln else 2)
+        return encoder + 5
 
     def flops(self, formula: str = "reference") -> float:
         """FLOPs of one forward at the TRUE widths (the padding is overhead, not work); formulas as in ``Engine.flops``."""

@@ -160,6 +160,16 @@ def test_so400m_geometry_against_eager(naflex):
     print("so400m", "naflex" if naflex else "patch14-384", "min cos vs bf16 eager", cos.min().item(), "vs fp32 eager", cos32.min().item())
     assert out.shape == (B, 1152) and cos.min() >= 0.9995 and cos32.min() >= 0.9995
     assert torch.equal(emb.embed(inp if naflex else inp["pixel_values"]).float().cpu(), out)       # graph replay
+    # the same tower with the separate LayerNorm pass, and with one GEMM per launch: same embeddings within the gate, and
+    # chained vs unchained bit-identical
+    from ittai_b200.siglip.kernel import Engine
+    for kw in (dict(fold_ln=False), dict(chain=False)):
+        alt = Siglip2Embedder(vm, batch_size=B, engine=Engine(vm, B, **kw))
+        got = alt.embed(inp if naflex else inp["pixel_values"]).float().cpu()
+        alt.engine.check()
+        assert F.cosine_similarity(got, want, dim=-1).min() >= 0.9995
+        if "chain" in kw and emb.engine.chain:
+            assert torch.equal(got, out)
 
 
 @gpu
