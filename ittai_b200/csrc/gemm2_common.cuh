@@ -10,7 +10,10 @@
 namespace ittai {
 
 constexpr int PM = 256, PN = 256, PK = 64;   // pair tile
-constexpr int kStages2 = 5;                       // 4, 5 and 6 stages measured the same: the main loop is supply-bound
+#ifndef ITTAI_GEMM2_STAGES
+#define ITTAI_GEMM2_STAGES 5
+#endif
+constexpr int kStages2 = ITTAI_GEMM2_STAGES;                       // 4, 5 and 6 stages measured the same: the main loop is supply-bound
 constexpr int kEpiWarps = 8;                      // 2 warps per TMEM lane quarter (16 warps were slower: the epilogue is
                                                   // bound by the conversion pipe and shared memory, not by latency)
 constexpr int kEpiCols = PN / (kEpiWarps / 4);    // accumulator columns per epilogue warp
