@@ -3,9 +3,10 @@
 tower (``:33``).  The reference's inputs (a hub checkpoint and one COCO image) are not available offline, so the tower
 is the ViT-B/16-224 configuration with seeded random weights and the pixels are N(0, 1) (seed 3).
 
-  python benchmarks/siglip.py [batch=64] [--ours-only] [--compile] [--per-op] [--so400m]
+  python benchmarks/siglip.py [batch=64] [--ours-only] [--compile] [--per-op] [--so400m] [--naflex]
 
-``--so400m`` takes the reference benchmark's default geometry instead (so400m-patch14-384: 27 layers, width 1152, 16 heads
+``--naflex`` takes the variable-resolution base tower (the reference wrapper's default model family: patch rows, 256 patches
+per image, here all of them valid).  ``--so400m`` takes the reference benchmark's default geometry instead (so400m-patch14-384: 27 layers, width 1152, 16 heads
 of 72, MLP 4304, 729 tokens per image), which runs on zero-padded weights.
 
 ``--per-op`` prints the timings of one encoder layer's kernels instead (each repeated inside one CUDA graph).
@@ -85,12 +86,16 @@ def main():
     if "--per-op" in sys.argv:
         per_op(B)
         return
-    so400m = "--so400m" in sys.argv
-    vm = hf.build_hf_so400m(device="cuda") if so400m else hf.build_hf(seed=2, device="cuda")
+    so400m, naflex = "--so400m" in sys.argv, "--naflex" in sys.argv
+    vm = hf.build_hf_so400m(device="cuda") if so400m else hf.build_hf_naflex(device="cuda") if naflex else hf.build_hf(seed=2, device="cuda")
     emb = Siglip2Embedder(vm, batch_size=B)
-    px = torch.randn(B, 3, 384, 384, generator=torch.Generator().manual_seed(3)).cuda() if so400m else hf.pixels(B, seed=3).cuda()
-    inp = {"pixel_values": px}
-    kw = {"pixel_values": px.to(torch.bfloat16)}
+    if naflex:
+        inp = {k: v.cuda() for k, v in hf.naflex_inputs([(16, 16)] * B).items()}
+        kw = dict(inp, pixel_values=inp["pixel_values"].to(torch.bfloat16))
+    else:
+        px = torch.randn(B, 3, 384, 384, generator=torch.Generator().manual_seed(3)).cuda() if so400m else hf.pixels(B, seed=3).cuda()
+        inp = {"pixel_values": px}
+        kw = {"pixel_values": px.to(torch.bfloat16)}
     with torch.inference_mode():
         t_eager = float("nan") if "--ours-only" in sys.argv else ms(lambda: vm(**kw))
         ref = vm(**kw).pooler_output.float()

@@ -1,17 +1,17 @@
 // Dense attention for short sequences (SigLIP: 196 tokens, head_dim 64) on tcgen05: S = Q K^T and O = P V are
 // tensor-memory MMAs.  The reference's attention task (src/ittai/siglip/kernel.py:366-500) keeps Q resident and streams
-// K/V blocks through mma.sync; with at most 224 keys the whole of K and V fits in shared memory, so here there is no
+// K/V blocks through mma.sync; with at most 256 keys the whole of K and V fits in shared memory, so here there is no
 // key loop at all.
 //
 // One persistent CTA per SM holds two independent groups of 9 warps.  A group walks its share of the (sequence, head)
 // items; per item it loads K and V once and handles the one or two tiles of 128 query rows one after the other.  The
-// next item's Q and K are fetched as soon as the last score MMA of the current item has completed, its V once the last
-// PV MMA has, so the loads hide behind the softmax and the epilogue of the tile in flight; barriers and tensor memory
-// are set up once per CTA.  The two groups share nothing but the SM: while one is in its softmax pass the other is
+// next tile's Q (and after an item's last tile the next item's K) is fetched as soon as the current score MMAs have
+// completed, the next item's V once the last PV MMA has, so the loads hide behind the softmax and the epilogue of the
+// tile in flight; barriers and tensor memory are set up once per CTA.  The two groups share nothing but the SM: while one is in its softmax pass the other is
 // usually in its MMAs or its epilogue.
 //
-// The keys are handled as two halves of up to 112, each with its own score MMA, its own softmax threads and its own
-// PV MMA into its own accumulator; the halves meet only in the epilogue.  A softmax thread owns one query row of one
+// The keys are handled as two halves (112 + the rest up to 224 keys, 128 + the rest above), each with its own score
+// MMA, its own softmax threads and its own PV MMA into its own accumulator; the halves meet only in the epilogue.  A softmax thread owns one query row of one
 // half and makes ONE pass over its score columns: p = 2^(s * scale - ref), where ref is the maximum of the row's first
 // chunk of 16 columns, raised only when the running row sum passes 2^60 (then the P chunks already written and the sum
 // are rescaled: a rare, warp-uniform branch).  A lagging ref costs no accuracy: P is bf16 and the sums are fp32, both
@@ -20,8 +20,8 @@
 //
 // Roles in a group: warp 0 (one lane) issues the TMA loads and every MMA.  Warps 1-8 are the softmax: two warps per
 // TMEM lane quarter (one per half of the keys), one thread per query row; in the epilogue each takes half of the output
-// columns.  TMEM (256 columns per group): half A's scores in 0..111, half B's in 128..239; P of a half as packed bf16
-// over the first 56 columns of that half's scores, each chunk written behind the reads of the thread that owns it; O_A
+// columns.  TMEM (256 columns per group): half A's scores from column 0, half B's from 128; P of a half as packed bf16
+// over the first half of that half's score columns, each chunk written behind the reads of the thread that owns it; O_A
 // in 64..127 and O_B in 192..255, written once every score column has been consumed.
 // Every wait is an mbarrier wait with a bound; on expiry the abort flag routes all roles to the common exit, where
 // TMEM is freed.
@@ -31,8 +31,9 @@
 
 namespace ittai {
 
-constexpr int kTcKeys = 224;                 // most keys per sequence (a multiple of 16)
-constexpr int kTcHalf = 112;                 // keys per half
+constexpr int kTcKeys = 256;                 // most keys per sequence (a multiple of 16)
+// keys of the first half: 112 up to 224 keys (SigLIP's 196 tokens: 112 + 96, seven and six chunks of 16 per thread), 128 above
+__host__ __device__ constexpr int tc_half(int n_keys) { return n_keys > 224 ? 128 : 112; }
 constexpr int kTcHD = 64;
 constexpr int kTcGroup = 288;                // threads of a group: 1 issuing warp + 8 softmax warps
 constexpr int kTcThreads = 2 * kTcGroup;
@@ -40,12 +41,15 @@ constexpr uint32_t kTcCols = 256;            // tensor-memory columns of a group
 constexpr uint32_t kTcColB = 128;            // first score / P column of half B
 constexpr uint32_t kTcOColA = 64, kTcOColB = 192;
 constexpr uint32_t kTcSpin = 1u << 22;
-// shared-memory plan of a group (bytes, every tile 1024-aligned)
-constexpr uint32_t kOffQ = 0;                // [2 query tiles][128 rows][128 B]
-constexpr uint32_t kOffK = 2 * 16384;        // [224 rows][128 B]
-constexpr uint32_t kOffV = kOffK + kTcKeys * 128;
-constexpr uint32_t kOffStage = kOffV + kTcKeys * 128;   // [128 rows][128 B] output staging tile
-constexpr uint32_t kOffBar = kOffStage + 16384;
+// shared-memory plan of a group (bytes, every tile 1024-aligned): query tiles [128 rows][128 B], K and V [box rows][128 B],
+// the output staging tile [128 rows][128 B].  With loads of 224 rows there is room for two query tiles (the next tile's Q
+// is fetched while the current one is still being read); with 256 rows for one.
+__host__ __device__ constexpr uint32_t tc_off_k(int kv_box) { return kv_box > 224 ? 16384u : 32768u; }
+__host__ __device__ constexpr uint32_t tc_off_v(int kv_box) { return tc_off_k(kv_box) + (uint32_t)kv_box * 128u; }
+__host__ __device__ constexpr uint32_t tc_off_stage(int kv_box) { return tc_off_v(kv_box) + (uint32_t)kv_box * 128u; }
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffBar = 32768 + 2 * 224 * 128 + 16384;
+static_assert(tc_off_stage(224) + 16384 <= kOffBar && tc_off_stage(256) + 16384 <= kOffBar, "both plans end before the barriers");
 constexpr uint32_t kOffX = kOffBar + 128;    // float [2 stats][2 halves][128 rows]
 constexpr uint32_t kTcGroupSmem = (kOffX + 2048 + 1023) & ~1023u;
 constexpr uint32_t kTcSmem = 2 * kTcGroupSmem + 1024;
@@ -75,6 +79,7 @@ __device__ __forceinline__ float ex2_fast(float x) {
     return y;
 }
 
+template <int KVBOX>           // rows of a K / V load: 224 (two query-tile buffers) or 256 (one)
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const AttnTcArgs a) {
@@ -85,20 +90,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int tid = threadIdx.x - grp * kTcGroup;
     unsigned char* sm = sm0 + grp * kTcGroupSmem;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(sm + kOffBar);
-    unsigned long long* bar_load = bars;          // Q tiles and K landed                             (one phase per item)
+    unsigned long long* bar_k = bars;             // K landed                                         (one phase per item)
     unsigned long long* bar_v = bars + 1;         // V landed                                         (one phase per item)
+    unsigned long long* bar_q = bars + 8;         // Q tile landed                                    (one phase per query tile)
     unsigned long long* bar_s = bars + 2;         // [2]: scores of half A / half B ready             (one phase per query tile)
     unsigned long long* bar_p = bars + 4;         // [2]: P of half A / half B written, 128 arrivals  (one phase per query tile)
     unsigned long long* bar_o = bars + 6;         // O_A and O_B ready                                (one phase per query tile)
     unsigned long long* bar_free = bars + 7;      // O read back: tensor memory may be overwritten, 256 arrivals
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm0 + kOffBar + 96);      // CTA-wide, in group 0's region
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm0 + kOffBar + 96);      // CTA-wide, in group 0's region (behind its 9 barriers)
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* xref = reinterpret_cast<float*>(sm + kOffX);    // [half][row]: the reference the row's P is scaled by
     float* xsum = xref + 256;                              // [half][row]: sum of that P
 
     const int warp = tid >> 5, lane = tid & 31;
+    constexpr uint32_t kOffK = tc_off_k(KVBOX), kOffV = tc_off_v(KVBOX), kOffStage = tc_off_stage(KVBOX);
+    constexpr uint32_t n_qbuf = KVBOX > 224 ? 1u : 2u;
     if (tid == 0) {
-        mbar_init(bar_load, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_s + 1, 1);
+        mbar_init(bar_k, 1); mbar_init(bar_q, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_s + 1, 1);
         mbar_init(bar_p, 128); mbar_init(bar_p + 1, 128); mbar_init(bar_o, 1); mbar_init(bar_free, 256);
         if (grp == 0) *abort_flag = 0;
         fence_mbar_init();
@@ -115,20 +123,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (warp == 0) {
         if (lane == 0) {
             // the sequence record of an item: {first query row, queries, first key row, keys}
-            auto issue_qk = [&](int it, const int4& si) {
-                const int head = it % a.n_heads, nt = min(2, max(1, (si.y + 127) >> 7));
-                mbar_expect_tx(bar_load, nt * 128 * 128 + kTcKeys * 128);
-                for (int mt = 0; mt < nt; ++mt) tma_load_2d(sm + kOffQ + mt * 16384, &tm_q, head * kTcHD, si.x + mt * 128, bar_load);
-                tma_load_2d(sm + kOffK, &tm_k, (head / a.group) * kTcHD, si.z, bar_load);
+            auto issue_q = [&](int it, const int4& si, int mt, uint32_t tile) {      // `tile`: running tile number, picks the buffer
+                mbar_expect_tx(bar_q, 128 * 128);
+                tma_load_2d(sm + kOffQ + (tile % n_qbuf) * 16384, &tm_q, (it % a.n_heads) * kTcHD, si.x + mt * 128, bar_q);
+            };
+            auto issue_k = [&](int it, const int4& si) {
+                mbar_expect_tx(bar_k, KVBOX * 128);
+                tma_load_2d(sm + kOffK, &tm_k, ((it % a.n_heads) / a.group) * kTcHD, si.z, bar_k);
             };
             auto issue_v = [&](int it, const int4& si) {
-                mbar_expect_tx(bar_v, kTcKeys * 128);
+                mbar_expect_tx(bar_v, KVBOX * 128);
                 tma_load_2d(sm + kOffV, &tm_v, ((it % a.n_heads) / a.group) * kTcHD, si.z, bar_v);
             };
             int4 snext = make_int4(0, 0, 0, 0);
-            if (first < a.n_items) { snext = a.seqs[first / a.n_heads]; issue_qk(first, snext); issue_v(first, snext); }
+            if (first < a.n_items) { snext = a.seqs[first / a.n_heads]; issue_q(first, snext, 0, 0u); issue_k(first, snext); issue_v(first, snext); }
             const uint64_t dk = umma_desc_sw128(sm + kOffK), dv = umma_desc_sw128(sm + kOffV);
-            const uint64_t dkb = dk + (uint64_t)((kTcHalf * 128) >> 4);
             constexpr uint32_t idesc_o = umma_idesc_bf16(128, kTcHD) | umma_idesc_b_mn;
             uint32_t tcount = 0, icount = 0;
             bool ok = true;
@@ -139,18 +148,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (more) snext = a.seqs[(it + stride) / a.n_heads];     // long before it is used
                 const int n_tiles = min(2, max(1, (sinfo.y + 127) >> 7));
                 const int n_keys = max(16, (sinfo.w + 15) & ~15);
-                const int n_a = min(n_keys, kTcHalf), n_b = n_keys - n_a;
+                const int half = tc_half(n_keys), n_a = min(n_keys, half), n_b = n_keys - n_a;
+                const uint64_t dkb = dk + (uint64_t)((half * 128) >> 4);
                 const uint32_t idesc_a = umma_idesc_bf16(128, n_a), idesc_b = umma_idesc_bf16(128, max(n_b, 16));
-                ok = mbar_wait_abortable(bar_load, icount & 1u, abort_flag);
+                ok = mbar_wait_abortable(bar_k, icount & 1u, abort_flag);
 #pragma unroll 1
                 for (int mt = 0; ok && mt < n_tiles; ++mt, ++tcount) {
                     const uint32_t ph = tcount & 1u;
                     const bool last = mt == n_tiles - 1;
-                    if (tcount > 0) ok = mbar_wait_abortable(bar_free, ph ^ 1u, abort_flag);   // the tile before has read its O back
+                    ok = mbar_wait_abortable(bar_q, ph, abort_flag);
+                    if (ok && tcount > 0) ok = mbar_wait_abortable(bar_free, ph ^ 1u, abort_flag);   // the tile before has read its O back
                     if (!ok) break;
                     // ---- S = Q K^T per half: 4 k-steps of 16 head dims each
                     tc_fence_after();
-                    const uint64_t dq = umma_desc_sw128(sm + kOffQ + mt * 16384);
+                    const uint64_t dq = umma_desc_sw128(sm + kOffQ + (tcount % n_qbuf) * 16384);
 #pragma unroll
                     for (int k = 0; k < kTcHD / 16; ++k) umma_bf16(tmem_base, dq + 2 * k, dk + 2 * k, idesc_a, k > 0 ? 1u : 0u);
                     umma_commit(bar_s);
@@ -159,11 +170,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                         for (int k = 0; k < kTcHD / 16; ++k) umma_bf16(tmem_base + kTcColB, dq + 2 * k, dkb + 2 * k, idesc_b, k > 0 ? 1u : 0u);
                     }
                     umma_commit(bar_s + 1);          // also without a second half: the barrier keeps one phase per tile
-                    if (last && more) {
-                        // the item's last score MMA has read Q and K: fetch the next item's
-                        ok = mbar_wait_abortable(bar_s + 1, ph, abort_flag);
-                        if (!ok) break;
-                        issue_qk(it + stride, snext);
+                    if (!last || more) {
+                        // the next tile's Q: at once into the other buffer, or into the only one when the score MMAs have
+                        // read it; the next item's K when this item's last score MMA has read K
+                        const int q_it = last ? it + stride : it, q_mt = last ? 0 : mt + 1;
+                        const int4& q_si = last ? snext : sinfo;
+                        if (n_qbuf == 2u) issue_q(q_it, q_si, q_mt, tcount + 1);
+                        if (n_qbuf == 1u || last) {
+                            ok = mbar_wait_abortable(bar_s + 1, ph, abort_flag);
+                            if (!ok) break;
+                        }
+                        if (n_qbuf == 1u) issue_q(q_it, q_si, q_mt, tcount + 1);
+                        if (last) issue_k(it + stride, snext);
                     }
                     // ---- O = P V per half: P from tensor memory, V rows (keys) 16 at a time.  The two halves
                     // accumulate into different columns, so their MMAs alternate: an MMA of this shape is bound by its
@@ -177,7 +195,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     for (int ks = 0; ks < n_a / 16; ++ks) {
                         umma_bf16_tmem_a(tmem_base + kTcOColA, tmem_base + 8 * ks, dv + (uint64_t)ks * (2048 >> 4), idesc_o, ks > 0 ? 1u : 0u);
                         if (ks < n_b / 16)
-                            umma_bf16_tmem_a(tmem_base + kTcOColB, tmem_base + kTcColB + 8 * ks, dv + (uint64_t)(kTcHalf / 16 + ks) * (2048 >> 4), idesc_o, ks > 0 ? 1u : 0u);
+                            umma_bf16_tmem_a(tmem_base + kTcOColB, tmem_base + kTcColB + 8 * ks, dv + (uint64_t)(half / 16 + ks) * (2048 >> 4), idesc_o, ks > 0 ? 1u : 0u);
                     }
                     umma_commit(bar_o);
                     if (last && more) {
@@ -208,8 +226,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const int q_len = sinfo.y, kv_len = sinfo.w;
             const int n_tiles = min(2, max(1, (q_len + 127) >> 7));
             const int n_keys = max(16, (kv_len + 15) & ~15);
-            const int n_a = min(n_keys, kTcHalf), n_b = n_keys - n_a;
-            const int c_lo = hf * kTcHalf, c_hi = c_lo + (hf ? n_b : n_a);
+            const int half = tc_half(n_keys), n_a = min(n_keys, half), n_b = n_keys - n_a;
+            const int c_lo = hf * half, c_hi = c_lo + (hf ? n_b : n_a);
             const bool has = c_lo < c_hi;                    // false for half B when the sequence has at most 112 keys
 #pragma unroll 1
             for (int mt = 0; mt < n_tiles; ++mt, ++tcount) {
@@ -401,14 +419,16 @@ int attn_tc_launch(const IttaiAttention* p, cudaStream_t st) {
     CUtensorMap tq, tk, tv;
     const int kv_heads = p->n_heads / p->group;
     int rc = make_tmap_bf16(&tq, p->q, p->q_rows_total, (long long)p->n_heads * 64, p->q_row, 128);
-    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tk, p->k, p->kv_rows_total, (long long)kv_heads * 64, p->k_row, kTcKeys);
-    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tv, p->v, p->kv_rows_total, (long long)kv_heads * 64, p->v_row, kTcKeys);
+    const int kv_box = p->max_kv_len > 224 ? 256 : 224;        // the shorter box spares SigLIP's 196 keys an eighth of the traffic
+    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tk, p->k, p->kv_rows_total, (long long)kv_heads * 64, p->k_row, kv_box);
+    if (rc == ITTAI_OK) rc = make_tmap_bf16(&tv, p->v, p->kv_rows_total, (long long)kv_heads * 64, p->v_row, kv_box);
     if (rc != ITTAI_OK) return rc;
     static thread_local int attr_dev = -1, n_sms = 1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem);
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<224>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attn_tc_kernel)");
         cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
         attr_dev = dev;
@@ -423,7 +443,8 @@ int attn_tc_launch(const IttaiAttention* p, cudaStream_t st) {
     a.n_heads = p->n_heads;
     a.n_items = p->n_heads * p->n_seqs;
     const int grid = std::max(1, std::min(n_sms, a.n_items));
-    const cudaError_t e = launch_pdl(attn_tc_kernel, dim3(grid), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a);
+    const cudaError_t e = kv_box == 224 ? launch_pdl(attn_tc_kernel<224>, dim3(grid), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a)
+                                        : launch_pdl(attn_tc_kernel<256>, dim3(grid), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a);
     return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_tc_kernel");
 }
 

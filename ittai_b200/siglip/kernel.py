@@ -162,17 +162,16 @@ class Engine:
             _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p,
                                            ops._stream(self.pixels)))
         fold = self.fold_ln
-        # with variable-resolution inputs an image's keys are its first key_len rows (the records in `seqs` say how many)
-        # and may number 256: more than the tensor-memory kernel's 224, so those towers run the register-tile kernel
-        kv_max = S if self.conv else 0
+        # with variable-resolution inputs an image's keys are its first key_len rows (the records in `seqs` say how many);
+        # the tensor-memory kernel takes up to 256 keys and queries per image, longer sequences fall to the register tiles
+        kv_max = S
         embed = dict(bias=self.bpe, residual=self.pos, out=self.x, stats_out=self.stats_m if fold else None)
         if not self.chain:
             ops.gemm(self.patches, self.wpe, st, **embed)
         def attention():
             ops.attention(self.qkv, self.qkv[:, D:], self.qkv[:, 2 * D:], self.attn, self.seqs, n_heads=H, group=1, head_dim=hd,
                           causal=False, max_q_len=S, q_strides=(3 * D, hd), k_strides=(3 * D, hd, 0), v_strides=(3 * D, hd, 0),
-                          o_strides=(D, hd), max_kv_len=kv_max, q_rows_total=self.M if self.conv else 0,
-                          kv_rows_total=self.M if self.conv else 0, status=st if self.conv else None)
+                          o_strides=(D, hd), max_kv_len=kv_max, q_rows_total=self.M, kv_rows_total=self.M, status=st)
 
         if self.chain:
             self.chain_flags.zero_()

@@ -40,7 +40,8 @@ def test_attention_dense_packed_qkv(B, S):
 
 
 @gpu
-@pytest.mark.parametrize("lens", [[196] * 5, [224, 65, 130, 200], [128, 129], [70], [112, 113, 100, 97], [208, 81, 127]])
+@pytest.mark.parametrize("lens", [[196] * 5, [224, 65, 130, 200], [128, 129], [70], [112, 113, 100, 97], [208, 81, 127],
+                                  [256, 256, 225], [240, 96, 256, 241]])
 def test_attention_tensor_memory_kernel(lens):
     """The tcgen05 kernel (row totals + status words given): ragged sequences packed in one q | k | v matrix, with rows
     past the last sequence left as NaN-free garbage.  Same reference and tolerance as the register-tile kernels."""
@@ -65,7 +66,7 @@ def test_attention_tensor_memory_kernel(lens):
 
 @gpu
 @pytest.mark.parametrize("kind", ["ramp", "step"])
-@pytest.mark.parametrize("n", [196, 224, 120])
+@pytest.mark.parametrize("n", [196, 224, 120, 256])
 def test_attention_tensor_memory_kernel_rising_scores(n, kind):
     """Scores that grow along the keys by far more than a row's softmax reference may lag behind: the one-pass softmax
     has to raise its reference and rescale the probabilities it has already written, in both halves of the keys, and the
