@@ -260,10 +260,11 @@ typedef struct IttaiAttention {
     int32_t max_kv_len;    /* largest kv_rows over the sequences, or 0 if unknown (enables the short-sequence kernel) */
     /* The tensor-memory kernels address q, k and v through TMA tensor maps and need the row counts of the matrices they
      * point into, plus status words for their bounded waits; leave the three at 0/NULL to stay on the register-tile
-     * kernels.  Covered: head_dim 64, dense, 65..256 queries and at most 224 keys per sequence, heads adjacent in a row
+     * kernels.  Covered: head_dim 64, dense, 65..256 queries and at most 256 keys per sequence, heads adjacent in a row
      * (q_head = k_head = v_head = 64, k_seq = v_seq = 0); and head_dim 128 with a key loop, causal or dense, q_head = 128,
-     * keys and values as dense rows (k_row = v_row = 128, head and sequence strides multiples of 128, equal for k and v:
-     * the cache layout), more than 64 queries in some sequence. */
+     * more than 64 queries in some sequence, keys and values either as dense rows (k_row = v_row = 128, head and sequence
+     * strides multiples of 128, equal for k and v: the cache layout) or packed like the queries (k_head = v_head = 128,
+     * k_seq = v_seq = 0, k_row = v_row > 128: the heads of a token side by side in one row). */
     int32_t q_rows_total;  /* rows of the matrix behind q (every sequence's q_row0 + q rows lies inside) */
     int32_t kv_rows_total; /* rows of the matrices behind k and v */
     int32_t reserved0;
