@@ -227,6 +227,9 @@ typedef struct IttaiGemm {
     float stats_eps;        /* LayerNorm epsilon, used when stats_parts > 0 */
     int32_t stats_k;        /* stats_parts > 0: the number of columns of A the statistics are over, when A is zero-padded
                                beyond its true width (the zero columns add nothing to the sums); 0 = k */
+    int32_t stats_rms;      /* stats_parts > 0: 1 = the folded norm is an RMSNorm: mean = 0, rstd = 1 / sqrt(sum x^2 / k + eps)
+                               (col_sums is not used and may hold zeros); the reference's Qwen3 kernels finish their norms
+                               this way (src/ittai/qwen3/base.py:59-78, 84-109).  Allowed with ITTAI_EPI_QKROPE. */
     const IttaiQkRope* qk_rope; /* host pointer, read during the call; required by ITTAI_EPI_QKROPE, NULL otherwise */
 } IttaiGemm;
 

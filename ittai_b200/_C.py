@@ -62,7 +62,7 @@ class Gemm(C.Structure):
         ("ld_a", C.c_int32), ("ld_w", C.c_int32), ("ld_out", C.c_int32), ("ld_res", C.c_int32),
         ("a", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
         ("out", C.c_void_p), ("status", C.c_void_p), ("row_stats", C.c_void_p), ("col_sums", C.c_void_p),
-        ("stats_out", C.c_void_p), ("stats_parts", C.c_int32), ("stats_eps", C.c_float), ("stats_k", C.c_int32), ("qk_rope", C.POINTER(QkRope)),
+        ("stats_out", C.c_void_p), ("stats_parts", C.c_int32), ("stats_eps", C.c_float), ("stats_k", C.c_int32), ("stats_rms", C.c_int32), ("qk_rope", C.POINTER(QkRope)),
     ]
 
 

@@ -213,7 +213,7 @@ gemm2_chain_kernel(const __grid_constant__ ChainParams P) {
                     float s1 = 0.f, s2 = 0.f;
                     for (int i = 0; i < g.stats_parts; ++i) { const float2 tt = ps[i]; s1 += tt.x; s2 += tt.y; }
                     const float inv_k = 1.0f / (float)(g.stats_k > 0 ? g.stats_k : g.K);
-                    mean = s1 * inv_k;
+                    mean = g.stats_rms ? 0.f : s1 * inv_k;
                     rstd = rsqrtf(fmaxf(s2 * inv_k - mean * mean, 0.f) + g.stats_eps);
                 }
             }

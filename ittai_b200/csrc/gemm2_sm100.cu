@@ -22,7 +22,7 @@ namespace ittai {
 // to the output matrix through the staging tile and a TMA store, k and v go to their cache rows through the staging
 // tile with four lanes per 64-byte row piece (whole sectors), each lane having looked up the rows it stores.
 __device__ __forceinline__ void epilogue_qkrope(const GemmArgs& g, const CUtensorMap* tm_out, uint32_t t_addr, unsigned char* so,
-                                                const uint32_t* sgain, uint32_t& cc, int row0, int col0, int lane) {
+                                                const uint32_t* sgain, uint32_t& cc, int row0, int col0, int lane, float row_scale) {
     constexpr int HD = ITTAI_Q3_HD, NKV = ITTAI_Q3_NKV;
     const int head = col0 / HD, t = row0 + lane;
     const bool valid = t < g.M;
@@ -33,7 +33,7 @@ __device__ __forceinline__ void epilogue_qkrope(const GemmArgs& g, const CUtenso
         tmem_ld_32x32(t_addr + 32 * ch, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) pk[16 * ch + i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        for (int i = 0; i < 16; ++i) pk[16 * ch + i] = pack_bf16x2(__uint_as_float(r[2 * i]) * row_scale, __uint_as_float(r[2 * i + 1]) * row_scale);   // a folded RMSNorm's rstd of the row, else 1
     }
     if (head < 24) {
         float ss = 0.f;
@@ -233,7 +233,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         float s1 = 0.f, s2 = 0.f;
                         for (int i = 0; i < g.stats_parts; ++i) { const float2 t = ps[i]; s1 += t.x; s2 += t.y; }
                         const float inv_k = 1.0f / (float)(g.stats_k > 0 ? g.stats_k : g.K);
-                        mean = s1 * inv_k;
+                        mean = g.stats_rms ? 0.f : s1 * inv_k;
                         rstd = rsqrtf(fmaxf(s2 * inv_k - mean * mean, 0.f) + g.stats_eps);
                     }
                 }
@@ -253,7 +253,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tc_fence_after();
             if (g.epi == ITTAI_EPI_QKROPE) {
                 epilogue_qkrope(g, &tm_out, tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PN + kEpiCols * cq), so,
-                                reinterpret_cast<const uint32_t*>(sbias), cc, row0, col0, lane);
+                                reinterpret_cast<const uint32_t*>(sbias), cc, row0, col0, lane, rstd);
             } else
 #pragma unroll 1
             for (uint32_t ch = 0; ch < kChunks && ok; ++ch, ++cc) {

@@ -21,6 +21,7 @@ struct GemmArgs {
     int stats_parts;         // > 0: row_stats holds [M][parts][2] partial sums over K instead of (mean, rstd)
     float stats_eps;
     int stats_k;             // columns the folded LayerNorm's statistics are over (A may be zero-padded beyond them); 0 = K
+    int stats_rms;           // 1: the folded norm is an RMSNorm (mean 0, rstd from the sum of squares alone)
     IttaiQkRope rope;        // ITTAI_EPI_QKROPE only
 };
 

@@ -175,9 +175,10 @@ int gemm_args_from_abi(const IttaiGemm* a, GemmArgs* gp, CUtensorMap* tm_a, CUte
     if (a->epi < ITTAI_EPI_NONE || a->epi > ITTAI_EPI_QKROPE) { set_error("unknown epilogue %d", a->epi); return ITTAI_E_ARG; }
     if (a->epi == ITTAI_EPI_QKROPE) {
         const IttaiQkRope* r = a->qk_rope;
-        if (a->n != ITTAI_Q3_DQKV || a->m <= GM || a->bias || a->residual || a->row_stats || a->stats_out || !r || !r->qn || !r->kn || !r->rope ||
+        if (a->n != ITTAI_Q3_DQKV || a->m <= GM || a->bias || a->residual || (a->row_stats && !(a->stats_rms && a->stats_parts > 0)) || a->stats_out ||
+            !r || !r->qn || !r->kn || !r->rope ||
             !r->pos || !r->seq || !r->slot || !r->kcache_layer || !r->vcache_layer || r->kv_cap < 1) {
-            set_error("the QK-norm + RoPE epilogue needs N = %d, M > %d, no bias / residual / statistics and a complete IttaiQkRope", ITTAI_Q3_DQKV, GM);
+            set_error("the QK-norm + RoPE epilogue needs N = %d, M > %d, no bias / residual / output statistics, row statistics only as RMS partial sums, and a complete IttaiQkRope", ITTAI_Q3_DQKV, GM);
             return ITTAI_E_ARG;
         }
     }
@@ -189,6 +190,7 @@ int gemm_args_from_abi(const IttaiGemm* a, GemmArgs* gp, CUtensorMap* tm_a, CUte
     if (a->stats_out != nullptr && (a->m <= GM || a->epi == ITTAI_EPI_SWIGLU)) { set_error("stats_out needs M > %d and no SwiGLU", GM); return ITTAI_E_ARG; }
     if (a->stats_parts < 0 || a->stats_parts > 64) { set_error("stats_parts %d out of range", a->stats_parts); return ITTAI_E_ARG; }
     if (a->stats_k < 0 || a->stats_k > a->k) { set_error("stats_k %d: between 0 and K", a->stats_k); return ITTAI_E_ARG; }
+    if (a->stats_rms != 0 && (a->stats_rms != 1 || a->stats_parts <= 0)) { set_error("stats_rms is 0 or 1 and needs partial sums (stats_parts > 0)"); return ITTAI_E_ARG; }
     const int ld_a = a->ld_a ? a->ld_a : a->k, ld_w = a->ld_w ? a->ld_w : a->k;
     const int n_out = a->epi == ITTAI_EPI_SWIGLU ? a->n / 2 : a->n;
     const int ld_out = a->ld_out ? a->ld_out : n_out, ld_res = a->ld_res ? a->ld_res : a->n;
@@ -215,6 +217,7 @@ int gemm_args_from_abi(const IttaiGemm* a, GemmArgs* gp, CUtensorMap* tm_a, CUte
     g.stats_parts = a->stats_parts;
     g.stats_eps = a->stats_eps;
     g.stats_k = a->stats_k;
+    g.stats_rms = a->stats_rms;
     if (a->epi == ITTAI_EPI_QKROPE) g.rope = *a->qk_rope; else g.rope = IttaiQkRope{};
     return ITTAI_OK;
 }

@@ -24,7 +24,7 @@ def _stream(t: torch.Tensor):
 def gemm_desc(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, epi: int = _C.EPI_NONE, out: torch.Tensor | None = None,
               row_stats: torch.Tensor | None = None, col_sums: torch.Tensor | None = None, stats_out: torch.Tensor | None = None,
-              stats_eps: float = 0.0, qk_rope: dict | None = None, stats_k: int = 0):
+              stats_eps: float = 0.0, qk_rope: dict | None = None, stats_k: int = 0, stats_rms: bool = False):
     """The ``IttaiGemm`` record of ``gemm(...)`` with the same arguments, and its output tensor: ``(record, out)``.
 
     ``out = epilogue(a @ w.T)`` on the tcgen05 GEMM: a [M, K] and w [N, K] bf16 (last dim contiguous), bias fp32 [N],
@@ -59,6 +59,7 @@ def gemm_desc(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor, bias: torc
         if row_stats.dim() == 3:
             assert row_stats.shape[1] * 128 == k and stats_eps > 0
             g.stats_parts, g.stats_eps, g.stats_k = row_stats.shape[1], stats_eps, stats_k     # stats_k: true width of a zero-padded A
+            g.stats_rms = int(stats_rms)       # RMSNorm: no mean; col_sums unused (zeros)
     if stats_out is not None:
         assert stats_out.dtype == torch.float32 and stats_out.is_contiguous() and tuple(stats_out.shape) == (m, n // 128, 2)
         g.stats_out = stats_out.data_ptr()

@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 from .. import _C, ops
-from .config import BM, D, DQ, DQKV, EPS, FF, HD, NH, NKV, QB
+from .config import BM, D, DGU, DQ, DQKV, EPS, FF, HD, NH, NKV, QB
 from .decoder import _strip, pack_weights, rope_table
 from .tasks import build_tasks
 
@@ -48,9 +48,20 @@ class PrefillCore:
     the reference's Engine owns its buffers: ``src/ittai/qwen3/engine.py:123-134``); weights and the key/value store are
     borrowed."""
 
-    def __init__(self, w: dict, n_layers: int, max_tokens: int, device, fused_rope: bool = True):
+    def __init__(self, w: dict, n_layers: int, max_tokens: int, device, fused_rope: bool = True, fold_norm: bool = False):
         self.w, self.L, self.M, self.dev = w, n_layers, max_tokens, device
         self.fused_rope = fused_rope       # QK-norm + RoPE + cache scatter inside the QKV GEMM's epilogue (needs > 128 rows)
+        # ``fold_norm``: the RMSNorms in front of the QKV and gate/up projections are folded into those GEMMs, as in the
+        # reference's kernels (``src/ittai/qwen3/engine.py:107-114``: gain folded into the weights in fp32 and rounded once;
+        # ``base.py:59-78``: the residual epilogue before leaves per-row partial sums of squares, the consuming epilogue
+        # applies rstd): no norm kernel is left in a layer but the very first.  Off, every rounding point is the eager
+        # module's (what the decoder's prefill uses: its cache feeds the decode loop).
+        self.fold_norm = fold_norm
+        if fold_norm:
+            fold = lambda W, g: (W.float() * g.float()[:, None, :]).to(torch.bfloat16).contiguous()
+            self.wqkv_f, self.wgu_f = fold(w["wqkv"], w["ln1"]), fold(w["wgu"], w["ln2"])
+            self.stats = torch.zeros(max_tokens, D // 128, 2, dtype=torch.float32, device=device)
+            self.zeros_qkv, self.zeros_gu = (torch.zeros(n, dtype=torch.float32, device=device) for n in (DQKV, DGU))
         z = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=device)
         self.h, self.xn, self.qkv, self.attn, self.act = z(max_tokens, D), z(max_tokens, D), z(max_tokens, DQKV), z(max_tokens, DQ), z(max_tokens, FF)
         self.status = ops.new_status(device)
@@ -62,25 +73,35 @@ class PrefillCore:
         h, xn, qkv, attn, act = self.h[:T], self.xn[:T], self.qkv[:T], self.attn[:T], self.act[:T]
         s = ops._stream(h)
         _C.check(L.ittai_embed_rows(tokens.data_ptr(), w["embed"].data_ptr(), h.data_ptr(), T, w["embed"].shape[0], s))
+        fold = self.fold_norm and T > 128
         for l in range(self.L):
             kc, vc = kv_layer(l)
-            ops.rmsnorm_rows(h, w["ln1"][l], EPS, out=xn)
+            # layer 0 reads the embedding rows, which no GEMM epilogue produced: its first norm is a pass of its own
+            folded = fold and l > 0
+            if folded:
+                x_in, wq, ln = h, self.wqkv_f[l], dict(row_stats=self.stats[:T], col_sums=self.zeros_qkv, stats_eps=EPS, stats_rms=True)
+            else:
+                ops.rmsnorm_rows(h, w["ln1"][l], EPS, out=xn)
+                x_in, wq, ln = xn, w["wqkv"][l], {}
             if T > 128 and self.fused_rope:
                 # QK-norm + RoPE + cache scatter inside the QKV GEMM's epilogue (the reference's qkv epilogue, base.py:84-109)
-                ops.gemm(xn, w["wqkv"][l], st, out=qkv, epi=_C.EPI_QKROPE,
+                ops.gemm(x_in, wq, st, out=qkv, epi=_C.EPI_QKROPE, **ln,
                          qk_rope=dict(qn=w["qn"][l], kn=w["kn"][l], rope=rope, pos=pos, seq=seq, slot=slot, kcache=kc, vcache=vc, kv_cap=kv_cap, eps=EPS))
             else:
-                ops.gemm(xn, w["wqkv"][l], st, out=qkv)
+                ops.gemm(x_in, wq, st, out=qkv, **ln)
                 _C.check(L.ittai_qwen3_qk_rope_scatter(qkv.data_ptr(), w["qn"][l].data_ptr(), w["kn"][l].data_ptr(), rope.data_ptr(),
                                                        pos.data_ptr(), seq.data_ptr(), slot.data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                                        T, kv_cap, EPS, s))
             ops.attention(qkv, kc, vc, attn, seqs, n_heads=NH, group=NH // NKV, head_dim=HD, causal=True, max_q_len=max_q_len,
                           q_strides=(DQKV, HD), k_strides=k_strides, v_strides=k_strides, o_strides=(DQ, HD),
                           q_rows_total=T, kv_rows_total=kc.numel() // HD, status=st)
-            ops.gemm(attn, w["wo"][l], st, residual=h, out=h)
-            ops.rmsnorm_rows(h, w["ln2"][l], EPS, out=xn)
-            ops.gemm(xn, w["wgu"][l], st, epi=_C.EPI_SWIGLU, out=act)
-            ops.gemm(act, w["wd"][l], st, residual=h, out=h)
+            ops.gemm(attn, w["wo"][l], st, residual=h, out=h, stats_out=self.stats[:T] if fold else None)
+            if fold:
+                ops.gemm(h, self.wgu_f[l], st, epi=_C.EPI_SWIGLU, out=act, row_stats=self.stats[:T], col_sums=self.zeros_gu, stats_eps=EPS, stats_rms=True)
+            else:
+                ops.rmsnorm_rows(h, w["ln2"][l], EPS, out=xn)
+                ops.gemm(xn, w["wgu"][l], st, epi=_C.EPI_SWIGLU, out=act)
+            ops.gemm(act, w["wd"][l], st, residual=h, out=h, stats_out=self.stats[:T] if fold and l + 1 < self.L else None)
         return h
 
 
@@ -91,7 +112,7 @@ class Engine:
 
     @torch.no_grad()
     def __init__(self, sd, max_tokens, max_seqs, arch=None, tile_n=None, stages=None, kv_block=None, group_m=None, warps=8,
-                 device="cuda", graph=True, fused_rope=True):
+                 device="cuda", graph=True, fused_rope=True, fold_norm=True):
         sd = _strip(sd if isinstance(sd, dict) else sd.state_dict())
         self.dev = torch.device(device)
         self.M, self.Bmax = (max_tokens + BM - 1) // BM * BM, max_seqs
@@ -99,7 +120,7 @@ class Engine:
         self.w = pack_weights(sd, self.L, self.dev)
         self.embed, self.fin_w = self.w["embed"], self.w["fin_w"]
         self.rope = rope_table(self.M, self.dev)
-        self.core = PrefillCore(self.w, self.L, self.M, self.dev, fused_rope=fused_rope)
+        self.core = PrefillCore(self.w, self.L, self.M, self.dev, fused_rope=fused_rope, fold_norm=fold_norm)
         z = lambda *s, dt: torch.zeros(*s, dtype=dt, device=self.dev)
         # one packed key/value store reused by every layer: the embedding pass keeps no cache
         self.kbuf, self.vbuf = z(1, NKV, self.M, HD, dt=torch.bfloat16), z(1, NKV, self.M, HD, dt=torch.bfloat16)

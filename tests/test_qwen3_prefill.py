@@ -40,6 +40,18 @@ def test_engine_embeddings_match_oracle(tiny_hf):
     out2 = emb.embed(ids[::-1]).cpu()
     assert F.cosine_similarity(out2.flip(0), out, dim=-1).min() >= 0.99999
     assert emb.validate(ids[:3]) > 0.999
+    # the same engine with every RMSNorm as a pass of its own (the eager modules' rounding points) instead of folded into
+    # the GEMMs: both clear the gate, and they agree with each other far inside it
+    from ittai_b200.qwen3.engine import Engine
+    assert emb.engine.core.fold_norm
+    plain = Engine(model.state_dict(), 1024, 8, fold_norm=False)
+    out3 = plain.forward(ids).cpu()
+    plain.check()
+    assert not plain.core.fold_norm and F.cosine_similarity(out3, out, dim=-1).min() >= 0.9999
+    for i, s in enumerate(ids):
+        R = ref.Qwen3Ref(model.state_dict(), dims, 256)
+        R.forward(torch.tensor(s))
+        assert F.cosine_similarity(out3[i], R.embed_pool(), dim=0) >= 0.9995
 
 
 @gpu
