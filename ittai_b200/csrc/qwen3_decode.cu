@@ -23,9 +23,7 @@ namespace ittai {
 
 constexpr int D = ITTAI_Q3_D, NKV = ITTAI_Q3_NKV, HD = ITTAI_Q3_HD, FF = ITTAI_Q3_FF;
 constexpr int DQ = ITTAI_Q3_DQ, DKV = ITTAI_Q3_DKV, DQKV = ITTAI_Q3_DQKV, DGU = ITTAI_Q3_DGU;
-#ifndef ATTN_HOLD_MAX_TILES
-#define ATTN_HOLD_MAX_TILES 2
-#endif
+constexpr int kHoldMaxTiles = 2;                 // longest attention split (ring tiles) that still hands its tiles back in pairs
 constexpr int kTile = 128;                       // cache positions per attention tile = one ring entry of K and one of V
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kPartFloats = 12 * 16;             // at most 12 tiles (16 rows x 256 columns) per CTA and phase
@@ -587,7 +585,7 @@ __device__ bool phase_attn(Cta& c, int l) {
         // two tiles (K and V of each: 128 KB) are held before they go back, when the ring has room for that and more and
         // the split is those two tiles; a longer split hands every tile back at once, so that the feeding lane can stay
         // two tiles ahead instead of waiting for 128 KB to come free in one piece
-        const int hold = (c.st.ring_bytes >= 5u * kTile * HD * 2 && n_ring_tiles <= ATTN_HOLD_MAX_TILES) ? 2 : 1;
+        const int hold = (c.st.ring_bytes >= 5u * kTile * HD * 2 && n_ring_tiles <= kHoldMaxTiles) ? 2 : 1;
         for (int j = 0; j * kTile < n_pos; ++j) {
             const int ring_rows = it.n_old - j * kTile < 0 ? 0 : (it.n_old - j * kTile < kTile ? it.n_old - j * kTile : kTile);
             const bool from_ring = j < n_ring_tiles;
