@@ -442,7 +442,13 @@ int attn_tc_launch(const IttaiAttention* p, cudaStream_t st) {
     a.status = p->status;
     a.n_heads = p->n_heads;
     a.n_items = p->n_heads * p->n_seqs;
-    const int grid = std::max(1, std::min(n_sms, a.n_items));
+    // the fewest CTAs that finish in the same number of rounds: 768 items take three rounds on 296 groups and on 256 alike,
+    // and the SMs left out do not draw power (the sustained rate is power-capped)
+    int grid = std::max(1, std::min(n_sms, a.n_items));
+    if (a.n_items > n_sms) {
+        const int rounds = (a.n_items + 2 * n_sms - 1) / (2 * n_sms);
+        grid = std::min(n_sms, ((a.n_items + rounds - 1) / rounds + 1) / 2);
+    }
     const cudaError_t e = kv_box == 224 ? launch_pdl(attn_tc_kernel<224>, dim3(grid), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a)
                                         : launch_pdl(attn_tc_kernel<256>, dim3(grid), dim3(kTcThreads), kTcSmem, st, 1, tq, tk, tv, a);
     return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_tc_kernel");
