@@ -293,9 +293,11 @@ int ittai_layernorm_rows(const void* x, int ld_x, const void* gain, const void* 
 int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void* kn, const void* rope, const int32_t* pos,
                                 const int32_t* seq, const int32_t* slot, void* kcache_layer, void* vcache_layer,
                                 int n_tokens, int kv_cap, float eps, void* stream);
-/* fp32 pixels [B, 3, H, W] -> bf16 patch rows [B * (H/p) * (W/p), 3 p p] in (channel, row, col) order
- * (the torch unfold of src/ittai/siglip/kernel.py:633-637). */
-int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, void* stream);
+/* fp32 pixels [B, 3, H, W] -> bf16 patch rows [B * (H/p) * (W/p)][ld_out]: the first 3 p p columns of a row, in (channel,
+ * row, col) order (the torch unfold of src/ittai/siglip/kernel.py:633-637); ld_out = 0 means dense rows, a larger ld_out
+ * leaves the columns beyond untouched (zero-padded K).  Even patch sizes and widths; H/p and W/p round down, the pixels
+ * beyond the last whole patch are dropped (a stride-p convolution without padding). */
+int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, int ld_out, void* stream);
 /* out[t, :] = table[ids[t], :], rows of 1024 bf16 (src/ittai/qwen3/base.py:147-162). */
 int ittai_embed_rows(const int32_t* ids, const void* table, void* out, int rows, int vocab, void* stream);
 /* Embedding head: out[s] = l2_normalise(rmsnorm(h[rows[s]]) * gain) in fp32 (src/ittai/qwen3/base.py:131-145). */

@@ -106,7 +106,7 @@ def lib() -> C.CDLL:
     L.ittai_layernorm_rows.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, f32, vp]
     L.ittai_row_stats.argtypes = [vp, i32, vp, i32, i32, f32, vp]
     L.ittai_qwen3_qk_rope_scatter.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, vp]
-    L.ittai_siglip_im2col.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+    L.ittai_siglip_im2col.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp]
     L.ittai_embed_rows.argtypes = [vp, vp, vp, i32, i32, vp]
     L.ittai_qwen3_final_pool.argtypes = [vp, vp, vp, vp, i32, f32, vp]
     if L.ittai_version() != ABI_VERSION:

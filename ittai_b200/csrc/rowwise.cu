@@ -207,22 +207,31 @@ __global__ void __launch_bounds__(kRowThreads) qk_rope_scatter_kernel(bf16* __re
     *reinterpret_cast<uint4*>(dst + HD / 2 + 8 * sub) = make_uint4(ohi[0], ohi[1], ohi[2], ohi[3]);
 }
 
-// SigLIP patch gather: fp32 pixels [B, 3, H, W] -> bf16 patches [B * (H/p) * (W/p), 3 * p * p] in (channel, row, col)
-// order, the order a Conv2d weight flattens to (reference src/ittai/siglip/kernel.py:633-637).  One thread per
-// 4 consecutive pixels of a patch row.
-__global__ void __launch_bounds__(256) im2col_kernel(const float* __restrict__ px, bf16* __restrict__ out, int B, int H, int W, int p) {
+// SigLIP patch gather: fp32 pixels [B, 3, H, W] -> bf16 patches [B * (H/p) * (W/p)][ld_out], the first 3 * p * p columns of
+// a row in (channel, row, col) order, the order a Conv2d weight flattens to (reference src/ittai/siglip/kernel.py:633-637);
+// columns beyond are left as they are (a zero-padded K stays zero), and pixels beyond the last whole patch are dropped, as a
+// Conv2d of stride p without padding drops them.  One thread per V consecutive pixels of a patch row:
+// V = 4 when the patch size is a multiple of 4, else 2 (patch 14).
+template <int V>
+__global__ void __launch_bounds__(256) im2col_kernel(const float* __restrict__ px, bf16* __restrict__ out, int B, int H, int W, int p, int ld_out) {
     pdl_trigger();
     pdl_wait();
-    // 32-bit index arithmetic (the host checks that the element count fits); a thread's position inside a patch row
-    // group is fixed across its grid-stride steps when the stride is a multiple of the patch size in 4-pixel units
-    const unsigned gw = W / p, gh = H / p, pp = p * p, kp4 = 3 * pp / 4, p4 = p / 4;
-    const unsigned total = (unsigned)B * gh * gw * kp4;
+    // 32-bit index arithmetic (the host checks that the element count fits)
+    const unsigned gw = W / p, gh = H / p, pp = p * p, kpv = 3 * pp / V, pv = p / V;
+    const unsigned total = (unsigned)B * gh * gw * kpv;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const unsigned patch = i / kp4, col4 = i - patch * kp4;          // element = 4 consecutive pixels of a patch row
-        const unsigned c = col4 / (pp / 4), rem = col4 - c * (pp / 4), py = rem / p4, px4 = rem - py * p4;
+        const unsigned patch = i / kpv, colv = i - patch * kpv;          // element = V consecutive pixels of a patch row
+        const unsigned c = colv / (pp / V), rem = colv - c * (pp / V), py = rem / pv, pxv = rem - py * pv;
         const unsigned b = patch / (gh * gw), pi = patch - b * (gh * gw), pr = pi / gw, pc = pi - pr * gw;
-        const float4 v = __ldg(reinterpret_cast<const float4*>(px + (((size_t)b * 3 + c) * H + pr * p + py) * W + pc * p + px4 * 4));
-        *reinterpret_cast<uint2*>(out + (size_t)i * 4) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+        const float* src = px + (((size_t)b * 3 + c) * H + pr * p + py) * W + pc * p + pxv * V;
+        bf16* dst = out + (size_t)patch * ld_out + (size_t)colv * V;
+        if constexpr (V == 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+        } else {
+            const float2 v = __ldg(reinterpret_cast<const float2*>(src));
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(v.x, v.y);
+        }
     }
 }
 
@@ -314,12 +323,19 @@ extern "C" int ittai_qwen3_qk_rope_scatter(void* qkv, const void* qn, const void
     return launched("qk_rope_scatter_kernel");
 }
 
-extern "C" int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, void* stream) {
-    if (!pixels || !patches || batch < 1 || patch % 4 || height % patch || width % patch) { set_error("im2col: bad argument"); return ITTAI_E_ARG; }
-    if ((unsigned long long)batch * height * width * 3 / 4 >= (1ull << 31)) { set_error("im2col: more than 2^33 pixels values in one call"); return ITTAI_E_ARG; }
-    const size_t total = (size_t)batch * height * width * 3 / 4;
+extern "C" int ittai_siglip_im2col(const float* pixels, void* patches, int batch, int height, int width, int patch, int ld_out, void* stream) {
+    const int row = 3 * patch * patch;
+    if (ld_out == 0) ld_out = row;
+    if (!pixels || !patches || batch < 1 || patch < 2 || patch % 2 || height < patch || width < patch || width % 2 || ld_out < row || ld_out % 2) {
+        set_error("im2col: bad argument (even patch size and image width, ld_out >= 3 p p and even)");
+        return ITTAI_E_ARG;
+    }
+    const int v = patch % 4 == 0 && width % 4 == 0 && ld_out % 4 == 0 ? 4 : 2;
+    if ((unsigned long long)batch * height * width * 3 / v >= (1ull << 31)) { set_error("im2col: too many pixel values in one call"); return ITTAI_E_ARG; }
+    const size_t total = (size_t)batch * height * width * 3 / v;
     const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    launch_pdl(im2col_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, 1, pixels, (bf16*)patches, batch, height, width, patch);
+    if (v == 4) launch_pdl(im2col_kernel<4>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, 1, pixels, (bf16*)patches, batch, height, width, patch, ld_out);
+    else launch_pdl(im2col_kernel<2>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, 1, pixels, (bf16*)patches, batch, height, width, patch, ld_out);
     return launched("im2col_kernel");
 }
 

@@ -159,7 +159,7 @@ class Engine:
         D, S, B, H, hd, eps = self.D, self.S0, self.B, self.H, self.hd, self.eps
         L, st = _C.lib(), self.status
         if self.conv:
-            _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p,
+            _C.check(L.ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p, 0,
                                            ops._stream(self.pixels)))
         fold = self.fold_ln
         # with variable-resolution inputs an image's keys are its first key_len rows (the records in `seqs` say how many);

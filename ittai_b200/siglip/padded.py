@@ -131,10 +131,9 @@ class PaddedEngine:
     def _body(self):
         D, S, B, H, hdp, eps, st = self.D, self.S0, self.B, self.H, self.hdp, self.eps, self.status
         Hp = H * hdp
-        if self.conv:       # patch rows in (channel, row, column) order: what a Conv2d weight flattens to
-            p = self.p
-            rows = self.pixels.unfold(2, p, p).unfold(3, p, p).permute(0, 2, 3, 1, 4, 5).reshape(self.M, self.Kp0)
-            self.patches[:, :self.Kp0].copy_(rows)
+        if self.conv:       # patch rows in (channel, row, column) order: what a Conv2d weight flattens to; the padding columns stay zero
+            _C.check(_C.lib().ittai_siglip_im2col(self.pixels.data_ptr(), self.patches.data_ptr(), B, self.img, self.img, self.p, self.Kp,
+                                                  ops._stream(self.pixels)))
         att = dict(n_heads=H, group=1, head_dim=hdp, causal=False)
 
         def attention():
@@ -222,10 +221,10 @@ class PaddedEngine:
         ops.check_status(self.status)
 
     def launches_per_forward(self) -> int:
-        """Kernels in one forward (all inside one CUDA graph; the patch rows of a fixed-resolution tower come from torch ops)."""
+        """Kernels in one forward (all inside one CUDA graph)."""
         n_l = len(self.layers)
         encoder = (n_l + 1) + n_l if self.chain else 1 + n_l * (5 if self.fold_ln else 7) + (1 if self.fold_ln else 2)
-        return encoder + 5
+        return (1 if self.conv else 0) + encoder + 5
 
     def flops(self, formula: str = "reference") -> float:
         """FLOPs of one forward at the TRUE widths (the padding is overhead, not work); formulas as in ``Engine.flops``."""

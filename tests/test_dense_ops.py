@@ -237,9 +237,15 @@ def test_im2col_embed_pool():
     L = _C.lib()
     px = torch.randn(3, 3, 224, 224, device="cuda")
     out = torch.empty(3 * 196, 768, dtype=torch.bfloat16, device="cuda")
-    _C.check(L.ittai_siglip_im2col(px.data_ptr(), out.data_ptr(), 3, 224, 224, 16, None))
+    _C.check(L.ittai_siglip_im2col(px.data_ptr(), out.data_ptr(), 3, 224, 224, 16, 0, None))
     want = px.unfold(2, 16, 16).unfold(3, 16, 16).permute(0, 2, 3, 1, 4, 5).reshape(3 * 196, 768).to(torch.bfloat16)
     assert torch.equal(out, want)
+    # patch 14 (two pixels per thread) into rows padded from 588 to 640 columns: the padding is left alone
+    px14 = torch.randn(2, 3, 60, 76, device="cuda")   # 4 and 6 pixels beyond the last whole patch
+    out14 = torch.full((2 * 4 * 5, 640), 7.0, dtype=torch.bfloat16, device="cuda")
+    _C.check(L.ittai_siglip_im2col(px14.data_ptr(), out14.data_ptr(), 2, 60, 76, 14, 640, None))
+    want14 = px14[:, :, :56, :70].unfold(2, 14, 14).unfold(3, 14, 14).permute(0, 2, 3, 1, 4, 5).reshape(40, 588).to(torch.bfloat16)
+    assert torch.equal(out14[:, :588], want14) and bool((out14[:, 588:] == 7.0).all())
     table = _rand(500, 1024, seed=9)
     ids = torch.tensor([3, 499, 0, 17], dtype=torch.int32, device="cuda")
     rows = torch.empty(4, 1024, dtype=torch.bfloat16, device="cuda")
