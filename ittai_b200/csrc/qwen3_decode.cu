@@ -494,7 +494,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // of 128 positions (a K entry and a V entry per tile); the row of the token being computed is taken from shared memory
 // and appended to the cache by the split that owns its position.  Each split publishes (m, l, o[2][128]); the first
 // `nc` splits of a head then each merge a slice of the 256 outputs.
+template <int NB>
 __device__ bool phase_attn(Cta& c, int l) {
+    // Four or more sequences: a CTA walks many tiles, and the scores q k of a tile come from the tensor cores (below).
+    // One sequence keeps the fp32 dot products (its two tiles per CTA run at the memory rate as they are), and so do
+    // two (measured 1.4 % slower per step with the tensor-core scores).
+    constexpr bool kMmaScores = NB >= 4;
     const IttaiQwen3Decode& p = c.p;
     const int B = p.batch;
     const int n_splits = attn_splits(c.ncta, B);
@@ -549,7 +554,10 @@ __device__ bool phase_attn(Cta& c, int l) {
                 }
             } else {
                 const float qscale = 0.08838834764831845f * kLog2e;   // head_dim^-0.5 * log2(e)
-                *reinterpret_cast<float4*>(&at->qs[c.warp][4 * c.lane]) = make_float4(r[0] * qscale, r[1] * qscale, r[2] * qscale, r[3] * qscale);
+                if constexpr (kMmaScores)     // the rotated query as it is (bf16 values), the scale goes onto the scores
+                    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(at->qs[c.warp]) + 4 * c.lane) = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+                else
+                    *reinterpret_cast<float4*>(&at->qs[c.warp][4 * c.lane]) = make_float4(r[0] * qscale, r[1] * qscale, r[2] * qscale, r[3] * qscale);
             }
         } else if (c.warp == 3 && has_new) {
             const int e0 = DQ + DKV + g * HD;
@@ -569,10 +577,28 @@ __device__ bool phase_attn(Cta& c, int l) {
         //    modulo 32), with no CTA-wide barrier inside a tile; the 32 private (m, l, o) are merged once at the end.
         const int half = c.lane >> 4, sub = c.lane & 15;
         float q0[8], q1[8], acc0[8], acc1[8];
+        // Tensor-core scores: a warp owns 8 consecutive positions of a tile, rows 0-7 of an m16n8k16 A operand read
+        // straight from the tile (rows 8-15 are zero); the two query heads are N columns.  Rows of a tile are 256 bytes
+        // apart, so rows g and g + 1 read at the same columns would meet in the same banks: even rows read the first 32
+        // dims of a 64-dim window while odd rows read the second 32, then the other way round, with N columns 0, 1
+        // carrying the heads' values of the half the even rows hold and columns 2, 3 those of the half the odd rows
+        // hold.  Row g's scores end up in D[g][2 (g & 1) + head], in lane 4 g + (g & 1).
+        uint4 qf[2][2];
+        const int mg = c.lane >> 2, mt = c.lane & 3;
+        if constexpr (kMmaScores) {
+#pragma unroll
+            for (int wi = 0; wi < 2; ++wi)
+#pragma unroll
+                for (int st = 0; st < 2; ++st)
+                    qf[wi][st] = mg < 4 ? *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(at->qs[mg & 1]) + 64 * wi + 32 * ((mg >> 1) ^ st) + 8 * mt)
+                                        : make_uint4(0u, 0u, 0u, 0u);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            q0[e] = at->qs[0][sub * 8 + e];
-            q1[e] = at->qs[1][sub * 8 + e];
+            if constexpr (!kMmaScores) {
+                q0[e] = at->qs[0][sub * 8 + e];
+                q1[e] = at->qs[1][sub * 8 + e];
+            }
             acc0[e] = 0.f; acc1[e] = 0.f;
         }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -599,27 +625,53 @@ __device__ bool phase_attn(Cta& c, int l) {
                 kt = reinterpret_cast<const bf16*>(pk);
                 vt = reinterpret_cast<const bf16*>(pv);
             }
-            uint4 kk[kTile / 32];
             bool valid[kTile / 32];
-#pragma unroll
-            for (int r = 0; r < kTile / 32; ++r) {
-                const int tl = r * 32 + c.warp * 2 + half;
-                valid[r] = j * kTile + tl < n_pos;
-                if (tl < ring_rows) kk[r] = *reinterpret_cast<const uint4*>(kt + (size_t)tl * HD + sub * 8);
-                else if (has_new && j * kTile + tl == it.n_old) kk[r] = *reinterpret_cast<const uint4*>(at->knew + sub * 8);
-                else kk[r] = make_uint4(0, 0, 0, 0);
-            }
             float s0[kTile / 32], s1[kTile / 32];
+            if constexpr (kMmaScores) {
+                const int tg = c.warp * 8 + mg;                  // the position whose key is row mg of this warp's A operand
+                const bf16* krow = tg < ring_rows ? kt + (size_t)tg * HD : at->knew;
+                const bool live = tg < ring_rows || (has_new && j * kTile + tg == it.n_old);
+                float d[4] = {0.f, 0.f, 0.f, 0.f}, e4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int r = 0; r < kTile / 32; ++r) {
-                float a0 = dot8(kk[r], q0, 0.f), a1 = dot8(kk[r], q1, 0.f);
+                for (int wi = 0; wi < 2; ++wi)
 #pragma unroll
-                for (int o = 8; o > 0; o >>= 1) {
-                    a0 += __shfl_xor_sync(0xffffffffu, a0, o);
-                    a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+                    for (int st = 0; st < 2; ++st) {
+                        uint4 va = make_uint4(0u, 0u, 0u, 0u);
+                        if (live) va = *reinterpret_cast<const uint4*>(krow + 64 * wi + 32 * ((mg & 1) ^ st) + 8 * mt);
+                        mma_bf16_16816(d, va.x, 0u, va.y, 0u, qf[wi][st].x, qf[wi][st].y);
+                        mma_bf16_16816(e4, va.z, 0u, va.w, 0u, qf[wi][st].z, qf[wi][st].w);
+                    }
+                const float qscale = 0.08838834764831845f * kLog2e;
+                const float sa = (d[0] + e4[0]) * qscale, sb = (d[1] + e4[1]) * qscale;
+#pragma unroll
+                for (int r = 0; r < kTile / 32; ++r) {           // this half-warp's position of round r is row 2 r + half
+                    const int tl = c.warp * 8 + 2 * r + half;
+                    valid[r] = j * kTile + tl < n_pos;
+                    const float a0 = __shfl_sync(0xffffffffu, sa, 8 * r + 5 * half), a1 = __shfl_sync(0xffffffffu, sb, 8 * r + 5 * half);
+                    s0[r] = valid[r] ? a0 : -INFINITY;
+                    s1[r] = valid[r] ? a1 : -INFINITY;
                 }
-                s0[r] = valid[r] ? a0 : -INFINITY;
-                s1[r] = valid[r] ? a1 : -INFINITY;
+            } else {
+                uint4 kk[kTile / 32];
+#pragma unroll
+                for (int r = 0; r < kTile / 32; ++r) {
+                    const int tl = r * 32 + c.warp * 2 + half;
+                    valid[r] = j * kTile + tl < n_pos;
+                    if (tl < ring_rows) kk[r] = *reinterpret_cast<const uint4*>(kt + (size_t)tl * HD + sub * 8);
+                    else if (has_new && j * kTile + tl == it.n_old) kk[r] = *reinterpret_cast<const uint4*>(at->knew + sub * 8);
+                    else kk[r] = make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int r = 0; r < kTile / 32; ++r) {
+                    float a0 = dot8(kk[r], q0, 0.f), a1 = dot8(kk[r], q1, 0.f);
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) {
+                        a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                        a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+                    }
+                    s0[r] = valid[r] ? a0 : -INFINITY;
+                    s1[r] = valid[r] ? a1 : -INFINITY;
+                }
             }
             float mt0 = m0, mt1 = m1;
 #pragma unroll
@@ -633,7 +685,7 @@ __device__ bool phase_attn(Cta& c, int l) {
             for (int r = 0; r < kTile / 32; ++r) {
                 const float p0 = ex2_approx(s0[r] - ms0), p1 = ex2_approx(s1[r] - ms1);
                 l0 += p0; l1 += p1;
-                const int tl = r * 32 + c.warp * 2 + half;
+                const int tl = kMmaScores ? c.warp * 8 + 2 * r + half : r * 32 + c.warp * 2 + half;
                 uint4 vr = make_uint4(0, 0, 0, 0);
                 if (tl < ring_rows) vr = *reinterpret_cast<const uint4*>(vt + (size_t)tl * HD + sub * 8);
                 else if (has_new && j * kTile + tl == it.n_old) vr = *reinterpret_cast<const uint4*>(at->vnew + sub * 8);
@@ -1090,7 +1142,7 @@ __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
     const uint32_t tag = tag_of(c, c.step, l);
     switch (phase) {
         case ITTAI_PH_QKV: return phase_qkv<NB>(c, l);
-        case ITTAI_PH_ATTN: return phase_attn(c, l);
+        case ITTAI_PH_ATTN: return phase_attn<NB>(c, l);
         case ITTAI_PH_OPROJ:
             return phase_proj_residual<NB, DQ>(c, ITTAI_PH_OPROJ, c.ws.attn, tag, l == 0 ? nullptr : c.ws.h, tag, c.ws.hmid, tag,
                                                (uint32_t)(c.step * c.p.n_layers + l) + 1u);
