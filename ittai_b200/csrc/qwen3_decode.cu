@@ -60,7 +60,8 @@ __host__ __device__ constexpr size_t q3_fixed_smem_bytes(int nb) {
 
 struct Cta {
     const IttaiQwen3Decode& p;
-    Q3Workspace ws;
+    const Q3Workspace& ws;   // the kernel's own parameter (read from constant memory where a pointer is used) at batch 1 and 2,
+                             // a register copy at batch 4 and 8: see ITTAI_MAKE_CTA
     SmemHdr* hdr;
     uint32_t* xs;       // [NB][FF/2] activations of the current GEMV as packed bf16 pairs (they are bf16 values: half the
                         // shared-memory traffic of fp32 and conflict-free 128-bit reads)
@@ -583,16 +584,7 @@ __device__ bool phase_attn(Cta& c, int l) {
         // dims of a 64-dim window while odd rows read the second 32, then the other way round, with N columns 0, 1
         // carrying the heads' values of the half the even rows hold and columns 2, 3 those of the half the odd rows
         // hold.  Row g's scores end up in D[g][2 (g & 1) + head], in lane 4 g + (g & 1).
-        uint4 qf[2][2];
         const int mg = c.lane >> 2, mt = c.lane & 3;
-        if constexpr (kMmaScores) {
-#pragma unroll
-            for (int wi = 0; wi < 2; ++wi)
-#pragma unroll
-                for (int st = 0; st < 2; ++st)
-                    qf[wi][st] = mg < 4 ? *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(at->qs[mg & 1]) + 64 * wi + 32 * ((mg >> 1) ^ st) + 8 * mt)
-                                        : make_uint4(0u, 0u, 0u, 0u);
-        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             if constexpr (!kMmaScores) {
@@ -632,14 +624,18 @@ __device__ bool phase_attn(Cta& c, int l) {
                 const bf16* krow = tg < ring_rows ? kt + (size_t)tg * HD : at->knew;
                 const bool live = tg < ring_rows || (has_new && j * kTile + tg == it.n_old);
                 float d[4] = {0.f, 0.f, 0.f, 0.f}, e4[4] = {0.f, 0.f, 0.f, 0.f};
+                // the query fragments come from shared memory every tile (four broadcast reads): kept in registers across
+                // the loop they are 16 of the 96 a thread has, and the loop spills
+                const bf16* qrow = reinterpret_cast<const bf16*>(at->qs[mg & 1]) + 8 * mt;
 #pragma unroll
                 for (int wi = 0; wi < 2; ++wi)
 #pragma unroll
                     for (int st = 0; st < 2; ++st) {
-                        uint4 va = make_uint4(0u, 0u, 0u, 0u);
+                        uint4 va = make_uint4(0u, 0u, 0u, 0u), qf = make_uint4(0u, 0u, 0u, 0u);
                         if (live) va = *reinterpret_cast<const uint4*>(krow + 64 * wi + 32 * ((mg & 1) ^ st) + 8 * mt);
-                        mma_bf16_16816(d, va.x, 0u, va.y, 0u, qf[wi][st].x, qf[wi][st].y);
-                        mma_bf16_16816(e4, va.z, 0u, va.w, 0u, qf[wi][st].z, qf[wi][st].w);
+                        if (mg < 4) qf = *reinterpret_cast<const uint4*>(qrow + 64 * wi + 32 * ((mg >> 1) ^ st));
+                        mma_bf16_16816(d, va.x, 0u, va.y, 0u, qf.x, qf.y);
+                        mma_bf16_16816(e4, va.z, 0u, va.w, 0u, qf.z, qf.w);
                     }
                 const float qscale = 0.08838834764831845f * kLog2e;
                 const float sa = (d[0] + e4[0]) * qscale, sb = (d[1] + e4[1]) * qscale;
@@ -1156,8 +1152,14 @@ __device__ __forceinline__ bool run_phase(Cta& c, int phase, int l) {
 // The per-CTA context is brace-initialised inside each kernel.  nvcc 12.9 mis-infers the shared state space for the
 // global pointers of a struct returned by value from a helper that also receives the shared-memory base, so there is
 // deliberately no make_cta() function.
+// The workspace pointers: held by reference to the kernel parameter they cost no registers (nine 64-bit pointers live
+// across every phase otherwise), which at batch 1 is worth 5 % of the token time (611 -> 579 us) and removes the batch-8
+// kernel's spills; the batch-8 step is 2.4 % slower that way at cache length 2048 all the same, so the larger batches keep
+// a register copy.
 #define ITTAI_MAKE_CTA(p, wsp, smem, nb, ring_bytes)                                                              \
-    Cta c{p, wsp, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<uint32_t*>(smem + kHdrBytes),                   \
+    const Q3Workspace ws_copy = wsp;                                                                              \
+    const Q3Workspace& ws_sel = (nb) >= 4 ? ws_copy : wsp;                                                        \
+    Cta c{p, ws_sel, reinterpret_cast<SmemHdr*>(smem), reinterpret_cast<uint32_t*>(smem + kHdrBytes),                \
           reinterpret_cast<SmemAttn*>(smem + kHdrBytes), (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x,       \
           (int)(threadIdx.x & 31), (int)(threadIdx.x >> 5),                                                       \
           Waiter{wsp.sync, p.status, p.spin_limit > 0 ? (uint32_t)p.spin_limit : kSpinLimit},                     \
