@@ -4,9 +4,9 @@
 // walking the visible keys 128 at a time.
 //
 //   warp 0, one lane: TMA loads (Q once; K and V blocks single-buffered, each refilled as soon as the MMA that read it
-//     has completed) and every MMA: S = Q K^T (M128 N128, 8 k-steps over the 128 dims), then O += P V as two
-//     M128 N64 series (one per half of the dims) whose A operand P is read from tensor memory and whose B operand V is
-//     used as loaded (MN-major).
+//     has completed) and every MMA: S = Q K^T (M128 N128, 8 k-steps over the 128 dims), then O += P V as one
+//     M128 N128 series whose A operand P is read from tensor memory and whose B operand V is used as loaded (MN-major:
+//     the two 64-dim swizzle atoms of the tile are one operand, 16 KB apart in the descriptor's leading-dimension field).
 //   warps 1-4: one thread per query row, no cross-thread exchange at all: row maximum over the block's 128 scores,
 //     P = 2^(s*scale - m) packed to bf16 and written back over the consumed S columns, running row sum.  The running
 //     maximum m is only raised when the block's maximum exceeds it by more than 8 (in log2 units): O in tensor memory
@@ -115,7 +115,7 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     if (warp == 0) {
         if (lane == 0) {
-            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128), idesc_o = umma_idesc_bf16(128, 64) | umma_idesc_b_mn;
+            constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128), idesc_o = umma_idesc_bf16(128, 128) | umma_idesc_b_mn;
             bool ok = fa_wait(bar_q, 0, abort_flag);
             for (int j = 0; j < n_blk && ok; ++j) {
                 const uint32_t ph = j & 1;
@@ -148,12 +148,11 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 // ---- O += P V: P from tensor memory (8 columns per 16 keys), V rows 16 at a time, one series per dim half
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const uint64_t dv = umma_desc_sw128(sm + kFaV + half * 16384);
+                {
+                    const uint64_t dv = umma_desc_sw128_mn(sm + kFaV, 16384);      // both 64-dim atoms of the V tile: N = 128
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks)
-                        umma_bf16_tmem_a(tmem_base + kFaOCol + 64 * half, tmem_base + 8 * ks, dv + (uint64_t)ks * (2048 >> 4), idesc_o,
+                        umma_bf16_tmem_a(tmem_base + kFaOCol, tmem_base + 8 * ks, dv + (uint64_t)ks * (2048 >> 4), idesc_o,
                                          (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(bar_o);

@@ -53,6 +53,17 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_tile) {
     d |= (uint64_t)2 << 61;
     return d;
 }
+// The same for an MN-major operand wider than one 64-element atom: `atom_stride` bytes from one 64-element group of the
+// MN dimension to the next (the leading-dimension byte offset; a K-major operand ignores the field).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(const void* smem_tile, uint32_t atom_stride) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(smem_tile) & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((atom_stride >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
 // Instruction descriptor for kind::f16: D fp32, A and B bf16, both K-major, tile M x N.
 // Bit 16 set (umma_idesc_b_mn) makes B MN-major: a [K rows][64 N-elements = 128 B] tile as TMA loads it, 8-row groups
 // 1024 B apart, one K-step of 16 rows = 2048 B.
