@@ -60,8 +60,10 @@ __global__ void __launch_bounds__(kFaThreads, 2)
 attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const AttnFaArgs a) {
     pdl_trigger();
-    const int head = blockIdx.x, mt = blockIdx.y, kvh = head / a.group;
-    const int4 sinfo = a.seqs[blockIdx.z];                 // written by the host long before: safe ahead of pdl_wait
+    // Grid (heads, sequences, query tiles) with the tiles in descending order: CTAs are handed out in index order, so the
+    // causal tiles that walk the most key blocks start first and the last wave is made of the short ones.
+    const int head = blockIdx.x, seq = blockIdx.y, mt = (int)gridDim.z - 1 - (int)blockIdx.z, kvh = head / a.group;
+    const int4 sinfo = a.seqs[seq];                        // written by the host long before: safe ahead of pdl_wait
     const int q_len = sinfo.y, kv_len = sinfo.w, r0 = mt * kFaBlk;
     if (r0 >= q_len) return;                               // the whole CTA: nothing allocated yet
     const int offset = kv_len - q_len;                     // causal: query r sees keys <= r + offset
@@ -88,7 +90,7 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     unsigned long long* bar_o = bars + 5;         // PV of the block done (also: V buffer free)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    const int kv_row = blockIdx.z * a.k_seq_rows + kvh * a.k_head_rows + sinfo.z;   // first key row of this (sequence, kv head)
+    const int kv_row = seq * a.k_seq_rows + kvh * a.k_head_rows + sinfo.z;   // first key row of this (sequence, kv head)
     const int kc = kvh * a.k_head_cols;                                             // and its first column
 
     if (threadIdx.x == 0) {
@@ -294,7 +296,7 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncthreads();
     if (*abort_flag) {
         if (threadIdx.x == 0) {
-            if (atomicCAS(&a.status[0], 0u, (uint32_t)ITTAI_ST_GEMM_TIMEOUT) == 0u) { a.status[1] = blockIdx.x; a.status[2] = blockIdx.z; }
+            if (atomicCAS(&a.status[0], 0u, (uint32_t)ITTAI_ST_GEMM_TIMEOUT) == 0u) { a.status[1] = blockIdx.x; a.status[2] = blockIdx.y; }
             const long long t0 = clock64();
             while (clock64() - t0 < 2000000) {}
         }
@@ -343,7 +345,7 @@ int attn_fa_launch(const IttaiAttention* p, cudaStream_t st) {
     a.k_head_cols = packed ? 128 : 0;
     a.scale_log2 = 1.4426950408889634f * 0.08838834764831845f;
     a.status = p->status;
-    const cudaError_t e = launch_pdl(attn_fa_kernel, dim3(p->n_heads, (p->max_q_len + 127) / 128, p->n_seqs), dim3(kFaThreads), kFaSmem, st, 1, tq, tk, tv, a);
+    const cudaError_t e = launch_pdl(attn_fa_kernel, dim3(p->n_heads, p->n_seqs, (p->max_q_len + 127) / 128), dim3(kFaThreads), kFaSmem, st, 1, tq, tk, tv, a);
     return e == cudaSuccess ? ITTAI_OK : cuda_fail(e, "launch attn_fa_kernel");
 }
 
