@@ -86,7 +86,7 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     unsigned long long* bar_k = bars + 1;         // K block landed (one phase per block)
     unsigned long long* bar_v = bars + 2;         // V block landed
     unsigned long long* bar_s = bars + 3;         // S of the block ready (also: K buffer free)
-    unsigned long long* bar_p = bars + 4;         // P written, O rescaled (128 arrivals)
+    unsigned long long* bar_p = bars + 4;         // P written, O rescaled (one arrival per softmax warp)
     unsigned long long* bar_o = bars + 5;         // PV of the block done (also: V buffer free)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -94,7 +94,7 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int kc = kvh * a.k_head_cols;                                             // and its first column
 
     if (threadIdx.x == 0) {
-        mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 128); mbar_init(bar_o, 1);
+        mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
         *abort_flag = 0;
         fence_mbar_init();
         pdl_wait();                                        // q, k, v come from the kernels before this one
@@ -259,8 +259,10 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 fence_proxy_async_smem();
             }
+            // one arrival per warp: 32 lanes arriving on one barrier word are 32 shared-memory atomics one after the other
             tc_fence_before();
-            fa_arrive(bar_p);
+            __syncwarp();
+            if (lane == 0) fa_arrive(bar_p);
         }
         if (!ok) break;
         // ---- epilogue: O / rowsum -> bf16 -> staging tile (the Q tile is dead) -> whole 256-byte rows
