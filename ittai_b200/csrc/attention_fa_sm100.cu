@@ -7,7 +7,8 @@
 //     has completed) and every MMA: S = Q K^T (M128 N128, 8 k-steps over the 128 dims), then O += P V as one
 //     M128 N128 series whose A operand P is read from tensor memory and whose B operand V is used as loaded (MN-major:
 //     the two 64-dim swizzle atoms of the tile are one operand, 16 KB apart in the descriptor's leading-dimension field).
-//   warps 1-4: one thread per query row, no cross-thread exchange at all: row maximum over the block's 128 scores,
+//   warps 1-4: one thread per query row, no cross-thread exchange at all: row maximum over the block's 128 scores
+//     (all requested from tensor memory at once, the first 64 kept in registers for the second pass),
 //     P = 2^(s*scale - m) packed to bf16 and written back over the consumed S columns, running row sum.  The running
 //     maximum m is only raised when the block's maximum exceeds it by more than 8 (in log2 units): O in tensor memory
 //     then has to be rescaled (load, multiply, store), which is rare after the first blocks; P may exceed 1 by up to
@@ -173,22 +174,33 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tc_fence_after();
             const int lim = row_limit - j * kFaBlk;          // columns 0..lim of this block are visible to this row
             const bool full = __all_sync(0xffffffffu, lim >= kFaBlk - 1);
-            // ---- pass 1: the block's row maximum
+            // ---- pass 1: the block's row maximum.  All 128 scores are requested at once (one wait instead of four round
+            //      trips to tensor memory); the first 64 stay in registers for pass 2, the others are read again there
+            //      (holding all 128 would spill: two CTAs per SM leave a thread 168 registers).
+            uint32_t sv[64], su[64];
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                tmem_ld_32x16(t_row + c0, *reinterpret_cast<uint32_t(*)[16]>(&sv[c0]));
+                tmem_ld_32x16(t_row + 64 + c0, *reinterpret_cast<uint32_t(*)[16]>(&su[c0]));
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+                tmem_ld_tie16(*reinterpret_cast<uint32_t(*)[16]>(&sv[c0]));
+                tmem_ld_tie16(*reinterpret_cast<uint32_t(*)[16]>(&su[c0]));
+            }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kFaBlk; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + c0, v);
-                tmem_ld_wait();
-                if (full) {
+            if (full) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        mx0 = fmaxf(mx0, __uint_as_float(v[i])); mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
-                        mx2 = fmaxf(mx2, __uint_as_float(v[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
-                    }
-                } else {
+                for (int i = 0; i < 64; i += 4) {
+                    mx0 = fmaxf(mx0, fmaxf(__uint_as_float(sv[i]), __uint_as_float(su[i]))); mx1 = fmaxf(mx1, fmaxf(__uint_as_float(sv[i + 1]), __uint_as_float(su[i + 1])));
+                    mx2 = fmaxf(mx2, fmaxf(__uint_as_float(sv[i + 2]), __uint_as_float(su[i + 2]))); mx3 = fmaxf(mx3, fmaxf(__uint_as_float(sv[i + 3]), __uint_as_float(su[i + 3])));
+                }
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) if (c0 + i <= lim) mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+                for (int i = 0; i < 64; ++i) {
+                    if (i <= lim) mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+                    if (64 + i <= lim) mx1 = fmaxf(mx1, __uint_as_float(su[i]));
                 }
             }
             const float bm = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;
@@ -234,17 +246,22 @@ attn_fa_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_st_32x8(t_row + (c0 >> 1), w);
             };
             {
+                // the second half of the scores is on its way again while the first half, still in registers, is worked on
                 uint32_t va[16], vb[16];
-                tmem_ld_32x16(t_row, va);
-#pragma unroll 1
-                for (int c0 = 0; c0 < kFaBlk; c0 += 32) {
-                    tmem_ld_wait16(va);
-                    tmem_ld_32x16(t_row + c0 + 16, vb);
-                    emit_p(va, c0);
-                    tmem_ld_wait16(vb);
-                    if (c0 + 32 < kFaBlk) tmem_ld_32x16(t_row + c0 + 32, va);
-                    emit_p(vb, c0 + 16);
-                }
+                tmem_ld_32x16(t_row + 64, va);
+                tmem_ld_32x16(t_row + 80, vb);
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 16) emit_p(*reinterpret_cast<uint32_t(*)[16]>(&sv[c0]), c0);
+                tmem_ld_wait16(va);
+                tmem_ld_tie16(vb);
+                emit_p(va, 64);
+                tmem_ld_32x16(t_row + 96, va);
+                emit_p(vb, 80);
+                tmem_ld_32x16(t_row + 112, vb);
+                tmem_ld_wait16(va);
+                tmem_ld_tie16(vb);
+                emit_p(va, 96);
+                emit_p(vb, 112);
                 tmem_st_wait();
             }
             if (j == n_blk - 1 && (kv_len & (kFaBlk - 1)) != 0 && kv_len < (j + 1) * kFaBlk) {

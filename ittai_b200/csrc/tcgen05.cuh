@@ -136,6 +136,14 @@ __device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
                  :: "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Names 16 registers of an earlier load behind a wait that has already been issued (an empty statement, ordered after the
+// wait because both are volatile): no use of them can be scheduled above it.
+__device__ __forceinline__ void tmem_ld_tie16(uint32_t (&r)[16]) {
+    asm volatile(""
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+}
 
 // try_wait with a suspend-time hint (nanoseconds): the hardware parks the waiting warp until the phase completes or the
 // time runs out, instead of returning to a poll loop that spends issue slots and power.
